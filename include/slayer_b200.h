@@ -1,0 +1,208 @@
+/*
+ * slayer_b200.h -- C ABI of the B200 (sm_100a) implementation of lava-dl's SLAYER
+ * hot path: Loihi-quantised neuron dynamics, spike functions, time shift and
+ * the causal temporal filter.
+ *
+ * This is the boundary a binding of lava-dl (ctypes today; pybind, cffi, ...)
+ * attaches to.  It replaces the seven JIT-compiled torch extensions of the
+ * reference (src/lava/lib/dl/slayer/neuron/dynamics/{leaky_integrator,
+ * adaptive_threshold,resonator,adaptive_resonator,adaptive_phase_th}.cu,
+ * src/lava/lib/dl/slayer/utils/time/shift.cu, src/lava/lib/dl/slayer/utils/
+ * filter/conv.cu) and the Python loops that run when those are not used.
+ *
+ * Conventions
+ *  - Every tensor is fp32, contiguous, device memory of the CURRENT device,
+ *    shaped [rows, T] with time contiguous: rows = batch * prod(spatial dims).
+ *    The caller owns all memory, including scratch; the library allocates
+ *    nothing and keeps no per-call state.
+ *  - Per-row vectors (states, final states) are float[rows].
+ *  - Decay-like parameters are float[n] with n == 1 (shared) or n == channels;
+ *    row r uses entry (r % rows_per_batch) / decay_block, where rows_per_batch
+ *    = prod(spatial dims) and decay_block = prod(spatial dims after the
+ *    channel dim).  Decays are the reference's "un-scaled integer" values
+ *    (0..4096), sin/cos are already scaled by 4096.
+ *  - Integer semantics follow the reference's CPU code path (int64 tensors,
+ *    truncation toward zero); states are held as int32, so results are exact
+ *    while every state magnitude stays below 2^31 (Loihi states are 24 bit).
+ *  - `stream` is a cudaStream_t passed as void*; kernels are launched on it
+ *    and nothing synchronises.
+ *  - Return value: SB_OK or a negative SB_ERR_*; sb_last_error_string() gives
+ *    the text for the calling thread.  Launch errors are checked after every
+ *    launch (the reference checks none, leaky_integrator.cu:140-150).
+ */
+#ifndef SLAYER_B200_H_
+#define SLAYER_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_OK 0
+#define SB_ERR_INVALID_ARG (-1)
+#define SB_ERR_CUDA (-2)
+#define SB_ERR_UNSUPPORTED (-3)
+
+/* bits of sb_device_status() */
+#define SB_DEV_TMA_TIMEOUT 1u /* a bulk tensor load did not arrive within the bounded wait */
+
+/* Row geometry shared by all time-recurrent entry points. */
+typedef struct sb_geom {
+  int64_t rows;           /* batch * prod(spatial) */
+  int64_t T;              /* time steps (contiguous axis) */
+  int64_t rows_per_batch; /* prod(spatial); only used when a parameter has n > 1 */
+  int64_t decay_block;    /* prod(spatial[1:]); only used when a parameter has n > 1 */
+} sb_geom;
+
+/* ---- library -------------------------------------------------------------- */
+int sb_version(void);
+const char* sb_last_error_string(void);
+/* Reads and clears the sticky device status word of the current device
+ * (synchronises the device). */
+int sb_device_status(unsigned int* bits);
+/* Bytes of scratch a backward call needs per parameter-gradient output
+ * (decay, sin, cos ...).  n is that parameter's element count. */
+int64_t sb_param_grad_scratch_bytes(int64_t rows, int64_t n);
+/* 1 when this [rows, T] problem takes the TMA-tiled kernels (T % 4 == 0, T >= 32,
+ * 16-byte aligned bases), 0 when it takes the plain-load kernels. */
+int sb_uses_tma(const void* base, int64_t T);
+
+/* ---- leaky integrator ------------------------------------------------------
+ * Replaces leaky_integrator.cu:112-153 (LIDynamicsFwd) / leaky_integrator.py:210-231.
+ * thr_scaled = fp32(threshold * w_scale); <= 0 disables the reset.
+ * final_state (nullable) receives y[..., -1]. */
+int sb_li_fwd(const float* x, const float* decay, int64_t n_decay, const float* state, float* y,
+              float* final_state, const sb_geom* g, float thr_scaled, int w_scale, void* stream);
+/* Replaces leaky_integrator.cu:155-200 (LIDynamicsBwd) / leaky_integrator.py:234-259.
+ * grad_decay (nullable, float[n_decay]) needs `y` (saved forward output) and
+ * `scratch` of sb_param_grad_scratch_bytes(rows, n_decay) bytes. */
+int sb_li_bwd(const float* grad_y, const float* y, const float* decay, int64_t n_decay, float* grad_x,
+              float* grad_decay, void* scratch, const sb_geom* g, void* stream);
+
+/* ---- adaptive threshold ----------------------------------------------------
+ * Replaces adaptive_threshold.cu:81-129 / adaptive_threshold.py:237-274.
+ * th_step = int(th_scale * w_scale), th0 = int(th0 * w_scale) (host ints). */
+int sb_ath_fwd(const float* x, const float* ref_state, const float* ref_decay, int64_t n_ref_decay,
+               const float* th_state, const float* th_decay, int64_t n_th_decay, float* threshold,
+               float* refractory, const sb_geom* g, int th_step, int th0, int w_scale, void* stream);
+
+/* ---- adaptive phase threshold ----------------------------------------------
+ * Replaces adaptive_phase_th.cu:89-143 / adaptive_phase_th.py:234-283. */
+int sb_apth_fwd(const float* re, const float* im, const float* im_state, const float* ref_state,
+                const float* ref_decay, int64_t n_ref_decay, const float* th_state, const float* th_decay,
+                int64_t n_th_decay, float* threshold, float* refractory, const sb_geom* g, int th_step, int th0,
+                int w_scale, void* stream);
+
+/* ---- resonator -------------------------------------------------------------
+ * Replaces resonator.cu:151-198 / resonator.py:333-376.
+ * reset != 0 enables the Izhikevich reset; then thr_scaled = fp32(threshold *
+ * w_scale) and im_reset = int(fp32(threshold * w_scale - 1)) (host computes
+ * the subtraction in double, as Python does). */
+int sb_res_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
+               int64_t n_decay, const float* re_state, const float* im_state, float* re, float* im,
+               const sb_geom* g, int reset, float thr_scaled, int im_reset, int w_scale, void* stream);
+/* Replaces resonator.cu:200-263 / resonator.py:379-467; also the backward of
+ * the adaptive resonator (adaptive_resonator.cu:245-308).  grad_sin/grad_cos
+ * (nullable, both or none) need re, im and two scratch areas. */
+int sb_res_bwd(const float* grad_re, const float* grad_im, const float* re, const float* im,
+               const float* sin_decay, const float* cos_decay, int64_t n_decay, float* grad_re_in,
+               float* grad_im_in, float* grad_sin, float* grad_cos, void* scratch_sin, void* scratch_cos,
+               const sb_geom* g, void* stream);
+
+/* ---- adaptive resonator ----------------------------------------------------
+ * Replaces adaptive_resonator.cu:178-243 / adaptive_resonator.py:379-436. */
+int sb_adres_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
+                 int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
+                 int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,
+                 const float* th_state, float* re, float* im, float* threshold, float* refractory,
+                 const sb_geom* g, int th_step, int th0, int w_scale, void* stream);
+
+/* ---- spike functions (element-wise) ----------------------------------------
+ * Replace the ATen op chains of spike/spike.py:64-126.  thr_tensor (nullable)
+ * is a per-element threshold of n floats, else thr is used. */
+int sb_spike_fwd(const float* v, const float* thr_tensor, float thr, float* spike, int64_t n, int graded,
+                 float scale, void* stream);
+int sb_spike_bwd(const float* v, const float* thr_tensor, float thr, const float* grad_spike, float* grad_v,
+                 int64_t n, float tau_rho, float scale_rho, int graded, void* stream);
+/* spike/complex.py:49-167.  imag_last is float[rows] (im at t = -1). */
+int sb_cspike_fwd(const float* re, const float* im, const float* thr_tensor, float thr, const float* imag_last,
+                  float* spike, int64_t rows, int64_t T, int graded, float scale, void* stream);
+int sb_cspike_bwd(const float* re, const float* im, const float* thr_tensor, float thr, const float* grad_spike,
+                  float* grad_re, float* grad_im, int64_t n, float tau_rho, float scale_rho, int graded,
+                  void* stream);
+
+/* ---- fused neurons -----------------------------------------------------------
+ * One pass for what neuron/{cuba,alif,rf,adrf}.py compute with several calls
+ * (dynamics ... spike) when no normalisation sits in between.  Require a
+ * power-of-two w_scale.  Nullable outputs are skipped.
+ *
+ * CUBA (neuron/cuba.py:274-421): thr = fp32(threshold + eps).
+ * Outputs: current (nullable), voltage, spike (nullable);
+ * final_c/final_v/final_s (nullable float[rows]) = last time bin of
+ * current, voltage (before reset) and spike. */
+int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
+                const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
+                float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
+                int w_scale, int graded, float spike_scale, void* stream);
+/* Backward of CUBA and ALIF forward: surrogate gradient + both integrators.
+ * thr_tensor (nullable): per-element threshold (ALIF passes th + ref).
+ * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch. */
+int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
+                const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
+                int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,
+                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream);
+
+/* ALIF (neuron/alif.py:383-591).  mode 0: forward() -> spike, voltage,
+ * thsum = threshold + refractory.  mode 1: dynamics() -> current, voltage,
+ * threshold, refractory (out0..out3). */
+int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
+                const float* ref_decay, int64_t n_ref_decay, const float* th_decay, int64_t n_th_decay,
+                const float* cstate, const float* vstate, const float* ref_state, const float* th_state,
+                float* out0, float* out1, float* out2, float* out3, float* final_c, float* final_v,
+                float* final_th, float* final_ref, float* final_s, const sb_geom* g, int th_step, int th0,
+                int w_scale, int mode, int graded, float spike_scale, void* stream);
+
+/* RF (neuron/rf.py) and ADRF (neuron/adrf.py:439-652).  adapt = 0: outputs
+ * spike, re, im (out0..out2) with scalar threshold.  adapt = 1, mode 0:
+ * spike, re, im, th + ref.  adapt = 1, mode 1: re, im, threshold, refractory. */
+int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
+              int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
+              int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,
+              const float* th_state, float* out0, float* out1, float* out2, float* out3, float* final_re,
+              float* final_im, float* final_th, float* final_ref, float* final_s, const sb_geom* g,
+              float threshold, int th_step, int th0, int w_scale, int adapt, int mode, int graded,
+              float spike_scale, void* stream);
+int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const float* thr_tensor, float thr,
+              const float* sin_decay, const float* cos_decay, int64_t n_decay, float* grad_re_in,
+              float* grad_im_in, float* grad_sin, float* grad_cos, void* scratch_sin, void* scratch_cos,
+              const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream);
+
+/* ---- time shift --------------------------------------------------------------
+ * Replaces shift.cu:80-175 / utils/time/shift.py:46-143:
+ * out[r, t] = in[r, t - d], zero fill, d = int(shift / sampling_time)
+ * (truncation toward zero, negative allowed).  lut (nullable, float[n_lut],
+ * n_lut = rows_per_batch) gives one shift per neuron, else `shift`. */
+int sb_shift(const float* x, const float* lut, int64_t n_lut, float shift, float sampling_time, float* out,
+             int64_t rows, int64_t T, void* stream);
+
+/* ---- causal temporal filter ----------------------------------------------------
+ * Replaces conv.cu:80-172 / utils/filter/conv.py:48-97.
+ * conv: out[r,t] = Ts * sum_{i<K} f[i] * in[r, t-i];  corr: ... in[r, t+i]. */
+int sb_fir_conv(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
+                int64_t T, void* stream);
+int sb_fir_corr(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
+                int64_t T, void* stream);
+/* Fused delay + filter (forward): conv(shift(x, lut), f); and its adjoint
+ * (backward): shift(corr(g, f), -lut).  One read and one write per element. */
+int sb_shift_fir_fwd(const float* x, const float* lut, int64_t n_lut, float shift, float shift_ts,
+                     const float* filter, int64_t K, float sampling_time, float* out, int64_t rows, int64_t T,
+                     void* stream);
+int sb_shift_fir_bwd(const float* grad_out, const float* lut, int64_t n_lut, float shift, float shift_ts,
+                     const float* filter, int64_t K, float sampling_time, float* grad_x, int64_t rows,
+                     int64_t T, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLAYER_B200_H_ */

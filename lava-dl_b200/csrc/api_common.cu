@@ -1,0 +1,288 @@
+// Host-side plumbing shared by every entry point: error text, the sticky device
+// status word, tensor-map encoding, launch planning, the parameter-gradient
+// fold kernel.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+#include <limits.h>
+
+#include "common.cuh"
+#include "rowscan.cuh"
+#include "reduce.cuh"
+
+namespace sb {
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+  return SB_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// device status word
+// ---------------------------------------------------------------------------
+__device__ unsigned int g_dev_status = 0;
+
+static constexpr int kMaxDev = 64;
+static unsigned int* g_status_ptr[kMaxDev] = {nullptr};
+
+unsigned int* status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+    set_error("no usable CUDA device (cudaGetDevice failed)");
+    return nullptr;
+  }
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_dev_status);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "cudaGetSymbolAddress(g_dev_status)");
+      return nullptr;
+    }
+    g_status_ptr[dev] = (unsigned int*)p;
+  }
+  return g_status_ptr[dev];
+}
+
+// ---------------------------------------------------------------------------
+// tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+bool tma_eligible(const void* const* ptrs, int n, int64_t T) {
+  if (T < kTileT || (T & 3)) return false;
+  for (int i = 0; i < n; ++i)
+    if (((uintptr_t)ptrs[i]) & 15u) return false;
+  return encode_fn() != nullptr;
+}
+
+int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return SB_ERR_UNSUPPORTED;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)T, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)T * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileT, (cuuint32_t)kTileR};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld T=%lld base=%p)", (int)r, (long long)rows,
+              (long long)T, base);
+    return SB_ERR_CUDA;
+  }
+  return SB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// thresholds: integer equivalents of fp32 comparisons
+// ---------------------------------------------------------------------------
+template <class Pred>
+static int first_int_where(Pred pred) {  // pred monotone: false ... false true ... true
+  long long lo = INT_MIN, hi = INT_MAX;
+  if (!pred((int)hi)) return INT_MAX;
+  while (lo < hi) {
+    long long mid = lo + (hi - lo) / 2;
+    if (pred((int)mid)) hi = mid; else lo = mid + 1;
+  }
+  return (int)lo;
+}
+
+int int_threshold_ge(float thr) {
+  return first_int_where([thr](int k) { return (float)k >= thr; });
+}
+int int_threshold_ge_scaled(float thr, float w) {
+  return first_int_where([thr, w](int k) {
+    volatile float q = (float)k / w;
+    return q >= thr;
+  });
+}
+
+bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// ---------------------------------------------------------------------------
+// launch planning
+// ---------------------------------------------------------------------------
+struct DevInfo {
+  int sms;
+  size_t smem_per_sm;
+  size_t smem_per_block_optin;
+  bool ok;
+};
+static DevInfo g_dev[kMaxDev];
+
+static const DevInfo& dev_info() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDev) dev = 0;
+  DevInfo& d = g_dev[dev];
+  if (!d.ok) {
+    int v = 0;
+    d.sms = 148; d.smem_per_sm = 228 * 1024; d.smem_per_block_optin = 227 * 1024;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) d.sms = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess && v > 0)
+      d.smem_per_sm = (size_t)v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0)
+      d.smem_per_block_optin = (size_t)v;
+    d.ok = true;
+  }
+  return d;
+}
+
+int sm_count() { return dev_info().sms; }
+
+// Warps never talk to each other, so the CTA size only decides how shared
+// memory is carved up.  Pick the warps-per-CTA (1..4) that keeps the most warps
+// resident per SM (each CTA costs its dynamic bytes plus 1 KB the hardware
+// reserves); small problems take one warp per CTA so every SM gets work.
+LaunchPlan plan_rowscan(int64_t rows, size_t bytes_per_warp, size_t fixed_bytes) {
+  const DevInfo& d = dev_info();
+  const int64_t nwarps = (rows + kTileR - 1) / kTileR;
+  int best_w = 1;
+  long best_res = -1;
+  for (int w = 1; w <= 4; ++w) {
+    const size_t cta = w * bytes_per_warp + fixed_bytes;
+    if (cta > d.smem_per_block_optin) break;
+    long ctas = (long)(d.smem_per_sm / (cta + 1024));
+    if (ctas > 32) ctas = 32;
+    long res = ctas * w;
+    if (res > 64) res = 64;
+    if (res > best_res) { best_res = res; best_w = w; }
+  }
+  if (nwarps <= (int64_t)d.sms * best_res) {
+    // not even one full wave: spread warps over SMs as evenly as possible
+    int w = (int)((nwarps + d.sms - 1) / d.sms);
+    if (w < 1) w = 1;
+    if (w < best_w) best_w = w;
+  }
+  LaunchPlan lp;
+  lp.warps_per_cta = best_w;
+  lp.ctas = (nwarps + best_w - 1) / best_w;
+  lp.smem = best_w * bytes_per_warp + fixed_bytes;
+  return lp;
+}
+
+// Opt a kernel into large dynamic shared memory.  Cheap enough to call per
+// launch; the attribute is per device and per function.
+int prepare_kernel(const void* fn, size_t smem) {
+  SB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  return SB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// parameter-gradient fold
+// ---------------------------------------------------------------------------
+int64_t scratch_slots(int64_t rows, int64_t n) {
+  const int64_t partials = (n <= 1) ? (rows + kTileR - 1) / kTileR : rows;
+  return partials + kFoldSlices * (n < 1 ? 1 : n);
+}
+
+__global__ void fold_stage1(const double* __restrict__ partial, double* __restrict__ stage, RowGeom g, int64_t n,
+                            int64_t nparts) {
+  // grid: (slices, n).  Block (s, c) sums the partials of channel c that fall in slice s.
+  const int64_t c = blockIdx.y;
+  const int s = blockIdx.x;
+  double acc = 0.0;
+  if (n <= 1) {
+    for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < nparts; i += (int64_t)gridDim.x * blockDim.x)
+      acc += partial[i];
+  } else {
+    // rows of channel c: for each batch b, [b*rpb + c*blk, b*rpb + (c+1)*blk)
+    const int64_t batches = g.rows / g.rows_per_batch;
+    const int64_t per = batches * g.decay_block;
+    for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < per; i += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t b = i / g.decay_block, j = i - b * g.decay_block;
+      acc += partial[b * g.rows_per_batch + c * g.decay_block + j];
+    }
+  }
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) stage[c * gridDim.x + s] = acc;
+}
+
+__global__ void fold_stage2(const double* __restrict__ stage, float* __restrict__ out, int slices, int64_t n) {
+  const int64_t c = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= n) return;
+  const int lane = threadIdx.x & 31;
+  double acc = 0.0;
+  for (int s = lane; s < slices; s += 32) acc += stage[c * slices + s];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[c] = (float)acc;
+}
+
+int fold_param_grad(double* scratch, float* out, const RowGeom& g, int64_t n, cudaStream_t st) {
+  if (n < 1) n = 1;
+  const int64_t nparts = (n <= 1) ? (g.rows + kTileR - 1) / kTileR : g.rows;
+  double* stage = scratch + nparts;
+  dim3 grid1(kFoldSlices, (unsigned)n);
+  fold_stage1<<<grid1, 256, 0, st>>>(scratch, stage, g, n, nparts);
+  SB_CUDA(cudaGetLastError());
+  const int wpb = 4;
+  fold_stage2<<<(unsigned)((n + wpb - 1) / wpb), wpb * 32, 0, st>>>(stage, out, kFoldSlices, n);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // namespace sb
+
+// ---------------------------------------------------------------------------
+// extern "C"
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int sb_version(void) { return 100; }
+
+const char* sb_last_error_string(void) { return sb::g_err; }
+
+int sb_device_status(unsigned int* bits) {
+  SB_REQUIRE(bits != nullptr, "bits is null");
+  unsigned int* p = sb::status_ptr();
+  if (!p) return SB_ERR_CUDA;
+  SB_CUDA(cudaDeviceSynchronize());
+  SB_CUDA(cudaMemcpy(bits, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+  SB_CUDA(cudaMemset(p, 0, sizeof(unsigned int)));
+  return SB_OK;
+}
+
+int64_t sb_param_grad_scratch_bytes(int64_t rows, int64_t n) {
+  if (rows < 0) return 0;
+  return sb::scratch_slots(rows, n) * (int64_t)sizeof(double);
+}
+
+int sb_uses_tma(const void* base, int64_t T) {
+  const void* p[1] = {base};
+  return sb::tma_eligible(p, 1, T) ? 1 : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,176 @@
+// Causal temporal filter (utils/filter/conv.py:48-97) as a shared-memory
+// sliding-window kernel, optionally fused with the per-neuron delay
+// (utils/time/shift.py) on its input (forward) or output (adjoint) side.
+//
+// One formulation covers conv, corr and both fused forms:
+//     z[u]   = Ts * sum_m h[m] * S(u + m - off)            u in [0, T)
+//     S(v)   = x[v - d_in]  if 0 <= v < T and 0 <= v - d_in < T else 0
+//     out[t] = z[t + d_out] if 0 <= t + d_out < T else 0
+//   conv : h = reversed filter, off = K - 1, d_in = d_out = 0
+//   corr : h = filter,          off = 0
+//   conv(shift(x, d)) : d_in = d;   shift(corr(g), -d) : d_out = d
+//
+// A block owns one row segment of 1024 outputs: it stages the
+// 1024 + K window in shared memory once (every input element is read from HBM
+// once), then each thread produces 16 consecutive outputs from registers, 16
+// taps at a time (a 32-word window per tap group, read as 128-bit words).
+// Shared memory is skewed by 4 words every 32 so that those 128-bit reads,
+// 64 bytes apart between neighbouring threads, are bank-conflict free.
+// At 64 taps the kernel does 64 FMAs per 8 bytes of HBM traffic, which puts it
+// at the FP32 issue limit rather than the HBM limit.
+#include "api_util.cuh"
+
+using namespace sb;
+
+namespace {
+
+constexpr int kOutPerThread = 16;
+constexpr int kFirThreads = 64;
+constexpr int kSeg = kOutPerThread * kFirThreads;  // outputs per block
+constexpr int kTapGroup = 16;
+
+__device__ __forceinline__ int skew(int i) { return i + ((i >> 5) << 2); }
+
+__global__ void __launch_bounds__(kFirThreads)
+fir_kernel(const float* __restrict__ x, const float* __restrict__ filt, int K, int Kp, bool reverse_taps, int off,
+           const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, bool shift_in, bool shift_out,
+           float ts, float* __restrict__ out, int64_t rows, int T) {
+  extern __shared__ float sm[];
+  float* h = sm;                 // Kp taps (zero padded)
+  float* win = sm + Kp;          // skewed window of kSeg + Kp words
+  const int nwin = kSeg + Kp;
+
+  for (int i = threadIdx.x; i < Kp; i += kFirThreads) {
+    float v = 0.f;
+    if (i < K) v = __ldg(filt + (reverse_taps ? (K - 1 - i) : i));
+    h[i] = v;
+  }
+
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    int d = 0;
+    if (shift_in || shift_out) {
+      const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
+      d = __float2int_rz(__fdiv_rn(sv, shift_ts));
+    }
+    const int d_in = shift_in ? d : 0;
+    const int d_out = shift_out ? d : 0;
+    const int64_t base = row * (int64_t)T;
+    const int t0 = blockIdx.x * kSeg;
+    const int v0 = t0 + d_out - off;  // S index of window word 0
+
+    __syncthreads();  // previous row's window fully consumed (and taps visible)
+    for (int i = threadIdx.x; i < nwin; i += kFirThreads) {
+      const int v = v0 + i;
+      const int s = v - d_in;
+      float val = 0.f;
+      if (v >= 0 && v < T && s >= 0 && s < T) val = __ldg(x + base + s);
+      win[skew(i)] = val;
+    }
+    __syncthreads();
+
+    float acc[kOutPerThread];
+#pragma unroll
+    for (int c = 0; c < kOutPerThread; ++c) acc[c] = 0.f;
+    const int c0 = threadIdx.x * kOutPerThread;
+
+    for (int m0 = 0; m0 < Kp; m0 += kTapGroup) {
+      float hv[kTapGroup];
+#pragma unroll
+      for (int q = 0; q < kTapGroup / 4; ++q) {
+        const float4 f4 = *reinterpret_cast<const float4*>(h + m0 + 4 * q);
+        hv[4 * q] = f4.x; hv[4 * q + 1] = f4.y; hv[4 * q + 2] = f4.z; hv[4 * q + 3] = f4.w;
+      }
+      float xv[kOutPerThread + kTapGroup];
+#pragma unroll
+      for (int q = 0; q < (kOutPerThread + kTapGroup) / 4; ++q) {
+        const float4 x4 = *reinterpret_cast<const float4*>(win + skew(c0 + m0 + 4 * q));
+        xv[4 * q] = x4.x; xv[4 * q + 1] = x4.y; xv[4 * q + 2] = x4.z; xv[4 * q + 3] = x4.w;
+      }
+#pragma unroll
+      for (int m = 0; m < kTapGroup; ++m) {
+#pragma unroll
+        for (int c = 0; c < kOutPerThread; ++c) acc[c] = fmaf(hv[m], xv[c + m], acc[c]);
+      }
+    }
+
+    const int t = t0 + c0;
+    float* dst = out + base + t;
+    const bool vec = ((((uintptr_t)dst) & 15u) == 0) && (t + kOutPerThread <= T);
+#pragma unroll
+    for (int c = 0; c < kOutPerThread; ++c) {
+      const int u = t + c + d_out;
+      acc[c] = (u >= 0 && u < T) ? __fmul_rn(acc[c], ts) : 0.f;
+    }
+    if (vec) {
+#pragma unroll
+      for (int q = 0; q < kOutPerThread / 4; ++q)
+        reinterpret_cast<float4*>(dst)[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < kOutPerThread; ++c)
+        if (t + c < T) dst[c] = acc[c];
+    }
+  }
+}
+
+int launch_fir(const float* x, const float* filt, int64_t K, bool corr, const float* lut, int64_t n_lut, float shift,
+               float shift_ts, bool shift_in, bool shift_out, float ts, float* out, int64_t rows, int64_t T,
+               void* stream) {
+  SB_REQUIRE(rows >= 0 && T >= 0 && T <= 2147483647LL - 4096, "bad geometry");
+  SB_REQUIRE(K >= 1 && K <= 4096, "filter length %lld outside [1, 4096]", (long long)K);
+  if (rows == 0 || T == 0) return SB_OK;
+  SB_REQUIRE(x && filt && out, "null tensor pointer");
+  SB_REQUIRE(x != out, "the filter cannot run in place");
+  if (shift_in || shift_out) {
+    SB_REQUIRE(shift_ts != 0.f, "shift sampling_time must be non-zero");
+    if (lut) SB_REQUIRE(n_lut > 0 && rows % n_lut == 0, "lut of %lld entries does not tile %lld rows",
+                        (long long)n_lut, (long long)rows);
+  }
+  const int Kp = (int)((K + kTapGroup - 1) / kTapGroup) * kTapGroup;
+  const int nwin = kSeg + Kp;
+  const size_t smem = sizeof(float) * (size_t)(Kp + nwin + ((nwin >> 5) << 2) + 8);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !attr_set[dev]) {
+    SB_CUDA(cudaFuncSetAttribute((const void*)fir_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr_set[dev] = true;
+  }
+  const unsigned gx = (unsigned)((T + kSeg - 1) / kSeg);
+  const unsigned gy = (unsigned)(rows < 65535 ? rows : 65535);
+  fir_kernel<<<dim3(gx, gy), kFirThreads, smem, (cudaStream_t)stream>>>(
+      x, filt, (int)K, Kp, !corr, corr ? 0 : (int)K - 1, lut, n_lut, shift, shift_ts, shift_in, shift_out, ts, out,
+      rows, (int)T);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sb_fir_conv(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
+                int64_t T, void* stream) {
+  return launch_fir(x, filter, K, false, nullptr, 0, 0.f, 1.f, false, false, sampling_time, out, rows, T, stream);
+}
+
+int sb_fir_corr(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
+                int64_t T, void* stream) {
+  return launch_fir(x, filter, K, true, nullptr, 0, 0.f, 1.f, false, false, sampling_time, out, rows, T, stream);
+}
+
+int sb_shift_fir_fwd(const float* x, const float* lut, int64_t n_lut, float shift, float shift_ts,
+                     const float* filter, int64_t K, float sampling_time, float* out, int64_t rows, int64_t T,
+                     void* stream) {
+  return launch_fir(x, filter, K, false, lut, n_lut, shift, shift_ts, true, false, sampling_time, out, rows, T,
+                    stream);
+}
+
+int sb_shift_fir_bwd(const float* grad_out, const float* lut, int64_t n_lut, float shift, float shift_ts,
+                     const float* filter, int64_t K, float sampling_time, float* grad_x, int64_t rows, int64_t T,
+                     void* stream) {
+  return launch_fir(grad_out, filter, K, true, lut, n_lut, shift, shift_ts, false, true, sampling_time, grad_x, rows,
+                    T, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,264 @@
+// Entry points for the fused neuron passes: what Neuron.forward() /
+// Neuron.dynamics() of neuron/{cuba,alif,rf,adrf}.py compute with several
+// dynamics calls plus a spike function, done in one walk over time.
+#include <limits.h>
+
+#include "api_util.cuh"
+#include "reduce.cuh"
+#include "rowscan.cuh"
+
+using namespace sb;
+
+static int64_t maxn(std::initializer_list<int64_t> v) {
+  int64_t m = 1;
+  for (int64_t x : v) m = x > m ? x : m;
+  return m;
+}
+static bool counts_ok(std::initializer_list<int64_t> v, int64_t nmax) {
+  for (int64_t x : v)
+    if (!(x == 1 || x == nmax)) return false;
+  return true;
+}
+
+static Surrogate make_surrogate(float tau_rho, float scale_rho, bool graded) {
+  // fp32 arithmetic in the order spike/spike.py:10-23 applies it to 0-dim fp32 tensors
+  Surrogate s;
+  s.tau = tau_rho;
+  volatile float half = scale_rho / 2.0f;
+  volatile float c = half / tau_rho;
+  s.c0 = graded ? scale_rho : c;
+  return s;
+}
+
+static CSurrogate make_csurrogate(float tau_rho, float scale_rho) {
+  // spike/complex.py:144-167, again in fp32
+  CSurrogate s;
+  s.tau = tau_rho;
+  s.scale_rho = scale_rho;
+  volatile float a = 0.5f / tau_rho;
+  volatile float b = 2.0f * tau_rho;
+  volatile float c = (-scale_rho) / tau_rho;
+  s.half_over_tau = a;
+  s.two_tau = b;
+  s.neg_scale_over_tau = c;
+  return s;
+}
+
+extern "C" {
+
+int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
+                const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
+                float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
+                int w_scale, int graded, float spike_scale, void* stream) {
+  RowGeom rg;
+  SB_TRY(check_count(n_cdecay, "current decay"));
+  SB_TRY(check_count(n_vdecay, "voltage decay"));
+  const int64_t nmax = maxn({n_cdecay, n_vdecay});
+  SB_TRY(check_geom(g, &rg, nmax));
+  SB_REQUIRE(counts_ok({n_cdecay, n_vdecay}, nmax), "decay counts disagree");
+  SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
+  SB_REQUIRE(cdecay && vdecay && cstate && vstate, "null parameter pointer");
+  SB_REQUIRE(voltage != nullptr, "voltage output is required");
+  const Scale sc = make_scale(w_scale);
+  // reset: int64 voltage >= Python float (thr * w_scale), evaluated in fp32 (leaky_integrator.py:218-225)
+  const float thr_scaled = (float)(threshold * (double)w_scale);
+  const int k_reset = thr_scaled > 0.f ? int_threshold_ge(thr_scaled) : INT_MAX;
+  // spike: fp32 voltage >= fp32(threshold) (spike/spike.py:86-88)
+  const int k_spike = int_threshold_ge_scaled((float)threshold, sc.w);
+  cudaStream_t st = (cudaStream_t)stream;
+  const float* in[1] = {x};
+#define SB_GO(C, S, G)                                                                              \
+  {                                                                                                 \
+    typename CubaFwd<C, S, G>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate,     \
+                                        final_c, final_v, final_s, k_reset, k_spike, spike_scale, sc}; \
+    float* out[3];                                                                                  \
+    int no = 0;                                                                                     \
+    if (C) out[no++] = current;                                                                     \
+    out[no++] = voltage;                                                                            \
+    if (S) out[no++] = spike;                                                                       \
+    return launch_rowscan<CubaFwd<C, S, G>>(p, rg, in, out, st);                                    \
+  }
+  if (current) {
+    if (spike) { if (graded) SB_GO(true, true, true) else SB_GO(true, true, false) }
+    else SB_GO(true, false, false)
+  } else {
+    if (spike) { if (graded) SB_GO(false, true, true) else SB_GO(false, true, false) }
+    else SB_GO(false, false, false)
+  }
+#undef SB_GO
+}
+
+int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
+                const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
+                int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,
+                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream) {
+  RowGeom rg;
+  SB_TRY(check_count(n_cdecay, "current decay"));
+  SB_TRY(check_count(n_vdecay, "voltage decay"));
+  const int64_t nmax = maxn({n_cdecay, n_vdecay});
+  SB_TRY(check_geom(g, &rg, nmax));
+  SB_REQUIRE(counts_ok({n_cdecay, n_vdecay}, nmax), "decay counts disagree");
+  SB_REQUIRE(cdecay && vdecay, "null parameter pointer");
+  SB_REQUIRE((grad_cdecay == nullptr) == (grad_vdecay == nullptr), "decay gradients come together");
+  const bool dgrad = grad_cdecay != nullptr;
+  if (dgrad)
+    SB_REQUIRE(current && scratch_c && scratch_v && scratch_c != scratch_v,
+               "decay gradients need the saved current and two scratch areas");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dgrad && (rg.rows == 0 || rg.T == 0)) {
+    SB_CUDA(cudaMemsetAsync(grad_cdecay, 0, sizeof(float) * n_cdecay, st));
+    SB_CUDA(cudaMemsetAsync(grad_vdecay, 0, sizeof(float) * n_vdecay, st));
+    return SB_OK;
+  }
+  const Surrogate sg = make_surrogate(tau_rho, scale_rho, graded != 0);
+  float* out[1] = {grad_x};
+#define SB_GO(TT, G, D)                                                                             \
+  {                                                                                                 \
+    typename CubaBwd<TT, G, D>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, sg, thr,           \
+                                         (double*)scratch_c, (double*)scratch_v};                   \
+    const float* in[4];                                                                             \
+    int ni = 0;                                                                                     \
+    in[ni++] = grad_spike;                                                                          \
+    in[ni++] = voltage;                                                                             \
+    if (TT) in[ni++] = thr_tensor;                                                                  \
+    if (D) in[ni++] = current;                                                                      \
+    SB_TRY((launch_rowscan<CubaBwd<TT, G, D>>(p, rg, in, out, st)));                                \
+  }
+  const bool tt = thr_tensor != nullptr;
+  if (tt) {
+    if (graded) { if (dgrad) SB_GO(true, true, true) else SB_GO(true, true, false) }
+    else        { if (dgrad) SB_GO(true, false, true) else SB_GO(true, false, false) }
+  } else {
+    if (graded) { if (dgrad) SB_GO(false, true, true) else SB_GO(false, true, false) }
+    else        { if (dgrad) SB_GO(false, false, true) else SB_GO(false, false, false) }
+  }
+#undef SB_GO
+  if (dgrad) {
+    SB_TRY(fold_param_grad((double*)scratch_c, grad_cdecay, rg, n_cdecay, st));
+    SB_TRY(fold_param_grad((double*)scratch_v, grad_vdecay, rg, n_vdecay, st));
+  }
+  return SB_OK;
+}
+
+int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
+                const float* ref_decay, int64_t n_ref_decay, const float* th_decay, int64_t n_th_decay,
+                const float* cstate, const float* vstate, const float* ref_state, const float* th_state,
+                float* out0, float* out1, float* out2, float* out3, float* final_c, float* final_v,
+                float* final_th, float* final_ref, float* final_s, const sb_geom* g, int th_step, int th0,
+                int w_scale, int mode, int graded, float spike_scale, void* stream) {
+  RowGeom rg;
+  SB_TRY(check_count(n_cdecay, "current decay"));
+  SB_TRY(check_count(n_vdecay, "voltage decay"));
+  SB_TRY(check_count(n_ref_decay, "refractory decay"));
+  SB_TRY(check_count(n_th_decay, "threshold decay"));
+  const int64_t nmax = maxn({n_cdecay, n_vdecay, n_ref_decay, n_th_decay});
+  SB_TRY(check_geom(g, &rg, nmax));
+  SB_REQUIRE(counts_ok({n_cdecay, n_vdecay, n_ref_decay, n_th_decay}, nmax), "decay counts disagree");
+  SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
+  SB_REQUIRE(cdecay && vdecay && ref_decay && th_decay && cstate && vstate && ref_state && th_state,
+             "null parameter pointer");
+  SB_REQUIRE(mode == 0 || mode == 1, "mode must be 0 (forward) or 1 (dynamics)");
+  const Scale sc = make_scale(w_scale);
+  AthParams ap{{ref_decay, n_ref_decay}, {th_decay, n_th_decay}, ref_state, th_state, th_step, th0};
+  cudaStream_t st = (cudaStream_t)stream;
+  const float* in[1] = {x};
+  float* out[4] = {out0, out1, out2, out3};
+#define SB_GO(D, G)                                                                                  \
+  {                                                                                                  \
+    typename AlifFwd<D, G>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,     \
+                                     final_c, final_v, final_th, final_ref, final_s, spike_scale, sc}; \
+    return launch_rowscan<AlifFwd<D, G>>(p, rg, in, out, st);                                        \
+  }
+  if (mode == 1) SB_GO(true, false)
+  else if (graded) SB_GO(false, true)
+  else SB_GO(false, false)
+#undef SB_GO
+}
+
+int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
+              int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
+              int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,
+              const float* th_state, float* out0, float* out1, float* out2, float* out3, float* final_re,
+              float* final_im, float* final_th, float* final_ref, float* final_s, const sb_geom* g,
+              float threshold, int th_step, int th0, int w_scale, int adapt, int mode, int graded,
+              float spike_scale, void* stream) {
+  RowGeom rg;
+  SB_TRY(check_count(n_decay, "sin/cos decay"));
+  if (!adapt) { n_ref_decay = 1; n_th_decay = 1; }
+  SB_TRY(check_count(n_ref_decay, "refractory decay"));
+  SB_TRY(check_count(n_th_decay, "threshold decay"));
+  const int64_t nmax = maxn({n_decay, n_ref_decay, n_th_decay});
+  SB_TRY(check_geom(g, &rg, nmax));
+  SB_REQUIRE(counts_ok({n_decay, n_ref_decay, n_th_decay}, nmax), "parameter counts disagree");
+  SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
+  SB_REQUIRE(sin_decay && cos_decay && re_state && im_state, "null parameter pointer");
+  SB_REQUIRE(!adapt || (ref_decay && th_decay && ref_state && th_state), "null adaptive parameter pointer");
+  SB_REQUIRE(mode == 0 || (mode == 1 && adapt), "mode 1 (dynamics) exists only for the adaptive neuron");
+  const Scale sc = make_scale(w_scale);
+  ResParams rp{{sin_decay, n_decay}, {cos_decay, n_decay}, re_state, im_state};
+  AthParams ap{{ref_decay, n_ref_decay}, {th_decay, n_th_decay}, ref_state, th_state, th_step, th0};
+  const int k_spike = int_threshold_ge_scaled(threshold, sc.w);
+  cudaStream_t st = (cudaStream_t)stream;
+  const float* in[2] = {re_in, im_in};
+  float* out[4] = {out0, out1, out2, out3};
+#define SB_GO(A, D, G)                                                                               \
+  {                                                                                                  \
+    typename RfFwd<A, D, G>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,      \
+                                      final_s, spike_scale, sc};                                     \
+    return launch_rowscan<RfFwd<A, D, G>>(p, rg, in, out, st);                                       \
+  }
+  if (adapt) {
+    if (mode == 1) SB_GO(true, true, false)
+    else if (graded) SB_GO(true, false, true)
+    else SB_GO(true, false, false)
+  } else {
+    if (graded) SB_GO(false, false, true)
+    else SB_GO(false, false, false)
+  }
+#undef SB_GO
+}
+
+int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const float* thr_tensor, float thr,
+              const float* sin_decay, const float* cos_decay, int64_t n_decay, float* grad_re_in,
+              float* grad_im_in, float* grad_sin, float* grad_cos, void* scratch_sin, void* scratch_cos,
+              const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream) {
+  RowGeom rg;
+  SB_TRY(check_count(n_decay, "sin/cos decay"));
+  SB_TRY(check_geom(g, &rg, n_decay));
+  SB_REQUIRE(sin_decay && cos_decay, "null parameter pointer");
+  SB_REQUIRE((grad_sin == nullptr) == (grad_cos == nullptr), "grad_sin and grad_cos come together");
+  const bool pgrad = grad_sin != nullptr;
+  if (pgrad)
+    SB_REQUIRE(scratch_sin && scratch_cos && scratch_sin != scratch_cos, "parameter gradients need two scratch areas");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (pgrad && (rg.rows == 0 || rg.T == 0)) {
+    SB_CUDA(cudaMemsetAsync(grad_sin, 0, sizeof(float) * n_decay, st));
+    SB_CUDA(cudaMemsetAsync(grad_cos, 0, sizeof(float) * n_decay, st));
+    return SB_OK;
+  }
+  const CSurrogate sg = make_csurrogate(tau_rho, scale_rho);
+  float* out[2] = {grad_re_in, grad_im_in};
+#define SB_GO(TT, G, P)                                                                              \
+  {                                                                                                  \
+    typename RfBwd<TT, G, P>::Params p{{sin_decay, n_decay}, {cos_decay, n_decay}, sg, thr,          \
+                                       (double*)scratch_sin, (double*)scratch_cos};                  \
+    const float* in[4] = {grad_spike, re, im, thr_tensor};                                           \
+    SB_TRY((launch_rowscan<RfBwd<TT, G, P>>(p, rg, in, out, st)));                                   \
+  }
+  const bool tt = thr_tensor != nullptr;
+  if (tt) {
+    if (graded) { if (pgrad) SB_GO(true, true, true) else SB_GO(true, true, false) }
+    else        { if (pgrad) SB_GO(true, false, true) else SB_GO(true, false, false) }
+  } else {
+    if (graded) { if (pgrad) SB_GO(false, true, true) else SB_GO(false, true, false) }
+    else        { if (pgrad) SB_GO(false, false, true) else SB_GO(false, false, false) }
+  }
+#undef SB_GO
+  if (pgrad) {
+    SB_TRY(fold_param_grad((double*)scratch_sin, grad_sin, rg, n_decay, st));
+    SB_TRY(fold_param_grad((double*)scratch_cos, grad_cos, rg, n_decay, st));
+  }
+  return SB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,683 @@
+// Per-step arithmetic of every time-recurrent op on the SLAYER hot path.
+// Each struct plugs into the row-scan skeleton (rowscan.cuh): init() loads the
+// per-row state and parameters into registers, step() advances one time bin,
+// tile_end() runs once per 32 steps, finish() writes per-row results.
+//
+// The arithmetic restates the CPU loops of lava-dl
+// (src/lava/lib/dl/slayer/neuron/dynamics/*.py, spike/*.py); each op cites the
+// lines it follows.  States are int32 with 64-bit products, i.e. exact while
+// every state stays inside int32 (Loihi states are 24 bit); fused ops skip the
+// float round trip between stages, which is the identity for |state| < 2^24 and
+// a power-of-two w_scale (the host only fuses in that case).
+#pragma once
+
+#include "common.cuh"
+
+namespace sb {
+
+// ---------------------------------------------------------------------------
+// Parameter blocks shared by several ops
+// ---------------------------------------------------------------------------
+struct DecayVec {       // un-scaled integer-valued floats, 1 or C entries
+  const float* v;
+  int64_t n;
+};
+
+struct Scale {
+  float w;      // w_scale as float
+  float inv_w;  // exact reciprocal when w_scale is a power of two
+};
+
+__device__ __forceinline__ float load_decay(const DecayVec& d, const RowGeom& g, int64_t row) {
+  return __ldg(d.v + param_index(g, row, d.n));
+}
+
+// Surrogate gradient of the spike function, spike/spike.py:10-23.
+//   binary: scale_rho / 2 / tau_rho * exp(-|v - thr| / tau_rho)
+//   graded: scale_rho * exp(min(v - thr, 0) / tau_rho)
+struct Surrogate {
+  float c0;    // binary: (scale_rho / 2) / tau_rho ; graded: scale_rho
+  float tau;
+};
+template <bool GRADED>
+__device__ __forceinline__ float surrogate(const Surrogate& s, float v, float thr) {
+  const float d = __fsub_rn(v, thr);
+  if (GRADED) return __fmul_rn(s.c0, expf(__fdiv_rn(fminf(d, 0.f), s.tau)));
+  return __fmul_rn(s.c0, expf(__fdiv_rn(-fabsf(d), s.tau)));
+}
+
+// Gradients of the phase-threshold (complex) spike, spike/complex.py:144-167.
+struct CSurrogate {
+  float tau;
+  float scale_rho;
+  float half_over_tau;  // (1 / 2) / tau_rho
+  float two_tau;        // 2 * tau_rho
+  float neg_scale_over_tau;  // -scale_rho / tau_rho
+};
+__device__ __forceinline__ float sgnf(float x) { return (x > 0.f) ? 1.f : ((x < 0.f) ? -1.f : 0.f); }
+template <bool GRADED>
+__device__ __forceinline__ void csurrogate(const CSurrogate& s, float re, float im, float thr, float& d_re,
+                                           float& d_im) {
+  float delta_real;
+  if (GRADED) delta_real = expf(__fdiv_rn(-fmaxf(__fsub_rn(thr, re), 0.f), s.tau));
+  else delta_real = __fmul_rn(s.half_over_tau, expf(__fdiv_rn(-fabsf(__fsub_rn(re, thr)), s.tau)));
+  const float delta_imag = __fmul_rn(s.half_over_tau, expf(__fdiv_rn(-fabsf(im), s.tau)));
+  const float step_real = __fmul_rn(
+      0.5f, __fadd_rn(1.f, __fmul_rn(sgnf(__fsub_rn(re, thr)), __fsub_rn(1.f, __fmul_rn(s.two_tau, delta_real)))));
+  d_re = __fmul_rn(__fmul_rn(s.scale_rho, delta_real), delta_imag);
+  d_im = __fmul_rn(__fmul_rn(__fmul_rn(s.neg_scale_over_tau, sgnf(im)), delta_imag), step_real);
+}
+
+// Per-thread accumulator for parameter gradients: fp32 inside a 32-step tile,
+// fp64 across tiles (keeps the sum of up to 10^9 terms within 1e-5 relative).
+struct GradAcc {
+  float f;
+  double d;
+  __device__ __forceinline__ void reset() { f = 0.f; d = 0.0; }
+  __device__ __forceinline__ void add(float x) { f = __fadd_rn(f, x); }
+  __device__ __forceinline__ void flush() { d += (double)f; f = 0.f; }
+};
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Writes one parameter-gradient partial.  Shared parameter: warp shuffle, one
+// slot per warp.  Per-channel parameter: one slot per row (lanes of a warp may
+// belong to different channels).  reduce_param_grad() folds the slots.
+__device__ __forceinline__ void store_partial(double* partial, bool shared, double v, bool valid, int lane,
+                                              int64_t row, int64_t warp_id) {
+  if (shared) {
+    const double s = warp_sum(valid ? v : 0.0);
+    if (lane == 0) partial[warp_id] = s;
+  } else if (valid) {
+    partial[row] = v;
+  }
+}
+
+// ===========================================================================
+// Leaky integrator forward: leaky_integrator.py:210-231
+//   y[t] = rshift0(y_old * (4096 - int(decay)), 12) + int(w * x[t])
+//   y_old = 0 where float(y[t]) >= thr * w (only when thr * w > 0) else y[t]
+// ===========================================================================
+template <bool RESET, bool POW2>
+struct LiFwd {
+  static constexpr int NIN = 1, NOUT = 1;
+  static constexpr bool REVERSE = false;
+  struct Params {
+    DecayVec decay;
+    const float* state;   // [rows]
+    float* final_state;   // [rows] or null: y[..., -1]
+    int k_reset;          // smallest int whose fp32 value reaches thr * w
+    Scale sc;
+  };
+  int y, mul, k_reset, last;
+  float w, inv_w;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w; k_reset = p.k_reset;
+    y = 0; mul = 4096; last = 0;
+    if (valid) {
+      mul = 4096 - (int)load_decay(p.decay, g, row);
+      y = to_fixed(w, __ldg(p.state + row));
+    }
+  }
+  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[1]) {
+    const int yn = mul_shift12(y, mul) + to_fixed(w, a[0]);
+    b[0] = from_fixed<POW2>(yn, w, inv_w);
+    last = yn;
+    y = (RESET && yn >= k_reset) ? 0 : yn;
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int, int64_t) {
+    if (p.final_state && valid) p.final_state[row] = from_fixed<POW2>(last, w, inv_w);
+  }
+};
+
+// ===========================================================================
+// Leaky integrator backward: leaky_integrator.py:234-259
+//   g[t] = (1 - decay / 4096) * g[t+1] + go[t]   (reset ignored)
+//   grad_decay = sum g[t+1] * y[t]
+// ===========================================================================
+template <bool DGRAD>
+struct LiBwd {
+  static constexpr int NIN = DGRAD ? 2 : 1, NOUT = 1;
+  static constexpr bool REVERSE = true;
+  struct Params {
+    DecayVec decay;
+    double* partial;  // scratch, see store_partial()
+  };
+  float a, gcur;
+  GradAcc acc;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    gcur = 0.f; acc.reset();
+    a = valid ? __fsub_rn(1.f, __fdiv_rn(load_decay(p.decay, g, row), 4096.f)) : 0.f;
+  }
+  __device__ __forceinline__ void step(const float (&in)[NIN], float (&b)[1]) {
+    if (DGRAD) acc.add(__fmul_rn(gcur, in[NIN - 1]));
+    gcur = __fadd_rn(__fmul_rn(a, gcur), in[0]);
+    b[0] = gcur;
+  }
+  __device__ __forceinline__ void tile_end() { if (DGRAD) acc.flush(); }
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int lane,
+                                         int64_t warp_id) {
+    if (DGRAD) store_partial(p.partial, p.decay.n <= 1, acc.d, valid, lane, row, warp_id);
+  }
+};
+
+// ===========================================================================
+// Adaptive threshold + refractory state machine shared by several ops:
+// adaptive_threshold.py:237-274 (and the same lines inside
+// adaptive_phase_th.py:234-283, adaptive_resonator.py:379-436)
+// ===========================================================================
+struct AthParams {
+  DecayVec ref_decay, th_decay;
+  const float* ref_state;  // [rows]
+  const float* th_state;   // [rows]
+  int th_step;             // int(th_scale * w_scale)
+  int th0;                 // int(th0 * w_scale)
+};
+struct AthState {
+  int th, ref, th_mul, ref_mul, th0, th_step;
+  int th_new, ref_new;
+  __device__ __forceinline__ void init(const AthParams& p, const RowGeom& g, int64_t row, bool valid, float w) {
+    th0 = p.th0; th_step = p.th_step;
+    th = th0; ref = 0; th_mul = 4096; ref_mul = 4096; th_new = th0; ref_new = 0;
+    if (valid) {
+      th = to_fixed(w, __ldg(p.th_state + row));
+      ref = to_fixed(w, __ldg(p.ref_state + row));
+      th_mul = 4096 - (int)load_decay(p.th_decay, g, row);
+      ref_mul = 4096 - (int)load_decay(p.ref_decay, g, row);
+    }
+  }
+  __device__ __forceinline__ void decay() {
+    ref_new = mul_shift12(ref, ref_mul);
+    th_new = mul_shift12(th - th0, th_mul) + th0;
+  }
+  __device__ __forceinline__ void commit(bool spike) {
+    th = th_new + (spike ? th_step : 0);
+    ref = ref_new + (spike ? 2 * th_new : 0);
+  }
+};
+
+template <bool POW2>
+struct AthFwd {
+  static constexpr int NIN = 1, NOUT = 2;  // out: threshold, refractory
+  static constexpr bool REVERSE = false;
+  struct Params {
+    AthParams ath;
+    Scale sc;
+  };
+  AthState s;
+  float w, inv_w;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w;
+    s.init(p.ath, g, row, valid, w);
+  }
+  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[2]) {
+    s.decay();
+    const int x = to_fixed(w, a[0]);
+    b[0] = from_fixed<POW2>(s.th_new, w, inv_w);
+    b[1] = from_fixed<POW2>(s.ref_new, w, inv_w);
+    s.commit(x >= s.th_new + s.ref_new);
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params&, const RowGeom&, int64_t, bool, int, int64_t) {}
+};
+
+// Adaptive phase threshold: adaptive_phase_th.py:234-283
+template <bool POW2>
+struct ApthFwd {
+  static constexpr int NIN = 2, NOUT = 2;  // in: re, im; out: threshold, refractory
+  static constexpr bool REVERSE = false;
+  struct Params {
+    AthParams ath;
+    const float* im_state;  // [rows]
+    Scale sc;
+  };
+  AthState s;
+  int im_old;
+  float w, inv_w;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w;
+    s.init(p.ath, g, row, valid, w);
+    im_old = valid ? to_fixed(w, __ldg(p.im_state + row)) : 0;
+  }
+  __device__ __forceinline__ void step(const float (&a)[2], float (&b)[2]) {
+    s.decay();
+    const int re = to_fixed(w, a[0]);
+    const int im = to_fixed(w, a[1]);
+    b[0] = from_fixed<POW2>(s.th_new, w, inv_w);
+    b[1] = from_fixed<POW2>(s.ref_new, w, inv_w);
+    s.commit(re >= s.th_new + s.ref_new && im >= 0 && im_old < 0);
+    im_old = im;
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params&, const RowGeom&, int64_t, bool, int, int64_t) {}
+};
+
+// ===========================================================================
+// Resonator state machine: resonator.py:333-376
+//   re[t] = rshift0(cos*re_o,12) - rshift0(sin*im_o,12) + int(w*re_in[t])
+//   im[t] = rshift0(sin*re_o,12) + rshift0(cos*im_o,12) + int(w*im_in[t])
+//   Izhikevich reset (thr*w >= 0): where float(im[t]) >= thr*w:
+//     re_o = 0, im_o = int(float(thr*w - 1)); elsewhere im_o passes through fp32
+// ===========================================================================
+struct ResParams {
+  DecayVec sin_decay, cos_decay;  // already scaled integer-valued floats, same count
+  const float* re_state;
+  const float* im_state;
+};
+struct ResState {
+  int re, im, sn, cs, re_new, im_new;
+  __device__ __forceinline__ void init(const ResParams& p, const RowGeom& g, int64_t row, bool valid, float w) {
+    re = im = sn = cs = re_new = im_new = 0;
+    if (valid) {
+      sn = (int)load_decay(p.sin_decay, g, row);
+      cs = (int)load_decay(p.cos_decay, g, row);
+      re = to_fixed(w, __ldg(p.re_state + row));
+      im = to_fixed(w, __ldg(p.im_state + row));
+    }
+  }
+  __device__ __forceinline__ void advance(float w, float re_in, float im_in) {
+    re_new = mul_shift12(cs, re) - mul_shift12(sn, im) + to_fixed(w, re_in);
+    im_new = mul_shift12(sn, re) + mul_shift12(cs, im) + to_fixed(w, im_in);
+  }
+  __device__ __forceinline__ void keep() { re = re_new; im = im_new; }
+};
+
+template <bool RESET, bool POW2>
+struct ResFwd {
+  static constexpr int NIN = 2, NOUT = 2;
+  static constexpr bool REVERSE = false;
+  struct Params {
+    ResParams res;
+    int k_thr;     // smallest int whose fp32 value reaches thr * w
+    int im_reset;  // int(float(thr * w - 1))
+    Scale sc;
+  };
+  ResState s;
+  int k_thr, im_reset;
+  float w, inv_w;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w; k_thr = p.k_thr; im_reset = p.im_reset;
+    s.init(p.res, g, row, valid, w);
+  }
+  __device__ __forceinline__ void step(const float (&a)[2], float (&b)[2]) {
+    s.advance(w, a[0], a[1]);
+    b[0] = from_fixed<POW2>(s.re_new, w, inv_w);
+    b[1] = from_fixed<POW2>(s.im_new, w, inv_w);
+    if (RESET) {
+      const bool spk = s.im_new >= k_thr;
+      s.re = spk ? 0 : s.re_new;
+      s.im = spk ? im_reset : __float2int_rz(__int2float_rn(s.im_new));
+    } else {
+      s.keep();
+    }
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params&, const RowGeom&, int64_t, bool, int, int64_t) {}
+};
+
+// Resonator backward: resonator.py:379-467 (also adaptive_resonator.py:439-525)
+template <bool PGRAD>
+struct ResBwd {
+  static constexpr int NIN = PGRAD ? 4 : 2, NOUT = 2;  // in: g_re, g_im, [re, im]
+  static constexpr bool REVERSE = true;
+  struct Params {
+    DecayVec sin_decay, cos_decay;
+    double* partial_sin;
+    double* partial_cos;
+  };
+  float sn, cs, gre, gim;
+  GradAcc asin_, acos_;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    gre = gim = 0.f; sn = cs = 0.f; asin_.reset(); acos_.reset();
+    if (valid) {
+      sn = __fdiv_rn(load_decay(p.sin_decay, g, row), 4096.f);
+      cs = __fdiv_rn(load_decay(p.cos_decay, g, row), 4096.f);
+    }
+  }
+  __device__ __forceinline__ void scan(float go_re, float go_im, float re, float im) {
+    if (PGRAD) {
+      asin_.add(__fadd_rn(__fmul_rn(-gre, im), __fmul_rn(gim, re)));
+      acos_.add(__fadd_rn(__fmul_rn(gre, re), __fmul_rn(gim, im)));
+    }
+    const float nre = __fadd_rn(__fadd_rn(__fmul_rn(cs, gre), __fmul_rn(sn, gim)), go_re);
+    const float nim = __fadd_rn(__fadd_rn(__fmul_rn(-sn, gre), __fmul_rn(cs, gim)), go_im);
+    gre = nre; gim = nim;
+  }
+  __device__ __forceinline__ void step(const float (&a)[NIN], float (&b)[2]) {
+    scan(a[0], a[1], PGRAD ? a[NIN - 2] : 0.f, PGRAD ? a[NIN - 1] : 0.f);
+    b[0] = gre; b[1] = gim;
+  }
+  __device__ __forceinline__ void tile_end() { if (PGRAD) { asin_.flush(); acos_.flush(); } }
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int lane,
+                                         int64_t warp_id) {
+    if (PGRAD) {
+      const bool shared = p.sin_decay.n <= 1;
+      store_partial(p.partial_sin, shared, asin_.d, valid, lane, row, warp_id);
+      store_partial(p.partial_cos, shared, acos_.d, valid, lane, row, warp_id);
+    }
+  }
+};
+
+// Adaptive resonator forward: adaptive_resonator.py:379-436
+template <bool POW2>
+struct AdResFwd {
+  static constexpr int NIN = 2, NOUT = 4;  // out: re, im, threshold, refractory
+  static constexpr bool REVERSE = false;
+  struct Params {
+    ResParams res;
+    AthParams ath;
+    Scale sc;
+  };
+  ResState r;
+  AthState s;
+  float w, inv_w;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w;
+    r.init(p.res, g, row, valid, w);
+    s.init(p.ath, g, row, valid, w);
+  }
+  __device__ __forceinline__ void step(const float (&a)[2], float (&b)[4]) {
+    s.decay();
+    r.advance(w, a[0], a[1]);
+    b[0] = from_fixed<POW2>(r.re_new, w, inv_w);
+    b[1] = from_fixed<POW2>(r.im_new, w, inv_w);
+    b[2] = from_fixed<POW2>(s.th_new, w, inv_w);
+    b[3] = from_fixed<POW2>(s.ref_new, w, inv_w);
+    s.commit(r.im_new >= s.th_new + s.ref_new);
+    r.keep();
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params&, const RowGeom&, int64_t, bool, int, int64_t) {}
+};
+
+// ===========================================================================
+// Fused CUBA neuron forward: neuron/cuba.py:274-421 with norm=None
+//   current = LI(x), voltage = LI(current, reset at threshold), spike(voltage)
+// Outputs (in tile order): [current], voltage, [spike]
+// ===========================================================================
+template <bool OUT_CUR, bool OUT_SPK, bool GRADED>
+struct CubaFwd {
+  static constexpr int NIN = 1, NOUT = 1 + (OUT_CUR ? 1 : 0) + (OUT_SPK ? 1 : 0);
+  static constexpr bool REVERSE = false;
+  static constexpr int IV = OUT_CUR ? 1 : 0, IS = IV + 1;
+  struct Params {
+    DecayVec cdecay, vdecay;
+    const float* cstate;
+    const float* vstate;
+    float* final_c;  // current[..., -1] or null
+    float* final_v;  // voltage[..., -1] (before reset) or null
+    float* final_s;  // spike[..., -1] or null
+    int k_reset;     // reset when v >= k_reset  (float(v) >= f32(thr * w))
+    int k_spike;     // spike when v >= k_spike  (float(v) / w >= f32(thr))
+    float spike_scale;
+    Scale sc;
+  };
+  int c, v, cmul, vmul, k_reset, k_spike, last_v;
+  float w, inv_w, spike_scale, last_s;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w; k_reset = p.k_reset; k_spike = p.k_spike; spike_scale = p.spike_scale;
+    c = v = last_v = 0; cmul = vmul = 4096; last_s = 0.f;
+    if (valid) {
+      cmul = 4096 - (int)load_decay(p.cdecay, g, row);
+      vmul = 4096 - (int)load_decay(p.vdecay, g, row);
+      c = to_fixed(w, __ldg(p.cstate + row));
+      v = to_fixed(w, __ldg(p.vstate + row));
+    }
+  }
+  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[NOUT]) {
+    c = mul_shift12(c, cmul) + to_fixed(w, a[0]);
+    const int vn = mul_shift12(v, vmul) + c;
+    const float vf = from_fixed<true>(vn, w, inv_w);
+    if (OUT_CUR) b[0] = from_fixed<true>(c, w, inv_w);
+    b[IV] = vf;
+    if (OUT_SPK) {
+      const bool s = vn >= k_spike;
+      last_s = GRADED ? __fdiv_rn(__fmul_rn(s ? 1.f : 0.f, vf), spike_scale) : (s ? 1.f : 0.f);
+      b[IS] = last_s;
+    }
+    last_v = vn;
+    v = (vn >= k_reset) ? 0 : vn;
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int, int64_t) {
+    if (!valid) return;
+    if (p.final_c) p.final_c[row] = from_fixed<true>(c, w, inv_w);
+    if (p.final_v) p.final_v[row] = from_fixed<true>(last_v, w, inv_w);
+    if (OUT_SPK && p.final_s) p.final_s[row] = last_s;
+  }
+};
+
+// ===========================================================================
+// Fused backward of CUBA / ALIF forward: spike surrogate (spike/spike.py:112-126)
+// then two reverse leaky-integrator scans (leaky_integrator.py:234-259).
+// Inputs (tile order): g_spike, voltage, [threshold tensor], [current]
+// Output: g_x
+// ===========================================================================
+template <bool TENSOR_THR, bool GRADED, bool DGRAD>
+struct CubaBwd {
+  static constexpr int NIN = 2 + (TENSOR_THR ? 1 : 0) + (DGRAD ? 1 : 0), NOUT = 1;
+  static constexpr bool REVERSE = true;
+  static constexpr int ITH = 2, ICUR = 2 + (TENSOR_THR ? 1 : 0);
+  struct Params {
+    DecayVec cdecay, vdecay;
+    Surrogate sg;
+    float thr;            // scalar threshold (fp32), ignored with a tensor threshold
+    double* partial_c;    // scratch for grad of current decay
+    double* partial_v;    // scratch for grad of voltage decay
+  };
+  float ac, av, gv, gx, thr;
+  Surrogate sg;
+  GradAcc accc, accv;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    gv = gx = 0.f; ac = av = 0.f; thr = p.thr; sg = p.sg; accc.reset(); accv.reset();
+    if (valid) {
+      ac = __fsub_rn(1.f, __fdiv_rn(load_decay(p.cdecay, g, row), 4096.f));
+      av = __fsub_rn(1.f, __fdiv_rn(load_decay(p.vdecay, g, row), 4096.f));
+    }
+  }
+  __device__ __forceinline__ void step(const float (&a)[NIN], float (&b)[1]) {
+    const float vol = a[1];
+    const float th = TENSOR_THR ? a[ITH] : thr;
+    const float gs = __fmul_rn(surrogate<GRADED>(sg, vol, th), a[0]);
+    if (DGRAD) {
+      accv.add(__fmul_rn(gv, vol));
+      accc.add(__fmul_rn(gx, a[ICUR]));
+    }
+    gv = __fadd_rn(__fmul_rn(av, gv), gs);
+    gx = __fadd_rn(__fmul_rn(ac, gx), gv);
+    b[0] = gx;
+  }
+  __device__ __forceinline__ void tile_end() { if (DGRAD) { accc.flush(); accv.flush(); } }
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int lane,
+                                         int64_t warp_id) {
+    if (DGRAD) {
+      store_partial(p.partial_c, p.cdecay.n <= 1, accc.d, valid, lane, row, warp_id);
+      store_partial(p.partial_v, p.vdecay.n <= 1, accv.d, valid, lane, row, warp_id);
+    }
+  }
+};
+
+// ===========================================================================
+// Fused ALIF forward: neuron/alif.py:383-591 with norm=None
+//   current = LI(x); voltage = LI(current) (no reset); (th, ref) = ATh(voltage)
+//   spike = voltage >= th + ref   (fp32 comparison of the returned series)
+// DYN: outputs current, voltage, threshold, refractory (what dynamics() returns)
+// else: outputs spike, voltage, threshold + refractory (what forward() needs)
+// ===========================================================================
+template <bool DYN, bool GRADED>
+struct AlifFwd {
+  static constexpr int NIN = 1, NOUT = DYN ? 4 : 3;
+  static constexpr bool REVERSE = false;
+  struct Params {
+    DecayVec cdecay, vdecay;
+    const float* cstate;
+    const float* vstate;
+    AthParams ath;
+    float* final_c; float* final_v; float* final_th; float* final_ref; float* final_s;  // [rows] or null
+    float spike_scale;
+    Scale sc;
+  };
+  int c, v, cmul, vmul;
+  AthState s;
+  float w, inv_w, spike_scale, last_s;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w; spike_scale = p.spike_scale;
+    c = v = 0; cmul = vmul = 4096; last_s = 0.f;
+    s.init(p.ath, g, row, valid, w);
+    if (valid) {
+      cmul = 4096 - (int)load_decay(p.cdecay, g, row);
+      vmul = 4096 - (int)load_decay(p.vdecay, g, row);
+      c = to_fixed(w, __ldg(p.cstate + row));
+      v = to_fixed(w, __ldg(p.vstate + row));
+    }
+  }
+  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[NOUT]) {
+    c = mul_shift12(c, cmul) + to_fixed(w, a[0]);
+    v = mul_shift12(v, vmul) + c;
+    s.decay();
+    const float vf = from_fixed<true>(v, w, inv_w);
+    const float thf = from_fixed<true>(s.th_new, w, inv_w);
+    const float reff = from_fixed<true>(s.ref_new, w, inv_w);
+    if (DYN) {
+      b[0] = from_fixed<true>(c, w, inv_w); b[1] = vf; b[2] = thf; b[3] = reff;
+    } else {
+      const float thsum = __fadd_rn(thf, reff);
+      const bool sp = vf >= thsum;
+      last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, vf), spike_scale) : (sp ? 1.f : 0.f);
+      b[0] = last_s; b[1] = vf; b[2] = thsum;
+    }
+    s.commit(v >= s.th_new + s.ref_new);
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int, int64_t) {
+    if (!valid) return;
+    if (p.final_c) p.final_c[row] = from_fixed<true>(c, w, inv_w);
+    if (p.final_v) p.final_v[row] = from_fixed<true>(v, w, inv_w);
+    if (p.final_th) p.final_th[row] = from_fixed<true>(s.th_new, w, inv_w);
+    if (p.final_ref) p.final_ref[row] = from_fixed<true>(s.ref_new, w, inv_w);
+    if (!DYN && p.final_s) p.final_s[row] = last_s;
+  }
+};
+
+// ===========================================================================
+// Fused resonate-and-fire forward.
+//   ADAPT = false: neuron/rf.py (resonator, scalar threshold, complex spike)
+//   ADAPT = true : neuron/adrf.py:439-652 (resonator -> adaptive_phase_th ->
+//                  complex spike with tensor threshold th + ref)
+// Complex spike: spike/complex.py:66-92
+//   spike = (re >= thr) * (im[t-1] < 0) * (im >= 0),  im[-1] = imag state
+// DYN (ADAPT only): outputs re, im, threshold, refractory
+// else            : outputs spike, re, im, [threshold + refractory]
+// ===========================================================================
+template <bool ADAPT, bool DYN, bool GRADED>
+struct RfFwd {
+  static_assert(ADAPT || !DYN, "DYN needs ADAPT");
+  static constexpr int NIN = 2, NOUT = ADAPT ? 4 : 3;
+  static constexpr bool REVERSE = false;
+  struct Params {
+    ResParams res;
+    AthParams ath;    // ADAPT only
+    int k_spike;      // !ADAPT: spike needs re >= k_spike (float(re)/w >= f32(thr))
+    float* final_re; float* final_im; float* final_th; float* final_ref; float* final_s;
+    float spike_scale;
+    Scale sc;
+  };
+  ResState r;
+  AthState s;
+  int k_spike, im_old_i;
+  bool im_prev_neg;
+  float w, inv_w, spike_scale, last_s;
+
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    w = p.sc.w; inv_w = p.sc.inv_w; k_spike = p.k_spike; spike_scale = p.spike_scale; last_s = 0.f;
+    r.init(p.res, g, row, valid, w);
+    if (ADAPT) s.init(p.ath, g, row, valid, w);
+    im_old_i = r.im;  // int(w * imag_state): adaptive_phase_th.py:258
+    im_prev_neg = valid ? (__ldg(p.res.im_state + row) < 0.f) : false;  // complex.py:72
+  }
+  __device__ __forceinline__ void step(const float (&a)[2], float (&b)[NOUT]) {
+    r.advance(w, a[0], a[1]);
+    r.keep();
+    const float ref_ = from_fixed<true>(r.re, w, inv_w);
+    const float imf = from_fixed<true>(r.im, w, inv_w);
+    if (ADAPT) {
+      s.decay();
+      const float thf = from_fixed<true>(s.th_new, w, inv_w);
+      const float rff = from_fixed<true>(s.ref_new, w, inv_w);
+      if (DYN) {
+        b[0] = ref_; b[1] = imf; b[2] = thf; b[3] = rff;
+      } else {
+        const float thsum = __fadd_rn(thf, rff);
+        const bool sp = (ref_ >= thsum) && im_prev_neg && (r.im >= 0);
+        last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
+        b[0] = last_s; b[1] = ref_; b[2] = imf; b[3] = thsum;
+      }
+      s.commit(r.re >= s.th_new + s.ref_new && r.im >= 0 && im_old_i < 0);
+      im_old_i = r.im;
+    } else {
+      const bool sp = (r.re >= k_spike) && im_prev_neg && (r.im >= 0);
+      last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
+      b[0] = last_s; b[1] = ref_; b[2] = imf;
+    }
+    im_prev_neg = r.im < 0;
+  }
+  __device__ __forceinline__ void tile_end() {}
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int, int64_t) {
+    if (!valid) return;
+    if (p.final_re) p.final_re[row] = from_fixed<true>(r.re, w, inv_w);
+    if (p.final_im) p.final_im[row] = from_fixed<true>(r.im, w, inv_w);
+    if (ADAPT && p.final_th) p.final_th[row] = from_fixed<true>(s.th_new, w, inv_w);
+    if (ADAPT && p.final_ref) p.final_ref[row] = from_fixed<true>(s.ref_new, w, inv_w);
+    if (!DYN && p.final_s) p.final_s[row] = last_s;
+  }
+};
+
+// ===========================================================================
+// Fused backward of RfFwd: complex-spike gradient (spike/complex.py:144-167)
+// followed by the reverse rotation scan (resonator.py:379-467).
+// Inputs: g_spike, re, im, [threshold tensor]; outputs: g_re_in, g_im_in
+// ===========================================================================
+template <bool TENSOR_THR, bool GRADED, bool PGRAD>
+struct RfBwd {
+  static constexpr int NIN = 3 + (TENSOR_THR ? 1 : 0), NOUT = 2;
+  static constexpr bool REVERSE = true;
+  struct Params {
+    DecayVec sin_decay, cos_decay;
+    CSurrogate sg;
+    float thr;
+    double* partial_sin;
+    double* partial_cos;
+  };
+  ResBwd<PGRAD> scan;
+  CSurrogate sg;
+  float thr;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    typename ResBwd<PGRAD>::Params rp{p.sin_decay, p.cos_decay, p.partial_sin, p.partial_cos};
+    scan.init(rp, g, row, valid);
+    sg = p.sg; thr = p.thr;
+  }
+  __device__ __forceinline__ void step(const float (&a)[NIN], float (&b)[2]) {
+    float dre, dim;
+    csurrogate<GRADED>(sg, a[1], a[2], TENSOR_THR ? a[NIN - 1] : thr, dre, dim);
+    scan.scan(__fmul_rn(a[0], dre), __fmul_rn(a[0], dim), a[1], a[2]);
+    b[0] = scan.gre; b[1] = scan.gim;
+  }
+  __device__ __forceinline__ void tile_end() { scan.tile_end(); }
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom& g, int64_t row, bool valid, int lane,
+                                         int64_t warp_id) {
+    typename ResBwd<PGRAD>::Params rp{p.sin_decay, p.cos_decay, p.partial_sin, p.partial_cos};
+    scan.finish(rp, g, row, valid, lane, warp_id);
+  }
+};
+
+}  // namespace sb

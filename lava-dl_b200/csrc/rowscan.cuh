@@ -1,0 +1,291 @@
+// Row-scan framework: the one kernel skeleton every time-recurrent op uses.
+//
+// Data layout (fixed by the lava-dl API): tensors are [rows, T] fp32 with time
+// contiguous; every row is an independent serial recurrence over T.  One lane
+// owns one row and keeps the recurrence state in registers.  A warp therefore
+// works on a 32-row band and walks it in 32-step time tiles:
+//
+//   global --TMA 2-D tile (32 rows x 128 B, swizzle-128B)--> shared
+//   lane l reads row l of the tile as 128-bit chunks (bank-conflict free),
+//   computes 4 steps per chunk, writes results back IN PLACE into the same
+//   tile slots (row l / chunk c is private to lane l)
+//   shared --TMA 2-D tile store--> global
+//
+// so global traffic is always 128-byte row segments although the math runs
+// "down the rows".  Warps are fully independent (own stages, own mbarriers, no
+// __syncthreads), a CTA is only a packaging unit for shared memory.
+//
+// Pipeline per warp with S stages of max(NIN, NOUT) tiles: while tile k is
+// computed, the loads of tiles k+1 .. k+S-2 are in flight; after the stores of
+// tile k are issued the stage used by tile k-1 is recycled for tile k+S-1 once
+// its stores have finished reading shared memory (bulk wait_group.read).
+//
+// When a tensor cannot be described to TMA (T not a multiple of 4, base not
+// 16-byte aligned, T < 32) the same ops run under rowscan_plain_kernel, which
+// fills the same swizzled tiles with plain coalesced loads.
+#pragma once
+
+#include "common.cuh"
+
+namespace sb {
+
+template <int N>
+struct MapPack {
+  CUtensorMap m[N];
+};
+
+template <int NIN, int NOUT>
+struct RowPtrs {
+  const float* in[NIN];
+  float* out[NOUT];
+};
+
+__host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
+
+// ---------------------------------------------------------------------------
+// One tile: 8 chunks of 4 steps.  nvalid < 32 only for the ragged last tile.
+// ---------------------------------------------------------------------------
+template <class Op, bool FULL>
+__device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, int nvalid) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+#pragma unroll 2
+  for (int cc = 0; cc < 8; ++cc) {
+    const int c = Op::REVERSE ? 7 - cc : cc;
+    if (!FULL && c * 4 >= nvalid) {
+      if (Op::REVERSE) continue; else break;
+    }
+    const uint32_t off = swz_chunk(lane, c);
+    float vin[NIN][4];
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) {
+      const float4 v = *reinterpret_cast<const float4*>(stage + i * kTileBytes + off);
+      vin[i][0] = v.x; vin[i][1] = v.y; vin[i][2] = v.z; vin[i][3] = v.w;
+    }
+    float vout[NOUT][4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = Op::REVERSE ? 3 - jj : jj;
+      float a[NIN], b[NOUT];
+#pragma unroll
+      for (int i = 0; i < NIN; ++i) a[i] = vin[i][j];
+      if (FULL || c * 4 + j < nvalid) {
+        op.step(a, b);
+      } else {
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) b[o] = 0.f;
+      }
+#pragma unroll
+      for (int o = 0; o < NOUT; ++o) vout[o][j] = b[o];
+    }
+#pragma unroll
+    for (int o = 0; o < NOUT; ++o) {
+      *reinterpret_cast<float4*>(stage + o * kTileBytes + off) =
+          make_float4(vout[o][0], vout[o][1], vout[o][2], vout[o][3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// TMA-pipelined kernel
+// ---------------------------------------------------------------------------
+template <class Op, int STAGES>
+__global__ void __launch_bounds__(128)
+rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
+                   const typename Op::Params p, const RowGeom g, unsigned int* status) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+  constexpr int kWarpBytes = STAGES * NT * kTileBytes;
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * nwarps + warp) * kTileR;
+  if (row0 >= g.rows) return;
+  // swizzle-128B tiles need 1024-byte alignment; the launch reserves the slack
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* wsm = smem + (size_t)warp * kWarpBytes;
+  const uint32_t bar0 = smem_u32(smem + (size_t)nwarps * kWarpBytes) + warp * STAGES * 8;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + s * 8, 1);
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  const int T = g.T;
+  const int ntiles = (T + kTileT - 1) / kTileT;
+  const int y = (int)row0;
+
+  auto tile_t0 = [&](int k) { return (Op::REVERSE ? (ntiles - 1 - k) : k) * kTileT; };
+  auto issue_load = [&](int k) {  // lane 0 only
+    const int s = k % STAGES;
+    const uint32_t bar = bar0 + s * 8;
+    mbar_expect_tx(bar, NIN * kTileBytes);
+#pragma unroll
+    for (int i = 0; i < NIN; ++i)
+      tma_load_2d(smem_u32(wsm + (s * NT + i) * kTileBytes), &maps.m[i], tile_t0(k), y, bar);
+  };
+
+  Op op;
+  const int64_t row = row0 + lane;
+  const bool valid = row < g.rows;
+  op.init(p, g, row, valid);
+
+  int issued = 0;
+  if (lane == 0) {
+    for (; issued < STAGES - 1 && issued < ntiles; ++issued) issue_load(issued);
+  }
+
+  bool ok = true;
+  int k = 0;
+  for (; k < ntiles; ++k) {
+    const int s = k % STAGES;
+    if (!mbar_wait(bar0 + s * 8, (k / STAGES) & 1)) { ok = false; break; }
+    uint8_t* stage = wsm + s * NT * kTileBytes;
+    const int t0 = tile_t0(k);
+    const int nvalid = T - t0;
+    if (nvalid >= kTileT) process_tile<Op, true>(op, stage, lane, kTileT);
+    else process_tile<Op, false>(op, stage, lane, nvalid);
+    op.tile_end();
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int o = 0; o < NOUT; ++o)
+        tma_store_2d(&maps.m[NIN + o], t0, y, smem_u32(stage + o * kTileBytes));
+      tma_commit();
+      const int kn = k + STAGES - 1;
+      if (kn < ntiles) {
+        tma_wait_read<1>();  // stores of tile k-1 have left shared memory
+        issue_load(kn);
+      }
+    }
+    __syncwarp();
+  }
+
+  if (lane == 0) tma_wait_all<0>();
+  if (!ok) {
+    // A load never arrived.  Record it, drain what this warp still has in
+    // flight (bounded), and leave without touching per-row outputs.
+    if (lane == 0) {
+      dev_flag(status, SB_DEV_TMA_TIMEOUT);
+      const int last = (k + STAGES - 1 < ntiles) ? k + STAGES - 1 : ntiles;
+      for (int kk = k + 1; kk < last; ++kk) (void)mbar_wait(bar0 + (kk % STAGES) * 8, (kk / STAGES) & 1);
+    }
+    return;
+  }
+  op.finish(p, g, row, valid, lane, (int64_t)blockIdx.x * nwarps + warp);
+}
+
+// ---------------------------------------------------------------------------
+// Plain-load kernel: any T, any alignment.  Same tiles, same ops.
+// ---------------------------------------------------------------------------
+template <class Op>
+__global__ void __launch_bounds__(128)
+rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::Params p, const RowGeom g,
+                     unsigned int* status) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+  extern __shared__ uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int64_t wid = (int64_t)blockIdx.x * nwarps + warp;
+  const int64_t row0 = wid * kTileR;
+  if (row0 >= g.rows) return;
+  uint8_t* stage = smem + (size_t)warp * NT * kTileBytes;
+  (void)status;
+
+  const int T = g.T;
+  const int ntiles = (T + kTileT - 1) / kTileT;
+  const int nrows = (int)((g.rows - row0) < kTileR ? (g.rows - row0) : kTileR);
+
+  Op op;
+  const int64_t row = row0 + lane;
+  const bool valid = row < g.rows;
+  op.init(p, g, row, valid);
+
+  for (int k = 0; k < ntiles; ++k) {
+    const int t0 = (Op::REVERSE ? (ntiles - 1 - k) : k) * kTileT;
+    const int nvalid = T - t0;
+    const bool tin = lane < nvalid;
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) {
+      const float* src = ptrs.in[i] + row0 * (int64_t)T + t0 + lane;
+#pragma unroll 8
+      for (int r = 0; r < kTileR; ++r) {
+        float v = 0.f;
+        if (tin && r < nrows) v = __ldg(src + (int64_t)r * T);
+        *reinterpret_cast<float*>(stage + i * kTileBytes + swz_elem(r, lane)) = v;
+      }
+    }
+    __syncwarp();
+    if (nvalid >= kTileT) process_tile<Op, true>(op, stage, lane, kTileT);
+    else process_tile<Op, false>(op, stage, lane, nvalid);
+    op.tile_end();
+    __syncwarp();
+#pragma unroll
+    for (int o = 0; o < NOUT; ++o) {
+      float* dst = ptrs.out[o] + row0 * (int64_t)T + t0 + lane;
+#pragma unroll 8
+      for (int r = 0; r < kTileR; ++r) {
+        if (tin && r < nrows)
+          dst[(int64_t)r * T] = *reinterpret_cast<const float*>(stage + o * kTileBytes + swz_elem(r, lane));
+      }
+    }
+    __syncwarp();
+  }
+  op.finish(p, g, row, valid, lane, wid);
+}
+
+// ---------------------------------------------------------------------------
+// Host launcher
+// ---------------------------------------------------------------------------
+struct LaunchPlan {
+  int warps_per_cta;
+  int64_t ctas;
+  size_t smem;
+};
+
+LaunchPlan plan_rowscan(int64_t rows, size_t bytes_per_warp, size_t fixed_bytes);
+int prepare_kernel(const void* fn, size_t smem);
+
+template <class Op, int STAGES = 3>
+int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
+                   cudaStream_t st) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+  if (g.rows == 0 || g.T == 0) return SB_OK;
+  SB_REQUIRE(g.rows > 0 && g.rows < (int64_t)2147483647 - 64, "rows out of range: %lld", (long long)g.rows);
+  SB_REQUIRE(g.T > 0, "T out of range");
+  const void* all[NIN + NOUT];
+  for (int i = 0; i < NIN; ++i) all[i] = in[i];
+  for (int o = 0; o < NOUT; ++o) all[NIN + o] = out[o];
+  for (int i = 0; i < NIN + NOUT; ++i) SB_REQUIRE(all[i] != nullptr, "null tensor pointer (slot %d)", i);
+  unsigned int* status = status_ptr();
+  if (!status) return SB_ERR_CUDA;
+
+  if (tma_eligible(all, NIN + NOUT, g.T)) {
+    MapPack<NIN + NOUT> maps;
+    for (int i = 0; i < NIN + NOUT; ++i) {
+      int rc = make_row_map(&maps.m[i], all[i], g.rows, g.T);
+      if (rc != SB_OK) return rc;
+    }
+    const size_t per_warp = (size_t)STAGES * NT * kTileBytes + STAGES * 8;
+    const LaunchPlan lp = plan_rowscan(g.rows, per_warp, 1024);
+    auto fn = rowscan_tma_kernel<Op, STAGES>;
+    int rc = prepare_kernel((const void*)fn, lp.smem);
+    if (rc != SB_OK) return rc;
+    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(maps, p, g, status);
+  } else {
+    RowPtrs<NIN, NOUT> ptrs;
+    for (int i = 0; i < NIN; ++i) ptrs.in[i] = in[i];
+    for (int o = 0; o < NOUT; ++o) ptrs.out[o] = out[o];
+    const size_t per_warp = (size_t)NT * kTileBytes;
+    const LaunchPlan lp = plan_rowscan(g.rows, per_warp, 0);
+    auto fn = rowscan_plain_kernel<Op>;
+    int rc = prepare_kernel((const void*)fn, lp.smem);
+    if (rc != SB_OK) return rc;
+    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(ptrs, p, g, status);
+  }
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // namespace sb

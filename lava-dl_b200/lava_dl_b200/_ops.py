@@ -1,0 +1,432 @@
+"""Functional layer between the torch-facing API and the C ABI.
+
+Every function takes/returns torch tensors, derives the row geometry the
+kernels need from the tensor shape, allocates outputs with torch and launches on
+the current stream.  Nothing here differentiates; autograd wiring lives in the
+``slayer`` sub-modules.
+"""
+
+import math
+
+import numpy as np
+import torch
+
+from . import _native as N
+
+
+def _rows_T(x):
+    T = x.shape[-1]
+    rows = x.numel() // T if T > 0 else 0
+    return rows, T
+
+
+def geom(x, *counts):
+    """``sb_geom`` of a ``[B, C, ..., T]`` tensor for parameters with the given
+    element counts (1 = shared, C = per channel)."""
+    rows, T = _rows_T(x)
+    rpb, blk = 1, 1
+    if x.dim() >= 3:
+        rpb = int(np.prod(x.shape[1:-1]))
+        blk = int(np.prod(x.shape[2:-1])) if x.dim() > 3 else 1
+    nmax = max(counts) if counts else 1
+    if nmax > 1:
+        if x.dim() < 3 or x.shape[1] != nmax:
+            raise ValueError(
+                f'per-channel parameter of {nmax} elements does not match input shape {tuple(x.shape)}'
+            )
+    return N.Geom(rows, T, rpb, blk)
+
+
+def _c(t):
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _param(p, like):
+    """Flatten a decay-like parameter to contiguous fp32 on the input's device."""
+    p = p.detach().to(device=like.device, dtype=torch.float32).reshape(-1)
+    return _c(p)
+
+
+def row_state(state, x):
+    """Broadcast a state to one value per row (``state * ones(x.shape[:-1])``)."""
+    lead = x.shape[:-1]
+    s = state.detach().to(device=x.device, dtype=torch.float32)
+    if s.numel() == 1:
+        return s.reshape(1).expand(int(np.prod(lead)) if len(lead) else 1).contiguous()
+    if tuple(s.shape) != tuple(lead):
+        s = s.expand(lead)
+    return _c(s).reshape(-1)
+
+
+def is_pow2(v):
+    v = int(v)
+    return v > 0 and (v & (v - 1)) == 0
+
+
+def f32(v):
+    return float(np.float32(v))
+
+
+# --------------------------------------------------------------------------
+# leaky integrator
+# --------------------------------------------------------------------------
+def li_fwd(x, decay, state, w_scale, threshold=None, want_final=False):
+    N.require_cuda(x)
+    x = _c(x)
+    decay = _param(decay, x)
+    st = row_state(state, x)
+    y = torch.empty_like(x)
+    fin = torch.empty(x.shape[:-1], device=x.device, dtype=torch.float32) if want_final else None
+    thr = -1.0 if threshold is None else float(threshold)
+    thr_scaled = thr * w_scale  # Python double, then fp32 at the boundary
+    g = geom(x, decay.numel())
+    N.call('sb_li_fwd', x, N.ptr(x), N.ptr(decay), decay.numel(), N.ptr(st), N.ptr(y), N.ptr(fin), g,
+           f32(thr_scaled) if thr_scaled > 0 else -1.0, int(w_scale), N.stream_of(x))
+    return (y, fin) if want_final else y
+
+
+def li_bwd(grad_y, y, decay, need_decay_grad):
+    N.require_cuda(grad_y)
+    grad_y = _c(grad_y)
+    dec = _param(decay, grad_y)
+    grad_x = torch.empty_like(grad_y)
+    g = geom(grad_y, dec.numel())
+    if need_decay_grad:
+        y = _c(y)
+        gd = torch.empty(dec.numel(), device=grad_y.device, dtype=torch.float32)
+        scr = N.scratch(g.rows, dec.numel(), grad_y.device)
+        N.call('sb_li_bwd', grad_y, N.ptr(grad_y), N.ptr(y), N.ptr(dec), dec.numel(), N.ptr(grad_x), N.ptr(gd),
+               N.ptr(scr), g, N.stream_of(grad_y))
+        return grad_x, gd.reshape(decay.shape)
+    N.call('sb_li_bwd', grad_y, N.ptr(grad_y), None, N.ptr(dec), dec.numel(), N.ptr(grad_x), None, None, g,
+           N.stream_of(grad_y))
+    return grad_x, None
+
+
+# --------------------------------------------------------------------------
+# adaptive threshold / phase threshold
+# --------------------------------------------------------------------------
+def ath_fwd(x, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale):
+    N.require_cuda(x)
+    x = _c(x)
+    rd, td = _param(ref_decay, x), _param(th_decay, x)
+    rs, ts = row_state(ref_state, x), row_state(th_state, x)
+    th = torch.empty_like(x)
+    ref = torch.empty_like(x)
+    g = geom(x, rd.numel(), td.numel())
+    N.call('sb_ath_fwd', x, N.ptr(x), N.ptr(rs), N.ptr(rd), rd.numel(), N.ptr(ts), N.ptr(td), td.numel(),
+           N.ptr(th), N.ptr(ref), g, int(th_scale * w_scale), int(th0 * w_scale), int(w_scale), N.stream_of(x))
+    return th, ref
+
+
+def apth_fwd(re, im, im_state, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale):
+    N.require_cuda(re, im)
+    re, im = _c(re), _c(im)
+    rd, td = _param(ref_decay, re), _param(th_decay, re)
+    ims, rs, ts = row_state(im_state, re), row_state(ref_state, re), row_state(th_state, re)
+    th = torch.empty_like(re)
+    ref = torch.empty_like(re)
+    g = geom(re, rd.numel(), td.numel())
+    N.call('sb_apth_fwd', re, N.ptr(re), N.ptr(im), N.ptr(ims), N.ptr(rs), N.ptr(rd), rd.numel(), N.ptr(ts),
+           N.ptr(td), td.numel(), N.ptr(th), N.ptr(ref), g, int(th_scale * w_scale), int(th0 * w_scale),
+           int(w_scale), N.stream_of(re))
+    return th, ref
+
+
+# --------------------------------------------------------------------------
+# resonator / adaptive resonator
+# --------------------------------------------------------------------------
+def res_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, w_scale, threshold=None):
+    N.require_cuda(re_in, im_in)
+    re_in, im_in = _c(re_in), _c(im_in)
+    sd, cd = _param(sin_decay, re_in), _param(cos_decay, re_in)
+    if sd.numel() != cd.numel():
+        raise ValueError('sin_decay and cos_decay must have the same number of elements')
+    rs, ims = row_state(re_state, re_in), row_state(im_state, im_in)
+    re = torch.empty_like(re_in)
+    im = torch.empty_like(im_in)
+    thr = -1.0 if threshold is None else float(threshold)
+    thr_scaled = thr * w_scale
+    reset = thr_scaled >= 0
+    im_reset = int(np.float32(thr_scaled - 1)) if reset else 0
+    g = geom(re_in, sd.numel())
+    N.call('sb_res_fwd', re_in, N.ptr(re_in), N.ptr(im_in), N.ptr(sd), N.ptr(cd), sd.numel(), N.ptr(rs),
+           N.ptr(ims), N.ptr(re), N.ptr(im), g, int(reset), f32(thr_scaled), im_reset, int(w_scale),
+           N.stream_of(re_in))
+    return re, im
+
+
+def res_bwd(grad_re, grad_im, re, im, sin_decay, cos_decay, need_param_grad):
+    N.require_cuda(grad_re, grad_im)
+    grad_re, grad_im = _c(grad_re), _c(grad_im)
+    sd, cd = _param(sin_decay, grad_re), _param(cos_decay, grad_re)
+    gre = torch.empty_like(grad_re)
+    gim = torch.empty_like(grad_im)
+    g = geom(grad_re, sd.numel())
+    if need_param_grad:
+        re, im = _c(re), _c(im)
+        gs = torch.empty(sd.numel(), device=grad_re.device, dtype=torch.float32)
+        gc = torch.empty_like(gs)
+        s1 = N.scratch(g.rows, sd.numel(), grad_re.device)
+        s2 = N.scratch(g.rows, sd.numel(), grad_re.device)
+        N.call('sb_res_bwd', grad_re, N.ptr(grad_re), N.ptr(grad_im), N.ptr(re), N.ptr(im), N.ptr(sd), N.ptr(cd),
+               sd.numel(), N.ptr(gre), N.ptr(gim), N.ptr(gs), N.ptr(gc), N.ptr(s1), N.ptr(s2), g,
+               N.stream_of(grad_re))
+        return gre, gim, gs.reshape(sin_decay.shape), gc.reshape(cos_decay.shape)
+    N.call('sb_res_bwd', grad_re, N.ptr(grad_re), N.ptr(grad_im), None, None, N.ptr(sd), N.ptr(cd), sd.numel(),
+           N.ptr(gre), N.ptr(gim), None, None, None, None, g, N.stream_of(grad_re))
+    return gre, gim, None, None
+
+
+def adres_fwd(re_in, im_in, sin_decay, cos_decay, ref_decay, th_decay, re_state, im_state, ref_state, th_state,
+              th_scale, th0, w_scale):
+    N.require_cuda(re_in, im_in)
+    re_in, im_in = _c(re_in), _c(im_in)
+    sd, cd = _param(sin_decay, re_in), _param(cos_decay, re_in)
+    rd, td = _param(ref_decay, re_in), _param(th_decay, re_in)
+    rs, ims = row_state(re_state, re_in), row_state(im_state, re_in)
+    refs, ths = row_state(ref_state, re_in), row_state(th_state, re_in)
+    outs = [torch.empty_like(re_in) for _ in range(4)]
+    g = geom(re_in, sd.numel(), rd.numel(), td.numel())
+    N.call('sb_adres_fwd', re_in, N.ptr(re_in), N.ptr(im_in), N.ptr(sd), N.ptr(cd), sd.numel(), N.ptr(rd),
+           rd.numel(), N.ptr(td), td.numel(), N.ptr(rs), N.ptr(ims), N.ptr(refs), N.ptr(ths), N.ptr(outs[0]),
+           N.ptr(outs[1]), N.ptr(outs[2]), N.ptr(outs[3]), g, int(th_scale * w_scale), int(th0 * w_scale),
+           int(w_scale), N.stream_of(re_in))
+    return tuple(outs)
+
+
+# --------------------------------------------------------------------------
+# spike functions
+# --------------------------------------------------------------------------
+def _thr_args(threshold, like):
+    """(tensor pointer or None, scalar) for a float-or-tensor threshold."""
+    if torch.is_tensor(threshold) and threshold.numel() > 1:
+        t = threshold.detach().to(device=like.device, dtype=torch.float32)
+        if t.shape != like.shape:
+            t = t.expand(like.shape)
+        return _c(t), 0.0
+    if torch.is_tensor(threshold):
+        return None, f32(threshold.item())
+    return None, f32(threshold)
+
+
+def spike_fwd(v, threshold, graded, scale):
+    N.require_cuda(v)
+    v = _c(v)
+    tt, ts = _thr_args(threshold, v)
+    out = torch.empty_like(v)
+    N.call('sb_spike_fwd', v, N.ptr(v), N.ptr(tt), ts, N.ptr(out), v.numel(), int(bool(graded)), float(scale),
+           N.stream_of(v))
+    return out
+
+
+def spike_bwd(v, threshold, grad_spike, tau_rho, scale_rho, graded):
+    N.require_cuda(v, grad_spike)
+    v, grad_spike = _c(v), _c(grad_spike)
+    tt, ts = _thr_args(threshold, v)
+    out = torch.empty_like(v)
+    N.call('sb_spike_bwd', v, N.ptr(v), N.ptr(tt), ts, N.ptr(grad_spike), N.ptr(out), v.numel(), f32(tau_rho),
+           f32(scale_rho), int(bool(graded)), N.stream_of(v))
+    return out
+
+
+def cspike_fwd(re, im, threshold, imag_last, graded, scale):
+    N.require_cuda(re, im)
+    re, im = _c(re), _c(im)
+    tt, ts = _thr_args(threshold, re)
+    if not torch.is_tensor(imag_last):
+        imag_last = torch.tensor(float(imag_last))
+    last = row_state(imag_last, im)
+    rows, T = _rows_T(re)
+    out = torch.empty_like(re)
+    N.call('sb_cspike_fwd', re, N.ptr(re), N.ptr(im), N.ptr(tt), ts, N.ptr(last), N.ptr(out), rows, T,
+           int(bool(graded)), float(scale), N.stream_of(re))
+    return out
+
+
+def cspike_bwd(re, im, threshold, grad_spike, tau_rho, scale_rho, graded):
+    N.require_cuda(re, im, grad_spike)
+    re, im, grad_spike = _c(re), _c(im), _c(grad_spike)
+    tt, ts = _thr_args(threshold, re)
+    gre = torch.empty_like(re)
+    gim = torch.empty_like(re)
+    N.call('sb_cspike_bwd', re, N.ptr(re), N.ptr(im), N.ptr(tt), ts, N.ptr(grad_spike), N.ptr(gre), N.ptr(gim),
+           re.numel(), f32(tau_rho), f32(scale_rho), int(bool(graded)), N.stream_of(re))
+    return gre, gim
+
+
+# --------------------------------------------------------------------------
+# shift / temporal filter
+# --------------------------------------------------------------------------
+def _lut_args(shift_val, x, sampling_time):
+    """(lut tensor or None, n_lut, scalar shift, shift sampling time)."""
+    if torch.is_tensor(shift_val) and shift_val.numel() > 1:
+        n_spatial = int(np.prod(x.shape[1:-1]))
+        if n_spatial != shift_val.numel():
+            raise Exception(
+                f'Expected spatial dimension of input and shift_val to be same. '
+                f'Found input.shape={tuple(x.shape)}, shift_val.shape={tuple(shift_val.shape)}.'
+            )
+        lut = _c(shift_val.detach().to(device=x.device, dtype=torch.float32).reshape(-1))
+        return lut, lut.numel(), 0.0, float(sampling_time)
+    if torch.is_tensor(shift_val):
+        shift_val = shift_val.item()
+    # scalar path: int(shift / sampling_time) in Python arithmetic (shift.py:55-56)
+    return None, 0, float(int(shift_val / sampling_time)), 1.0
+
+
+def shift(x, shift_val, sampling_time=1):
+    N.require_cuda(x)
+    if x.dim() <= 1:
+        raise AssertionError(f'Expected input to have at least two dimension. Found input.shape={tuple(x.shape)}.')
+    x = _c(x)
+    lut, n_lut, sv, ts = _lut_args(shift_val, x, sampling_time)
+    rows, T = _rows_T(x)
+    out = torch.empty_like(x)
+    N.call('sb_shift', x, N.ptr(x), N.ptr(lut), n_lut, sv, ts, N.ptr(out), rows, T, N.stream_of(x))
+    return out
+
+
+def fir(x, filt, sampling_time, corr):
+    N.require_cuda(x)
+    x = _c(x)
+    f = _c(filt.detach().to(device=x.device, dtype=torch.float32).reshape(-1))
+    rows, T = _rows_T(x)
+    out = torch.empty_like(x)
+    N.call('sb_fir_corr' if corr else 'sb_fir_conv', x, N.ptr(x), N.ptr(f), f.numel(), float(sampling_time),
+           N.ptr(out), rows, T, N.stream_of(x))
+    return out
+
+
+def shift_fir(x, shift_val, shift_ts, filt, sampling_time, backward):
+    N.require_cuda(x)
+    x = _c(x)
+    f = _c(filt.detach().to(device=x.device, dtype=torch.float32).reshape(-1))
+    lut, n_lut, sv, ts = _lut_args(shift_val, x, shift_ts)
+    rows, T = _rows_T(x)
+    out = torch.empty_like(x)
+    N.call('sb_shift_fir_bwd' if backward else 'sb_shift_fir_fwd', x, N.ptr(x), N.ptr(lut), n_lut, sv, ts,
+           N.ptr(f), f.numel(), float(sampling_time), N.ptr(out), rows, T, N.stream_of(x))
+    return out
+
+
+# --------------------------------------------------------------------------
+# fused neurons
+# --------------------------------------------------------------------------
+def _vec(shape_like):
+    return torch.empty(shape_like.shape[:-1], device=shape_like.device, dtype=torch.float32)
+
+
+def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current, want_spike, graded=False,
+             spike_scale=1.0):
+    """Returns dict with current/voltage/spike series and final_c/final_v/final_s."""
+    N.require_cuda(x)
+    x = _c(x)
+    cd, vd = _param(cdecay, x), _param(vdecay, x)
+    cs, vs = row_state(cstate, x), row_state(vstate, x)
+    cur = torch.empty_like(x) if want_current else None
+    vol = torch.empty_like(x)
+    spk = torch.empty_like(x) if want_spike else None
+    fc, fv = _vec(x), _vec(x)
+    fs = _vec(x) if want_spike else None
+    g = geom(x, cd.numel(), vd.numel())
+    N.call('sb_cuba_fwd', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(cs), N.ptr(vs),
+           N.ptr(cur), N.ptr(vol), N.ptr(spk), N.ptr(fc), N.ptr(fv), N.ptr(fs), g, float(threshold), int(w_scale),
+           int(bool(graded)), float(spike_scale), N.stream_of(x))
+    return dict(current=cur, voltage=vol, spike=spk, final_c=fc, final_v=fv, final_s=fs)
+
+
+def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_decay_grad):
+    N.require_cuda(grad_spike, voltage)
+    grad_spike, voltage = _c(grad_spike), _c(voltage)
+    cd, vd = _param(cdecay, voltage), _param(vdecay, voltage)
+    tt, ts = _thr_args(threshold, voltage)
+    gx = torch.empty_like(voltage)
+    g = geom(voltage, cd.numel(), vd.numel())
+    gcd = gvd = sc = sv = None
+    if need_decay_grad:
+        current = _c(current)
+        gcd = torch.empty(cd.numel(), device=voltage.device, dtype=torch.float32)
+        gvd = torch.empty(vd.numel(), device=voltage.device, dtype=torch.float32)
+        sc = N.scratch(g.rows, cd.numel(), voltage.device)
+        sv = N.scratch(g.rows, vd.numel(), voltage.device)
+    N.call('sb_cuba_bwd', voltage, N.ptr(grad_spike), N.ptr(voltage), N.ptr(tt), ts,
+           N.ptr(current) if need_decay_grad else None, N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(gx),
+           N.ptr(gcd), N.ptr(gvd), N.ptr(sc), N.ptr(sv), g, f32(tau_rho), f32(scale_rho), int(bool(graded)),
+           N.stream_of(voltage))
+    if need_decay_grad:
+        return gx, gcd.reshape(cdecay.shape), gvd.reshape(vdecay.shape)
+    return gx, None, None
+
+
+def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0, w_scale,
+             dynamics_mode, graded=False, spike_scale=1.0):
+    N.require_cuda(x)
+    x = _c(x)
+    cd, vd = _param(cdecay, x), _param(vdecay, x)
+    rd, td = _param(ref_decay, x), _param(th_decay, x)
+    cs, vs = row_state(cstate, x), row_state(vstate, x)
+    rs, ts = row_state(ref_state, x), row_state(th_state, x)
+    outs = [torch.empty_like(x) for _ in range(4 if dynamics_mode else 3)]
+    fin = [_vec(x) for _ in range(5)]
+    g = geom(x, cd.numel(), vd.numel(), rd.numel(), td.numel())
+    N.call('sb_alif_fwd', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(rd), rd.numel(),
+           N.ptr(td), td.numel(), N.ptr(cs), N.ptr(vs), N.ptr(rs), N.ptr(ts),
+           N.ptr(outs[0]), N.ptr(outs[1]), N.ptr(outs[2]), N.ptr(outs[3]) if dynamics_mode else None,
+           N.ptr(fin[0]), N.ptr(fin[1]), N.ptr(fin[2]), N.ptr(fin[3]), None if dynamics_mode else N.ptr(fin[4]),
+           g, int(th_step * w_scale), int(th0 * w_scale), int(w_scale), int(bool(dynamics_mode)),
+           int(bool(graded)), float(spike_scale), N.stream_of(x))
+    return outs, dict(final_c=fin[0], final_v=fin[1], final_th=fin[2], final_ref=fin[3], final_s=fin[4])
+
+
+def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_scale, graded=False,
+           spike_scale=1.0, adaptive=None, dynamics_mode=False):
+    """``adaptive`` = None for RF, else dict(ref_decay, th_decay, ref_state, th_state, th_step, th0)."""
+    N.require_cuda(re_in, im_in)
+    re_in, im_in = _c(re_in), _c(im_in)
+    sd, cd = _param(sin_decay, re_in), _param(cos_decay, re_in)
+    rs, ims = row_state(re_state, re_in), row_state(im_state, re_in)
+    adapt = adaptive is not None
+    if adapt:
+        rd, td = _param(adaptive['ref_decay'], re_in), _param(adaptive['th_decay'], re_in)
+        refs, ths = row_state(adaptive['ref_state'], re_in), row_state(adaptive['th_state'], re_in)
+        th_step, th0 = int(adaptive['th_step'] * w_scale), int(adaptive['th0'] * w_scale)
+        counts = (sd.numel(), rd.numel(), td.numel())
+    else:
+        rd = td = refs = ths = None
+        th_step = th0 = 0
+        counts = (sd.numel(),)
+    nout = 4 if adapt else 3
+    outs = [torch.empty_like(re_in) for _ in range(nout)]
+    fin = [_vec(re_in) for _ in range(5)]
+    g = geom(re_in, *counts)
+    N.call('sb_rf_fwd', re_in, N.ptr(re_in), N.ptr(im_in), N.ptr(sd), N.ptr(cd), sd.numel(),
+           N.ptr(rd), rd.numel() if adapt else 1, N.ptr(td), td.numel() if adapt else 1,
+           N.ptr(rs), N.ptr(ims), N.ptr(refs), N.ptr(ths),
+           N.ptr(outs[0]), N.ptr(outs[1]), N.ptr(outs[2]), N.ptr(outs[3]) if adapt else None,
+           N.ptr(fin[0]), N.ptr(fin[1]), N.ptr(fin[2]) if adapt else None, N.ptr(fin[3]) if adapt else None,
+           None if dynamics_mode else N.ptr(fin[4]), g, f32(threshold), th_step, th0, int(w_scale), int(adapt),
+           int(bool(dynamics_mode)), int(bool(graded)), float(spike_scale), N.stream_of(re_in))
+    return outs, dict(final_re=fin[0], final_im=fin[1], final_th=fin[2], final_ref=fin[3], final_s=fin[4])
+
+
+def rf_bwd(grad_spike, re, im, threshold, sin_decay, cos_decay, tau_rho, scale_rho, graded, need_param_grad):
+    N.require_cuda(grad_spike, re, im)
+    grad_spike, re, im = _c(grad_spike), _c(re), _c(im)
+    sd, cd = _param(sin_decay, re), _param(cos_decay, re)
+    tt, ts = _thr_args(threshold, re)
+    gre = torch.empty_like(re)
+    gim = torch.empty_like(re)
+    g = geom(re, sd.numel())
+    gs = gc = s1 = s2 = None
+    if need_param_grad:
+        gs = torch.empty(sd.numel(), device=re.device, dtype=torch.float32)
+        gc = torch.empty_like(gs)
+        s1 = N.scratch(g.rows, sd.numel(), re.device)
+        s2 = N.scratch(g.rows, sd.numel(), re.device)
+    N.call('sb_rf_bwd', re, N.ptr(grad_spike), N.ptr(re), N.ptr(im), N.ptr(tt), ts, N.ptr(sd), N.ptr(cd),
+           sd.numel(), N.ptr(gre), N.ptr(gim), N.ptr(gs), N.ptr(gc), N.ptr(s1), N.ptr(s2), g, f32(tau_rho),
+           f32(scale_rho), int(bool(graded)), N.stream_of(re))
+    if need_param_grad:
+        return gre, gim, gs.reshape(sin_decay.shape), gc.reshape(cos_decay.shape)
+    return gre, gim, None, None

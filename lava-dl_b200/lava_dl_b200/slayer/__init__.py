@@ -1,0 +1,5 @@
+"""Drop-in mirror of the hot-path part of ``lava.lib.dl.slayer``."""
+
+from . import jitconfig, utils, axon, spike, neuron  # noqa: F401
+
+__all__ = ['jitconfig', 'utils', 'axon', 'spike', 'neuron']

@@ -1,0 +1,5 @@
+"""Neuron models on the hot path (mirror of ``lava.lib.dl.slayer.neuron``)."""
+
+from . import dynamics, base, cuba, alif, rf, adrf  # noqa: F401
+
+__all__ = ['dynamics', 'base', 'cuba', 'alif', 'rf', 'adrf']

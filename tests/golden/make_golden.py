@@ -1,0 +1,352 @@
+"""Generates the golden vectors under tests/golden/ by running lava-dl itself.
+
+Run where the reference checkout is available (it is NOT needed to run the
+tests, only to regenerate the fixtures):
+
+    python tests/golden/make_golden.py /path/to/lava-dl
+
+The reference's CPU code path (the Python loops in
+src/lava/lib/dl/slayer/neuron/dynamics/*.py, spike/*.py, utils/time/shift.py,
+utils/filter/conv.py and the neuron classes) is imported unmodified;
+matplotlib and h5py, which the package imports at top level but the hot path
+never touches, are stubbed.  Every case stores its inputs, parameters and the
+reference's outputs in one .npz; tests replay the inputs through the oracle
+(CPU) and through the CUDA kernels (GPU).
+"""
+
+import os
+import sys
+import types
+
+import numpy as np
+
+
+def import_reference(root):
+    class _Stub(types.ModuleType):
+        def __getattr__(self, k):
+            if k.startswith('__'):
+                raise AttributeError(k)
+            return type(k, (), {})
+
+    for m in ['matplotlib', 'matplotlib.pyplot', 'matplotlib.animation', 'h5py']:
+        sys.modules[m] = _Stub(m)
+    sys.path.insert(0, os.path.join(root, 'src'))
+    import lava.lib.dl.slayer as slayer
+    return slayer
+
+
+def main():
+    root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    out_dir = os.path.dirname(os.path.abspath(__file__))
+    slayer = import_reference(root)
+    import torch
+    from lava.lib.dl.slayer.neuron.dynamics import (leaky_integrator, adaptive_threshold, resonator,
+                                                    adaptive_phase_th, adaptive_resonator)
+    from lava.lib.dl.slayer.spike import Spike
+    from lava.lib.dl.slayer.spike import complex as cspike
+    from lava.lib.dl.slayer.utils.time import shift
+    from lava.lib.dl.slayer.utils.filter import conv, corr
+    from lava.lib.dl.slayer.axon import delay as axon_delay
+
+    torch.set_num_threads(4)
+    gen = torch.Generator().manual_seed(20240607)
+
+    def randn(*shape, mean=0.0, std=1.0):
+        return mean + std * torch.randn(*shape, generator=gen)
+
+    def rand(*shape):
+        return torch.rand(*shape, generator=gen)
+
+    def npy(t):
+        return t.detach().cpu().numpy().copy()
+
+    cases = {}
+
+    def save(name, **arrays):
+        cases[name] = {k: (npy(v) if torch.is_tensor(v) else np.asarray(v)) for k, v in arrays.items()}
+
+    W = 4096
+    B, C, T = 3, 5, 77  # T deliberately not a multiple of 4 or 32
+    B2, C2, H2, T2 = 2, 3, 4, 64  # NCHWT-like (rank 4), T multiple of 32
+
+    # ------------------------------------------------------------------
+    # leaky integrator
+    # ------------------------------------------------------------------
+    for tag, shape, dec, thr in [
+        ('shared_nothr', (B, C, T), torch.tensor([410.0]), None),
+        ('shared_thr', (B, C, T), torch.tensor([123.0]), 1.25 + 0.01 / 4096),
+        ('chan_thr', (B, C, T), torch.tensor([100., 500., 1024., 3000., 4096.]), 0.5),
+        ('chan_nothr_T64', (B2, C2, T2), torch.tensor([0., 204.8, 2047.5]), None),
+        ('rank2', (7, 40), torch.tensor([300.0]), 1.0),
+    ]:
+        x = randn(*shape, mean=0.3)
+        state = (randn(*shape[:-1]) * 0.5 * W).round() / W
+        dec = dec.clone().requires_grad_(True)
+        xin = x.clone().requires_grad_(True)
+        y = leaky_integrator.dynamics(xin, dec, state, W, threshold=thr)
+        go = randn(*shape)
+        y.backward(go)
+        save(f'li_{tag}', x=x, decay=dec, state=state, threshold=np.float64(-1 if thr is None else thr),
+             w_scale=W, y=y, grad_out=go, grad_in=xin.grad, grad_decay=dec.grad)
+    # scalar (1-element) state and non power-of-two scale
+    x = randn(B, C, T, mean=0.2)
+    y = leaky_integrator.dynamics(x, torch.tensor([700.0]), torch.tensor([0.37]), 1000, threshold=0.8)
+    save('li_w1000', x=x, decay=np.array([700.0], np.float32), state=np.array([0.37], np.float32),
+         threshold=np.float64(0.8), w_scale=1000, y=y)
+
+    # ------------------------------------------------------------------
+    # adaptive threshold / adaptive phase threshold
+    # ------------------------------------------------------------------
+    for tag, shape, rd, td in [
+        ('shared', (B, C, T), torch.tensor([410.0]), torch.tensor([205.0])),
+        ('chan', (B, C, T), torch.tensor([100., 300., 500., 700., 900.]),
+         torch.tensor([50., 150., 250., 350., 450.])),
+    ]:
+        x = randn(*shape, mean=0.5, std=1.5)
+        ref_state = (rand(*shape[:-1]) * W).round() / W - 0.25
+        th_state = 1.0 + (rand(*shape[:-1]) * W).round() / W - 0.5
+        th, ref = adaptive_threshold.dynamics(x, ref_state, rd, th_state, td, 0.5, 1.0, W)
+        save(f'ath_{tag}', x=x, ref_state=ref_state, ref_decay=rd, th_state=th_state, th_decay=td,
+             th_scale=0.5, th0=1.0, w_scale=W, threshold=th, refractory=ref)
+
+        re = randn(*shape, std=1.5)
+        im = randn(*shape, std=1.5)
+        im_state = randn(*shape[:-1])
+        th, ref = adaptive_phase_th.dynamics(re, im, im_state, ref_state, rd, th_state, td, 0.25, 0.5, W)
+        save(f'apth_{tag}', re=re, im=im, im_state=im_state, ref_state=ref_state, ref_decay=rd,
+             th_state=th_state, th_decay=td, th_scale=0.25, th0=0.5, w_scale=W, threshold=th, refractory=ref)
+
+    # ------------------------------------------------------------------
+    # resonator / adaptive resonator
+    # ------------------------------------------------------------------
+    def sincos(periods, decay=0.1):
+        p = torch.as_tensor(periods, dtype=torch.float32)
+        return (4096 * torch.sin(2 * np.pi / p) * (1 - decay)).round(), \
+               (4096 * torch.cos(2 * np.pi / p) * (1 - decay)).round()
+
+    for tag, shape, periods, thr in [
+        ('shared', (B, C, T), [10.0], None),
+        ('chan', (B, C, T), [4.0, 8.0, 16.0, 25.0, 40.0], None),
+        ('shared_reset', (B, C, T), [12.0], 0.75),
+        ('chan_T64', (B2, C2, T2), [5.0, 9.0, 33.0], None),
+        ('neg_cos', (B, C, T), [3.0], None),  # period < 4 -> negative cos_decay
+    ]:
+        sd, cd = sincos(periods)
+        sd = sd.clone().requires_grad_(True)
+        cd = cd.clone().requires_grad_(True)
+        re_in = randn(*shape, std=0.5).requires_grad_(True)
+        im_in = randn(*shape, std=0.5).requires_grad_(True)
+        re_state = (randn(*shape[:-1]) * 0.3 * W).round() / W
+        im_state = (randn(*shape[:-1]) * 0.3 * W).round() / W
+        re, im = resonator.dynamics(re_in, im_in, sd, cd, re_state, im_state, W, threshold=thr)
+        g_re, g_im = randn(*shape), randn(*shape)
+        (re * g_re + im * g_im).sum().backward()
+        save(f'res_{tag}', re_in=re_in, im_in=im_in, sin_decay=sd, cos_decay=cd, re_state=re_state,
+             im_state=im_state, threshold=np.float64(-1 if thr is None else thr), w_scale=W, re=re, im=im,
+             grad_re=g_re, grad_im=g_im, grad_re_in=re_in.grad, grad_im_in=im_in.grad, grad_sin=sd.grad,
+             grad_cos=cd.grad)
+
+    for tag, shape, periods, rd, td in [
+        ('shared', (B, C, T), [10.0], torch.tensor([410.0]), torch.tensor([205.0])),
+        ('chan', (B, C, T), [4.0, 8.0, 16.0, 25.0, 40.0], torch.tensor([100., 300., 500., 700., 900.]),
+         torch.tensor([50., 150., 250., 350., 450.])),
+    ]:
+        sd, cd = sincos(periods)
+        sd = sd.clone().requires_grad_(True)
+        cd = cd.clone().requires_grad_(True)
+        re_in = randn(*shape, std=0.5).requires_grad_(True)
+        im_in = randn(*shape, std=0.5).requires_grad_(True)
+        re_state = (randn(*shape[:-1]) * 0.3 * W).round() / W
+        im_state = (randn(*shape[:-1]) * 0.3 * W).round() / W
+        ref_state = (rand(*shape[:-1]) * W).round() / W - 0.25
+        th_state = 0.5 + (rand(*shape[:-1]) * W).round() / W * 0.5
+        re, im, th, ref = adaptive_resonator.dynamics(
+            re_in, im_in, sd, cd, rd, td, re_state, im_state, ref_state, th_state, 0.25, 0.5, W)
+        g_re, g_im = randn(*shape), randn(*shape)
+        (re * g_re + im * g_im).sum().backward()
+        save(f'adres_{tag}', re_in=re_in, im_in=im_in, sin_decay=sd, cos_decay=cd, ref_decay=rd, th_decay=td,
+             re_state=re_state, im_state=im_state, ref_state=ref_state, th_state=th_state, th_scale=0.25,
+             th0=0.5, w_scale=W, re=re, im=im, threshold=th, refractory=ref, grad_re=g_re, grad_im=g_im,
+             grad_re_in=re_in.grad, grad_im_in=im_in.grad, grad_sin=sd.grad, grad_cos=cd.grad)
+
+    # ------------------------------------------------------------------
+    # spike functions
+    # ------------------------------------------------------------------
+    for tag, graded, tensor_thr in [('bin_scalar', False, False), ('bin_tensor', False, True),
+                                    ('graded_scalar', True, False), ('graded_tensor', True, True)]:
+        v = (randn(B, C, T, mean=0.8, std=1.0) * W).round() / W
+        v.requires_grad_(True)
+        thr = (1.0 + 0.3 * rand(B, C, T)) if tensor_thr else (1.25 + 0.01 / 4096)
+        s = Spike.apply(v, thr, 1.25 * 100, 0.1, graded, torch.zeros(B, C), 1)
+        gs = randn(B, C, T)
+        s.backward(gs)
+        save(f'spike_{tag}', v=v, threshold=thr if tensor_thr else np.float64(thr), tau_rho=1.25 * 100,
+             scale_rho=0.1, graded=graded, spike=s, grad_spike=gs, grad_v=v.grad)
+
+        re = (randn(B, C, T, std=1.0) * W).round() / W
+        im = (randn(B, C, T, std=1.0) * W).round() / W
+        re.requires_grad_(True)
+        im.requires_grad_(True)
+        cthr = (0.3 + 0.3 * rand(B, C, T)) if tensor_thr else 0.5
+        last = randn(B, C)
+        s = cspike.Spike.apply(re, im, cthr, 0.5 * 0.5, 10.0, graded, last, 1)
+        gs = randn(B, C, T)
+        s.backward(gs)
+        save(f'cspike_{tag}', re=re, im=im, threshold=cthr if tensor_thr else np.float64(cthr), tau_rho=0.25,
+             scale_rho=10.0, graded=graded, imag_last=last, spike=s, grad_spike=gs, grad_re=re.grad,
+             grad_im=im.grad)
+
+    # ------------------------------------------------------------------
+    # shift / filter
+    # ------------------------------------------------------------------
+    x = rand(B, C, T)
+    for tag, sv in [('p10', 10), ('m7', -7), ('zero', 0), ('big', 200)]:
+        save(f'shift_{tag}', x=x, shift=np.float64(sv), sampling_time=1.0, out=shift(x, sv))
+    lut = torch.tensor([0., 3., -5., 62.4, 76.0])
+    save('shift_lut', x=x, shift=lut, sampling_time=1.0, out=shift(x, lut))
+    x4 = rand(B2, C2, H2, T2)
+    lut4 = torch.randint(-8, 40, (C2, H2), generator=gen).float()
+    save('shift_lut_rank4', x=x4, shift=lut4, sampling_time=1.0, out=shift(x4, lut4))
+    save('shift_scalar_ts2', x=x, shift=np.float64(9), sampling_time=2.0, out=shift(x, 9, 2.0))
+
+    for tag, K, ts in [('k50', 50, 1.0), ('k64_ts2', 64, 2.0), ('k1', 1, 1.0), ('k100', 100, 1.0)]:
+        x = rand(B, C, T).requires_grad_(True)
+        f = torch.exp(-torch.arange(K).float() / 8) / 8 * (1 + 0.1 * randn(K))
+        y = conv(x, f, ts)
+        g = randn(B, C, T)
+        y.backward(g)
+        z = corr(x.detach(), f, ts)
+        save(f'fir_{tag}', x=x, filter=f, sampling_time=ts, conv=y, corr=z, grad_out=g, grad_conv=x.grad)
+
+    # delay (shift with autograd) followed by filter: the config-3 chain
+    x = (rand(B, C, T) < 0.2).float().requires_grad_(True)
+    d = torch.tensor([0., 1., 5., 30., 62.])
+    f = torch.exp(-torch.arange(64).float() / 8) / 8
+    y = conv(axon_delay(x, d), f)
+    g = randn(B, C, T)
+    y.backward(g)
+    save('delay_fir_chain', x=x, delay=d, filter=f, out=y, grad_out=g, grad_x=x.grad)
+
+    # ------------------------------------------------------------------
+    # neuron classes: forward, backward, persistent-state split
+    # ------------------------------------------------------------------
+    def run_neuron(make, inputs, param_names, set_params=None, split=None):
+        """Forward+backward of spike.sum()-like loss; optional two-chunk run with persistent state."""
+        res = {}
+        n = make()
+        ins = [i.clone().requires_grad_(True) for i in inputs]
+        arg = ins[0] if len(ins) == 1 else tuple(ins)
+        if set_params is not None:
+            with torch.no_grad():
+                n(arg)  # binds the shape and samples per-channel parameters
+                for k, v in set_params.items():
+                    getattr(n, k).data = v.clone()
+            n2 = n
+            for name, buf in n2.named_buffers():
+                if name.endswith('_state'):
+                    buf.zero_()
+                    if name == 'threshold_state':
+                        buf.add_(n2.threshold)
+        spike = n(arg)
+        g = randn(*spike.shape)
+        (spike * g).sum().backward()
+        res['spike'] = spike
+        res['grad_spike'] = g
+        for i, t in enumerate(ins):
+            res[f'grad_in{i}'] = t.grad
+        for k in param_names:
+            p = getattr(n, k)
+            res[f'param_{k}'] = p.data
+            if p.grad is not None:
+                res[f'grad_{k}'] = p.grad
+        with torch.no_grad():
+            m = make()
+            if set_params is not None:
+                m(arg)
+                for k, v in set_params.items():
+                    getattr(m, k).data = v.clone()
+                for name, buf in m.named_buffers():
+                    if name.endswith('_state'):
+                        buf.zero_()
+                        if name == 'threshold_state':
+                            buf.add_(m.threshold)
+            dyn = m.dynamics(arg)
+            for i, t in enumerate(dyn):
+                res[f'dyn{i}'] = t
+        if split is not None:
+            with torch.no_grad():
+                p = make()
+                p.persistent_state = True
+                if set_params is not None:
+                    p(arg)
+                    for k, v in set_params.items():
+                        getattr(p, k).data = v.clone()
+                    for name, buf in p.named_buffers():
+                        if name.endswith('_state'):
+                            buf.zero_()
+                            if name == 'threshold_state':
+                                buf.add_(p.threshold)
+                a = [i[..., :split] for i in inputs]
+                b = [i[..., split:] for i in inputs]
+                s1 = p(a[0] if len(a) == 1 else tuple(a))
+                s2 = p(b[0] if len(b) == 1 else tuple(b))
+                res['spike_split'] = torch.cat([s1, s2], dim=-1)
+                for name, buf in p.named_buffers():
+                    if name.endswith('_state'):
+                        res[f'final_{name}'] = buf
+        return res
+
+    x = randn(B, C, T, mean=0.3)
+    r = run_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03, requires_grad=True), [x],
+                   ['current_decay', 'voltage_decay'], split=30)
+    save('neuron_cuba_shared', x=x, **r)
+    r = run_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03, shared_param=False, requires_grad=True,
+                                                     graded_spike=True), [x],
+                   ['current_decay', 'voltage_decay'],
+                   set_params={'current_decay': torch.tensor([900., 1000., 1024., 1100., 1200.]),
+                               'voltage_decay': torch.tensor([100., 120., 123., 130., 140.])}, split=32)
+    save('neuron_cuba_chan_graded', x=x, **r)
+    x4 = randn(B2, C2, H2, T2, mean=0.3)
+    r = run_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03), [x4], ['current_decay', 'voltage_decay'],
+                   split=32)
+    save('neuron_cuba_rank4', x=x4, **r)
+
+    x = randn(B, C, T, mean=0.2)
+    r = run_neuron(lambda: slayer.neuron.alif.Neuron(1.0, 0.5, 0.2, 0.05, 0.1, 0.1), [x],
+                   ['current_decay', 'voltage_decay', 'threshold_decay', 'refractory_decay'], split=40)
+    save('neuron_alif_shared', x=x, **r)
+    r = run_neuron(lambda: slayer.neuron.alif.Neuron(1.0, 0.5, 0.2, 0.05, 0.1, 0.1, shared_param=False,
+                                                     requires_grad=True), [x],
+                   ['current_decay', 'voltage_decay', 'threshold_decay', 'refractory_decay'],
+                   set_params={'current_decay': torch.tensor([800., 810., 819., 830., 840.]),
+                               'voltage_decay': torch.tensor([200., 203., 205., 207., 210.]),
+                               'threshold_decay': torch.tensor([400., 405., 410., 415., 420.]),
+                               'refractory_decay': torch.tensor([380., 395., 410., 425., 440.])}, split=33)
+    save('neuron_alif_chan', x=x, **r)
+
+    re_in, im_in = randn(B, C, T, std=0.5), randn(B, C, T, std=0.5)
+    r = run_neuron(lambda: slayer.neuron.rf.Neuron(0.5, 10, 0.1, requires_grad=True), [re_in, im_in],
+                   ['sin_decay', 'cos_decay'], split=37)
+    save('neuron_rf_shared', re_in=re_in, im_in=im_in, **r)
+    sd, cd = sincos([10., 15., 20., 30., 40.])
+    r = run_neuron(lambda: slayer.neuron.adrf.Neuron(0.5, 0.25, [10, 40], 0.1, 0.1, 0.1, shared_param=False,
+                                                     requires_grad=True), [re_in, im_in],
+                   ['sin_decay', 'cos_decay', 'threshold_decay', 'refractory_decay'],
+                   set_params={'sin_decay': sd, 'cos_decay': cd,
+                               'threshold_decay': torch.full((5,), 410.),
+                               'refractory_decay': torch.full((5,), 410.)}, split=32)
+    save('neuron_adrf_chan', re_in=re_in, im_in=im_in, **r)
+    r = run_neuron(lambda: slayer.neuron.adrf.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1), [re_in, im_in],
+                   ['sin_decay', 'cos_decay', 'threshold_decay', 'refractory_decay'], split=50)
+    save('neuron_adrf_shared', re_in=re_in, im_in=im_in, **r)
+
+    total = 0
+    for name, arrays in cases.items():
+        path = os.path.join(out_dir, name + '.npz')
+        np.savez_compressed(path, **arrays)
+        total += os.path.getsize(path)
+    print(f'wrote {len(cases)} cases, {total / 1024:.0f} KiB, to {out_dir}')
+
+
+if __name__ == '__main__':
+    main()

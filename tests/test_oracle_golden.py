@@ -1,0 +1,189 @@
+"""The CPU oracle against outputs of lava-dl itself (tests/golden/*.npz, made by
+tests/golden/make_golden.py).  This is what pins the oracle; it runs without a
+GPU."""
+
+import numpy as np
+import pytest
+
+from _util import (assert_close, assert_exact, assert_quantised_equal, golden_cases, load_golden)
+from oracle import oracle as O
+
+
+def thr_of(g):
+    t = g['threshold']
+    return None if (t.ndim == 0 and float(t) < 0) else (float(t) if t.ndim == 0 else t)
+
+
+@pytest.mark.parametrize('name', golden_cases('li_'))
+def test_leaky_integrator(name):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    y = O.li_fwd(g['x'], g['decay'], g['state'], w, thr_of(g))
+    if w & (w - 1) == 0:
+        assert_quantised_equal(y, g['y'], w, 'li output')
+    assert_exact(y, g['y'], 'li output')
+    if 'grad_in' in g:
+        gi, gd = O.li_bwd(g['grad_out'], g['y'], g['decay'])
+        assert_close(gi, g['grad_in'], 'li grad_in')
+        assert_close(gd, g['grad_decay'], 'li grad_decay')
+
+
+@pytest.mark.parametrize('name', golden_cases('ath_'))
+def test_adaptive_threshold(name):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    th, ref = O.ath_fwd(g['x'], g['ref_state'], g['ref_decay'], g['th_state'], g['th_decay'],
+                        float(g['th_scale']), float(g['th0']), w)
+    assert_quantised_equal(th, g['threshold'], w, 'threshold')
+    assert_quantised_equal(ref, g['refractory'], w, 'refractory')
+
+
+@pytest.mark.parametrize('name', golden_cases('apth_'))
+def test_adaptive_phase_threshold(name):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    th, ref = O.apth_fwd(g['re'], g['im'], g['im_state'], g['ref_state'], g['ref_decay'], g['th_state'],
+                         g['th_decay'], float(g['th_scale']), float(g['th0']), w)
+    assert_quantised_equal(th, g['threshold'], w, 'threshold')
+    assert_quantised_equal(ref, g['refractory'], w, 'refractory')
+
+
+@pytest.mark.parametrize('name', golden_cases('res_'))
+def test_resonator(name):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    re, im = O.res_fwd(g['re_in'], g['im_in'], g['sin_decay'], g['cos_decay'], g['re_state'], g['im_state'], w,
+                       thr_of(g))
+    assert_quantised_equal(re, g['re'], w, 'real')
+    assert_quantised_equal(im, g['im'], w, 'imag')
+    a, b, gs, gc = O.res_bwd(g['grad_re'], g['grad_im'], g['re'], g['im'], g['sin_decay'], g['cos_decay'])
+    assert_close(a, g['grad_re_in'], 'grad_re_in')
+    assert_close(b, g['grad_im_in'], 'grad_im_in')
+    assert_close(gs, g['grad_sin'], 'grad_sin')
+    assert_close(gc, g['grad_cos'], 'grad_cos')
+
+
+@pytest.mark.parametrize('name', golden_cases('adres_'))
+def test_adaptive_resonator(name):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    re, im, th, ref = O.adres_fwd(g['re_in'], g['im_in'], g['sin_decay'], g['cos_decay'], g['ref_decay'],
+                                  g['th_decay'], g['re_state'], g['im_state'], g['ref_state'], g['th_state'],
+                                  float(g['th_scale']), float(g['th0']), w)
+    for got, key in ((re, 're'), (im, 'im'), (th, 'threshold'), (ref, 'refractory')):
+        assert_quantised_equal(got, g[key], w, key)
+    a, b, gs, gc = O.res_bwd(g['grad_re'], g['grad_im'], g['re'], g['im'], g['sin_decay'], g['cos_decay'])
+    assert_close(a, g['grad_re_in'], 'grad_re_in')
+    assert_close(b, g['grad_im_in'], 'grad_im_in')
+    assert_close(gs, g['grad_sin'], 'grad_sin')
+    assert_close(gc, g['grad_cos'], 'grad_cos')
+
+
+@pytest.mark.parametrize('name', golden_cases('spike_'))
+def test_spike(name):
+    g = load_golden(name)
+    thr = g['threshold'] if g['threshold'].ndim else float(g['threshold'])
+    graded = bool(g['graded'])
+    s = O.spike_fwd(g['v'], thr, graded, 1)
+    assert_exact(s, g['spike'], 'spike')
+    gv = O.spike_bwd(g['v'], thr, g['grad_spike'], float(g['tau_rho']), float(g['scale_rho']), graded)
+    assert_close(gv, g['grad_v'], 'grad_v')
+
+
+@pytest.mark.parametrize('name', golden_cases('cspike_'))
+def test_complex_spike(name):
+    g = load_golden(name)
+    thr = g['threshold'] if g['threshold'].ndim else float(g['threshold'])
+    graded = bool(g['graded'])
+    s = O.cspike_fwd(g['re'], g['im'], thr, g['imag_last'], graded, 1)
+    assert_exact(s, g['spike'], 'spike')
+    gre, gim = O.cspike_bwd(g['re'], g['im'], thr, g['grad_spike'], float(g['tau_rho']), float(g['scale_rho']),
+                            graded)
+    assert_close(gre, g['grad_re'], 'grad_re')
+    assert_close(gim, g['grad_im'], 'grad_im')
+
+
+@pytest.mark.parametrize('name', golden_cases('shift_'))
+def test_shift(name):
+    g = load_golden(name)
+    sv = g['shift'] if g['shift'].ndim else float(g['shift'])
+    assert_exact(O.shift(g['x'], sv, float(g['sampling_time'])), g['out'], 'shift')
+
+
+@pytest.mark.parametrize('name', golden_cases('fir_'))
+def test_fir(name):
+    g = load_golden(name)
+    ts = float(g['sampling_time'])
+    assert_close(O.conv(g['x'], g['filter'], ts), g['conv'], 'conv')
+    assert_close(O.corr(g['x'], g['filter'], ts), g['corr'], 'corr')
+    assert_close(O.corr(g['grad_out'], g['filter'], ts), g['grad_conv'], 'conv backward')
+
+
+def test_delay_filter_chain():
+    g = load_golden('delay_fir_chain')
+    y = O.conv(O.shift(g['x'], g['delay']), g['filter'])
+    assert_close(y, g['out'], 'conv(delay(x))')
+    gx = O.shift(O.corr(g['grad_out'], g['filter']), -g['delay'])
+    assert_close(gx, g['grad_x'], 'grad_x')
+
+
+# --------------------------------------------------------------------------
+# neuron-level sequences
+# --------------------------------------------------------------------------
+S = 4096
+
+
+@pytest.mark.parametrize('name', golden_cases('neuron_cuba'))
+def test_cuba_neuron(name):
+    g = load_golden(name)
+    graded = 'graded' in name
+    r = O.cuba(g['x'], 1.25, g['param_current_decay'], g['param_voltage_decay'], grad_spike=g['grad_spike'],
+               graded=graded)
+    assert_exact(r['spike'], g['spike'], 'spike')
+    assert_quantised_equal(r['current'], g['dyn0'], S, 'current')
+    assert_quantised_equal(r['voltage'], g['dyn1'], S, 'voltage')
+    assert_close(r['grad_x'], g['grad_in0'], 'grad_x')
+    if 'grad_current_decay' in g:
+        assert_close(r['grad_current_decay'], g['grad_current_decay'], 'grad current decay')
+        assert_close(r['grad_voltage_decay'], g['grad_voltage_decay'], 'grad voltage decay')
+
+
+@pytest.mark.parametrize('name', golden_cases('neuron_alif'))
+def test_alif_neuron(name):
+    g = load_golden(name)
+    r = O.alif(g['x'], 1.0, 0.5, g['param_current_decay'], g['param_voltage_decay'], g['param_threshold_decay'],
+               g['param_refractory_decay'], grad_spike=g['grad_spike'])
+    assert_exact(r['spike'], g['spike'], 'spike')
+    for i, k in enumerate(('current', 'voltage', 'threshold', 'refractory')):
+        assert_quantised_equal(r[k], g[f'dyn{i}'], S, k)
+    assert_close(r['grad_x'], g['grad_in0'], 'grad_x')
+    if 'grad_current_decay' in g:
+        assert_close(r['grad_current_decay'], g['grad_current_decay'], 'grad current decay')
+        assert_close(r['grad_voltage_decay'], g['grad_voltage_decay'], 'grad voltage decay')
+
+
+def test_rf_neuron():
+    g = load_golden('neuron_rf_shared')
+    r = O.rf(g['re_in'], g['im_in'], 0.5, g['param_sin_decay'], g['param_cos_decay'], grad_spike=g['grad_spike'])
+    assert_exact(r['spike'], g['spike'], 'spike')
+    assert_quantised_equal(r['real'], g['dyn0'], S, 'real')
+    assert_quantised_equal(r['imag'], g['dyn1'], S, 'imag')
+    assert_close(r['grad_re'], g['grad_in0'], 'grad_re')
+    assert_close(r['grad_im'], g['grad_in1'], 'grad_im')
+    assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
+    assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
+
+
+@pytest.mark.parametrize('name', golden_cases('neuron_adrf'))
+def test_adrf_neuron(name):
+    g = load_golden(name)
+    r = O.adrf(g['re_in'], g['im_in'], 0.5, 0.25, g['param_sin_decay'], g['param_cos_decay'],
+               g['param_threshold_decay'], g['param_refractory_decay'], grad_spike=g['grad_spike'])
+    assert_exact(r['spike'], g['spike'], 'spike')
+    for i, k in enumerate(('real', 'imag', 'threshold', 'refractory')):
+        assert_quantised_equal(r[k], g[f'dyn{i}'], S, k)
+    assert_close(r['grad_re'], g['grad_in0'], 'grad_re')
+    assert_close(r['grad_im'], g['grad_in1'], 'grad_im')
+    if 'grad_sin_decay' in g:
+        assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
+        assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
