@@ -83,12 +83,27 @@ bool tma_eligible(const void* const* ptrs, int n, int64_t T) {
   return encode_fn() != nullptr;
 }
 
+// The encode call is a driver-API function and wants a context current on the
+// calling thread.  Threads that have only been handed a device by the runtime
+// (an autograd worker after cudaSetDevice, say) may not have bound the primary
+// context yet; a no-op runtime call does that.
+static void bind_primary_context() {
+  static thread_local int bound_dev = -1;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  if (dev != bound_dev) {
+    cudaFree(nullptr);
+    bound_dev = dev;
+  }
+}
+
 int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return SB_ERR_UNSUPPORTED;
   }
+  bind_primary_context();
   const cuuint64_t dims[2] = {(cuuint64_t)T, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)T * 4};
   const cuuint32_t box[2] = {(cuuint32_t)kTileT, (cuuint32_t)kTileR};

@@ -53,6 +53,7 @@ int sb_li_fwd(const float* x, const float* decay, int64_t n_decay, const float* 
   RowGeom rg;
   SB_TRY(check_count(n_decay, "decay"));
   SB_TRY(check_geom(g, &rg, n_decay));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(w_scale > 0, "w_scale must be positive");
   SB_REQUIRE(decay && state, "null parameter pointer");
   const bool reset = thr_scaled > 0.f;
@@ -103,6 +104,7 @@ int sb_ath_fwd(const float* x, const float* ref_state, const float* ref_decay, i
   SB_TRY(check_count(n_ref_decay, "ref_decay"));
   SB_TRY(check_count(n_th_decay, "th_decay"));
   SB_TRY(check_geom(g, &rg, n_ref_decay > n_th_decay ? n_ref_decay : n_th_decay));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(n_ref_decay == 1 || n_th_decay == 1 || n_ref_decay == n_th_decay, "decay counts disagree");
   SB_REQUIRE(w_scale > 0, "w_scale must be positive");
   SB_REQUIRE(ref_state && ref_decay && th_state && th_decay, "null parameter pointer");
@@ -126,6 +128,7 @@ int sb_apth_fwd(const float* re, const float* im, const float* im_state, const f
   SB_TRY(check_count(n_ref_decay, "ref_decay"));
   SB_TRY(check_count(n_th_decay, "th_decay"));
   SB_TRY(check_geom(g, &rg, n_ref_decay > n_th_decay ? n_ref_decay : n_th_decay));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(n_ref_decay == 1 || n_th_decay == 1 || n_ref_decay == n_th_decay, "decay counts disagree");
   SB_REQUIRE(w_scale > 0, "w_scale must be positive");
   SB_REQUIRE(im_state && ref_state && ref_decay && th_state && th_decay, "null parameter pointer");
@@ -147,6 +150,7 @@ int sb_res_fwd(const float* re_in, const float* im_in, const float* sin_decay, c
   RowGeom rg;
   SB_TRY(check_count(n_decay, "sin/cos decay"));
   SB_TRY(check_geom(g, &rg, n_decay));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(w_scale > 0, "w_scale must be positive");
   SB_REQUIRE(sin_decay && cos_decay && re_state && im_state, "null parameter pointer");
   const float* in[2] = {re_in, im_in};
@@ -206,6 +210,7 @@ int sb_adres_fwd(const float* re_in, const float* im_in, const float* sin_decay,
   SB_TRY(check_count(n_th_decay, "th_decay"));
   const int64_t nmax = max3(n_decay, n_ref_decay, n_th_decay);
   SB_TRY(check_geom(g, &rg, nmax));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE((n_decay == 1 || n_decay == nmax) && (n_ref_decay == 1 || n_ref_decay == nmax) &&
                  (n_th_decay == 1 || n_th_decay == nmax),
              "parameter counts disagree");

@@ -55,6 +55,7 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
   SB_TRY(check_count(n_vdecay, "voltage decay"));
   const int64_t nmax = maxn({n_cdecay, n_vdecay});
   SB_TRY(check_geom(g, &rg, nmax));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(counts_ok({n_cdecay, n_vdecay}, nmax), "decay counts disagree");
   SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
   SB_REQUIRE(cdecay && vdecay && cstate && vstate, "null parameter pointer");
@@ -153,6 +154,7 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
   SB_TRY(check_count(n_th_decay, "threshold decay"));
   const int64_t nmax = maxn({n_cdecay, n_vdecay, n_ref_decay, n_th_decay});
   SB_TRY(check_geom(g, &rg, nmax));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(counts_ok({n_cdecay, n_vdecay, n_ref_decay, n_th_decay}, nmax), "decay counts disagree");
   SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
   SB_REQUIRE(cdecay && vdecay && ref_decay && th_decay && cstate && vstate && ref_state && th_state,
@@ -189,6 +191,7 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
   SB_TRY(check_count(n_th_decay, "threshold decay"));
   const int64_t nmax = maxn({n_decay, n_ref_decay, n_th_decay});
   SB_TRY(check_geom(g, &rg, nmax));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;  // nothing to do, pointers may be null
   SB_REQUIRE(counts_ok({n_decay, n_ref_decay, n_th_decay}, nmax), "parameter counts disagree");
   SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
   SB_REQUIRE(sin_decay && cos_decay && re_state && im_state, "null parameter pointer");

@@ -184,12 +184,12 @@ class Neuron(ResonatorBase):
             real, imag, threshold, refractory = self.dynamics(input)
             return self.spike(real, imag, threshold, refractory)
         real_input, imag_input = self._prepare(input)
-        adaptive = (quantize(self.refractory_decay), quantize(self.threshold_decay), self.refractory_state,
-                    self.threshold_state, self.threshold_step, self.threshold)
         spike, final_re, final_im, final_s, final_th, final_ref = _FusedForward.apply(
             real_input, imag_input, quantize(self.sin_decay), quantize(self.cos_decay), self.real_state,
             self.imag_state, self.threshold, self.s_scale, self.tau_rho * TAU_RHO_MULT,
-            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, adaptive)
+            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, quantize(self.refractory_decay),
+            quantize(self.threshold_decay), self.refractory_state, self.threshold_state, self.threshold_step,
+            self.threshold)
         if self.persistent_state:
             with torch.no_grad():
                 self.real_state = final_re

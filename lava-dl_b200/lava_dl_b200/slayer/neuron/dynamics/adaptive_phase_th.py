@@ -12,12 +12,25 @@ def dynamics(re_input, im_input, im_state, ref_state, ref_decay, th_state, th_de
     """Threshold and refractory traces of a resonator that spikes when the real
     part exceeds ``threshold + refractory`` while the imaginary part crosses
     zero upwards.  Returns ``(threshold, refractory)``; no gradient."""
-    with torch.no_grad():
-        threshold, refractory = _ops.apth_fwd(
-            re_input, im_input, im_state, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
+    threshold, refractory = _APTHDynamics.apply(
+        re_input, im_input, im_state, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
     if debug:
         _debug.check_quantised(w_scale, threshold=threshold, refractory=refractory)
     return threshold, refractory
+
+
+class _APTHDynamics(torch.autograd.Function):
+    """No gradient flows through this op (``adaptive_phase_th.py:227-231``)."""
+
+    @staticmethod
+    def forward(ctx, re_input, im_input, im_state, ref_state, ref_decay, th_state, th_decay, th_scale, th0,
+                w_scale):
+        return _ops.apth_fwd(re_input, im_input, im_state, ref_state, ref_decay, th_state, th_decay, th_scale,
+                             th0, w_scale)
+
+    @staticmethod
+    def backward(*_):
+        return (None,) * 10
 
 
 def persistent_ref_state(ref_state, spike, th_state):

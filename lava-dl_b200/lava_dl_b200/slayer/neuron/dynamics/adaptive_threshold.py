@@ -23,12 +23,25 @@ def dynamics(input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_s
 
     Returns ``(threshold, refractory)``; no gradient flows through this op.
     """
-    with torch.no_grad():
-        threshold, refractory = _ops.ath_fwd(
-            input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
+    threshold, refractory = _ATHDynamics.apply(
+        input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
     if debug:
         _debug.check_quantised(w_scale, threshold=threshold, refractory=refractory)
     return threshold, refractory
+
+
+class _ATHDynamics(torch.autograd.Function):
+    """No gradient flows through this op; like the reference
+    (``adaptive_threshold.py:230-234``) the backward hands ``None`` to every
+    input, which autograd turns into zero gradients for learnable decays."""
+
+    @staticmethod
+    def forward(ctx, input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale):
+        return _ops.ath_fwd(input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
+
+    @staticmethod
+    def backward(*_):
+        return (None,) * 8
 
 
 def persistent_ref_state(ref_state, spike, th_state):

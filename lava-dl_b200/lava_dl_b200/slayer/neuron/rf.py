@@ -27,16 +27,18 @@ def neuron_params(device_params, scale=1 << 6, p_scale=1 << 12):
 
 
 class _FusedForward(torch.autograd.Function):
-    """Resonator + phase-threshold spike in one pass each way.  ``adaptive`` is
-    None (RF) or the tuple (ref_decay, th_decay, ref_state, th_state, th_step,
-    th0) of the adaptive neuron."""
+    """Resonator + phase-threshold spike in one pass each way.  The adaptive
+    neuron additionally passes its threshold / refractory decays and states
+    (``ref_decay`` is None for the plain RF neuron)."""
 
     @staticmethod
     def forward(ctx, real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold, w_scale,
-                tau_rho, scale_rho, graded, adaptive):
+                tau_rho, scale_rho, graded, ref_decay=None, th_decay=None, ref_state=None, th_state=None,
+                th_step=0.0, th0=0.0):
         ad = None
-        if adaptive is not None:
-            ad = dict(zip(('ref_decay', 'th_decay', 'ref_state', 'th_state', 'th_step', 'th0'), adaptive))
+        if ref_decay is not None:
+            ad = dict(ref_decay=ref_decay, th_decay=th_decay, ref_state=ref_state, th_state=th_state,
+                      th_step=th_step, th0=th0)
         outs, fin = _ops.rf_fwd(real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold,
                                 w_scale, graded=graded, spike_scale=1.0, adaptive=ad)
         spike, real, imag = outs[:3]
@@ -62,7 +64,7 @@ class _FusedForward(torch.autograd.Function):
         gre, gim, gsin, gcos = _ops.rf_bwd(grad_spike, real, imag, threshold, sin_decay, cos_decay, tau_rho,
                                            scale_rho, graded, need)
         resonator._raise_on_nan(grad_sin_decay=gsin, grad_cos_decay=gcos)
-        return (gre, gim, gsin, gcos) + (None,) * 8
+        return (gre, gim, gsin, gcos) + (None,) * 13
 
 
 class ResonatorBase(base.Neuron):
@@ -251,7 +253,7 @@ class Neuron(ResonatorBase):
         spike, final_re, final_im, _ = _FusedForward.apply(
             real_input, imag_input, quantize(self.sin_decay), quantize(self.cos_decay), self.real_state,
             self.imag_state, self.threshold, self.s_scale, self.tau_rho * TAU_RHO_MULT,
-            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, None)
+            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, None, None, None, None, 0.0, 0.0)
         if self.persistent_state:
             with torch.no_grad():
                 self.real_state = final_re

@@ -1,0 +1,308 @@
+"""The CUDA path, driven through the lava-dl-shaped Python API, against outputs
+of lava-dl itself (tests/golden/*.npz).  Mirrors test_oracle_golden.py."""
+
+import numpy as np
+import pytest
+import torch
+
+from _util import (assert_close, assert_exact, assert_quantised_equal, cspike_term_scale, golden_cases, li_scale,
+                   load_golden, pgrad_scale, res_scale)
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+S = 4096
+
+
+def T(a, cuda, grad=False):
+    t = torch.tensor(np.asarray(a), dtype=torch.float32, device=cuda)
+    return t.requires_grad_(True) if grad else t
+
+
+def thr_of(g):
+    t = g['threshold']
+    return None if (t.ndim == 0 and float(t) < 0) else float(t)
+
+
+@pytest.fixture(scope='module')
+def slayer(cuda):
+    import lava_dl_b200.slayer as s
+    return s
+
+
+@pytest.mark.parametrize('name', golden_cases('li_'))
+def test_leaky_integrator(name, cuda, slayer):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    li = slayer.neuron.dynamics.leaky_integrator
+    x, dec = T(g['x'], cuda, True), T(g['decay'], cuda, True)
+    y = li.dynamics(x, dec, T(g['state'], cuda), w, threshold=thr_of(g), debug=(w & (w - 1) == 0))
+    assert_exact(y, g['y'], 'li output')
+    if 'grad_in' in g:
+        y.backward(T(g['grad_out'], cuda))
+        assert_close(x.grad, g['grad_in'], 'li grad_in', scale=li_scale(g['grad_out'], g['decay']))
+        assert_close(dec.grad, g['grad_decay'], 'li grad_decay',
+                     scale=pgrad_scale(g['decay'].size, (g['grad_in'], g['y'])))
+
+
+@pytest.mark.parametrize('name', golden_cases('ath_'))
+def test_adaptive_threshold(name, cuda, slayer):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    th, ref = slayer.neuron.dynamics.adaptive_threshold.dynamics(
+        T(g['x'], cuda), T(g['ref_state'], cuda), T(g['ref_decay'], cuda), T(g['th_state'], cuda),
+        T(g['th_decay'], cuda), float(g['th_scale']), float(g['th0']), w, debug=True)
+    assert_quantised_equal(th, g['threshold'], w, 'threshold')
+    assert_quantised_equal(ref, g['refractory'], w, 'refractory')
+
+
+@pytest.mark.parametrize('name', golden_cases('apth_'))
+def test_adaptive_phase_threshold(name, cuda, slayer):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    th, ref = slayer.neuron.dynamics.adaptive_phase_th.dynamics(
+        T(g['re'], cuda), T(g['im'], cuda), T(g['im_state'], cuda), T(g['ref_state'], cuda),
+        T(g['ref_decay'], cuda), T(g['th_state'], cuda), T(g['th_decay'], cuda), float(g['th_scale']),
+        float(g['th0']), w)
+    assert_quantised_equal(th, g['threshold'], w, 'threshold')
+    assert_quantised_equal(ref, g['refractory'], w, 'refractory')
+
+
+@pytest.mark.parametrize('name', golden_cases('res_'))
+def test_resonator(name, cuda, slayer):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    re_in, im_in = T(g['re_in'], cuda, True), T(g['im_in'], cuda, True)
+    sd, cd = T(g['sin_decay'], cuda, True), T(g['cos_decay'], cuda, True)
+    re, im = slayer.neuron.dynamics.resonator.dynamics(
+        re_in, im_in, sd, cd, T(g['re_state'], cuda), T(g['im_state'], cuda), w, threshold=thr_of(g))
+    assert_quantised_equal(re, g['re'], w, 'real')
+    assert_quantised_equal(im, g['im'], w, 'imag')
+    (re * T(g['grad_re'], cuda) + im * T(g['grad_im'], cuda)).sum().backward()
+    S_re, S_im = res_scale(g['grad_re'], g['grad_im'], g['sin_decay'], g['cos_decay'])
+    S_p = pgrad_scale(g['sin_decay'].size, (g['grad_re_in'], g['re']), (g['grad_re_in'], g['im']),
+                      (g['grad_im_in'], g['re']), (g['grad_im_in'], g['im']))
+    assert_close(re_in.grad, g['grad_re_in'], 'grad_re_in', scale=S_re)
+    assert_close(im_in.grad, g['grad_im_in'], 'grad_im_in', scale=S_im)
+    assert_close(sd.grad, g['grad_sin'], 'grad_sin', scale=S_p)
+    assert_close(cd.grad, g['grad_cos'], 'grad_cos', scale=S_p)
+
+
+@pytest.mark.parametrize('name', golden_cases('adres_'))
+def test_adaptive_resonator(name, cuda, slayer):
+    g = load_golden(name)
+    w = int(g['w_scale'])
+    re_in, im_in = T(g['re_in'], cuda, True), T(g['im_in'], cuda, True)
+    sd, cd = T(g['sin_decay'], cuda, True), T(g['cos_decay'], cuda, True)
+    re, im, th, ref = slayer.neuron.dynamics.adaptive_resonator.dynamics(
+        re_in, im_in, sd, cd, T(g['ref_decay'], cuda), T(g['th_decay'], cuda), T(g['re_state'], cuda),
+        T(g['im_state'], cuda), T(g['ref_state'], cuda), T(g['th_state'], cuda), float(g['th_scale']),
+        float(g['th0']), w)
+    for got, key in ((re, 're'), (im, 'im'), (th, 'threshold'), (ref, 'refractory')):
+        assert_quantised_equal(got, g[key], w, key)
+    (re * T(g['grad_re'], cuda) + im * T(g['grad_im'], cuda)).sum().backward()
+    S_re, S_im = res_scale(g['grad_re'], g['grad_im'], g['sin_decay'], g['cos_decay'])
+    S_p = pgrad_scale(g['sin_decay'].size, (g['grad_re_in'], g['re']), (g['grad_re_in'], g['im']),
+                      (g['grad_im_in'], g['re']), (g['grad_im_in'], g['im']))
+    assert_close(re_in.grad, g['grad_re_in'], 'grad_re_in', scale=S_re)
+    assert_close(im_in.grad, g['grad_im_in'], 'grad_im_in', scale=S_im)
+    assert_close(sd.grad, g['grad_sin'], 'grad_sin', scale=S_p)
+    assert_close(cd.grad, g['grad_cos'], 'grad_cos', scale=S_p)
+
+
+@pytest.mark.parametrize('name', golden_cases('spike_'))
+def test_spike(name, cuda, slayer):
+    g = load_golden(name)
+    thr = T(g['threshold'], cuda) if g['threshold'].ndim else float(g['threshold'])
+    graded = bool(g['graded'])
+    v = T(g['v'], cuda, True)
+    s = slayer.spike.Spike.apply(v, thr, float(g['tau_rho']), float(g['scale_rho']), graded,
+                                 torch.zeros(v.shape[:-1], device=cuda), 1)
+    assert_exact(s, g['spike'], 'spike')
+    s.backward(T(g['grad_spike'], cuda))
+    assert_close(v.grad, g['grad_v'], 'grad_v')
+
+
+@pytest.mark.parametrize('name', golden_cases('cspike_'))
+def test_complex_spike(name, cuda, slayer):
+    g = load_golden(name)
+    thr = T(g['threshold'], cuda) if g['threshold'].ndim else float(g['threshold'])
+    graded = bool(g['graded'])
+    re, im = T(g['re'], cuda, True), T(g['im'], cuda, True)
+    s = slayer.spike.complex.Spike.apply(re, im, thr, float(g['tau_rho']), float(g['scale_rho']), graded,
+                                         T(g['imag_last'], cuda), 1)
+    assert_exact(s, g['spike'], 'spike')
+    s.backward(T(g['grad_spike'], cuda))
+    t_re, t_im = cspike_term_scale(g['re'], g['im'], g['threshold'] if g['threshold'].ndim else float(g['threshold']),
+                                   g['grad_spike'], float(g['tau_rho']), float(g['scale_rho']), graded)
+    assert_close(re.grad, g['grad_re'], 'grad_re', scale=t_re)
+    assert_close(im.grad, g['grad_im'], 'grad_im', scale=t_im)
+
+
+@pytest.mark.parametrize('name', golden_cases('shift_'))
+def test_shift(name, cuda, slayer):
+    g = load_golden(name)
+    sv = T(g['shift'], cuda) if g['shift'].ndim else float(g['shift'])
+    out = slayer.utils.time.shift(T(g['x'], cuda), sv, float(g['sampling_time']))
+    assert_exact(out, g['out'], 'shift')
+
+
+@pytest.mark.parametrize('name', golden_cases('fir_'))
+def test_fir(name, cuda, slayer):
+    g = load_golden(name)
+    ts = float(g['sampling_time'])
+    x = T(g['x'], cuda, True)
+    f = T(g['filter'], cuda)
+    y = slayer.utils.filter.conv(x, f, ts)
+    assert_close(y, g['conv'], 'conv')
+    y.backward(T(g['grad_out'], cuda))
+    assert_close(x.grad, g['grad_conv'], 'conv backward')
+    assert_close(slayer.utils.filter.corr(T(g['x'], cuda), f, ts), g['corr'], 'corr')
+
+
+def test_delay_filter_chain(cuda, slayer):
+    g = load_golden('delay_fir_chain')
+    x = T(g['x'], cuda, True)
+    y = slayer.utils.filter.conv(slayer.axon.delay(x, T(g['delay'], cuda)), T(g['filter'], cuda))
+    assert_close(y, g['out'], 'conv(delay(x))')
+    y.backward(T(g['grad_out'], cuda))
+    assert_close(x.grad, g['grad_x'], 'grad_x')
+
+
+# --------------------------------------------------------------------------
+# neuron classes
+# --------------------------------------------------------------------------
+def _bind_params(neuron, g, names, arg, cuda):
+    """Bind the shape (first call) and then install the golden parameters."""
+    with torch.no_grad():
+        neuron(arg)
+        for k in names:
+            getattr(neuron, k).data = T(g[f'param_{k}'], cuda)
+        for name, buf in neuron.named_buffers():
+            if name.endswith('_state'):
+                buf.zero_()
+                if name == 'threshold_state':
+                    buf.add_(neuron.threshold)
+    return neuron
+
+
+def _neuron_scales(kind, g, neuron):
+    """Magnitude scans for the input and parameter gradients of a neuron (see _util)."""
+    gs = g['grad_spike']
+    graded = bool(neuron.graded_spike)
+    if kind in ('cuba', 'alif'):
+        cur, vol = g['dyn0'], g['dyn1']
+        cd, vd = np.round(g['param_current_decay']), np.round(g['param_voltage_decay'])
+        thr = (neuron.threshold + neuron.threshold_eps) if kind == 'cuba' else g['dyn2'] + g['dyn3']
+        g_v = O.spike_bwd(vol, thr, gs, neuron.tau_rho * 100, neuron.scale_rho * 0.1, graded)
+        g_c, _ = O.li_bwd(g_v, vol, vd)
+        return {'grad_in0': li_scale(li_scale(g_v, vd), cd),
+                'grad_current_decay': pgrad_scale(cd.size, (g['grad_in0'], cur)),
+                'grad_voltage_decay': pgrad_scale(vd.size, (g_c, vol))}
+    re, im = g['dyn0'], g['dyn1']
+    sd, cd = np.round(g['param_sin_decay']), np.round(g['param_cos_decay'])
+    if kind == 'rf':
+        thr, tau, srho = neuron.threshold, neuron.tau_rho * 0.5, neuron.scale_rho * 10
+    else:
+        thr, tau, srho = g['dyn2'] + g['dyn3'], neuron.tau_rho * 100, neuron.scale_rho * 0.1
+    s_re, s_im = cspike_term_scale(re, im, thr, gs, tau, srho, graded)
+    S_re, S_im = res_scale(s_re, s_im, sd, cd)
+    S_p = pgrad_scale(sd.size, (g['grad_in0'], re), (g['grad_in0'], im), (g['grad_in1'], re), (g['grad_in1'], im))
+    return {'grad_in0': S_re, 'grad_in1': S_im, 'grad_sin_decay': S_p, 'grad_cos_decay': S_p}
+
+
+def _check_neuron(make, g, names, input_keys, dyn_keys, split, cuda, kind):
+    ins = [T(g[k], cuda, True) for k in input_keys]
+    arg = ins[0] if len(ins) == 1 else tuple(ins)
+    plain = [T(g[k], cuda) for k in input_keys]
+    parg = plain[0] if len(plain) == 1 else tuple(plain)
+
+    n = _bind_params(make().to(cuda), g, names, parg, cuda)
+    spike = n(arg)
+    assert_exact(spike, g['spike'], 'spike')
+    (spike * T(g['grad_spike'], cuda)).sum().backward()
+    scales = _neuron_scales(kind, g, n)
+    for i, t in enumerate(ins):
+        assert_close(t.grad, g[f'grad_in{i}'], f'grad_in{i}', scale=scales[f'grad_in{i}'])
+    for k in names:
+        if f'grad_{k}' not in g:
+            assert getattr(n, k).grad is None, f'{k} is not learnable in this case'
+        elif f'grad_{k}' in scales:
+            assert_close(getattr(n, k).grad, g[f'grad_{k}'], f'grad_{k}', scale=scales[f'grad_{k}'])
+        else:  # threshold / refractory decays: the reference leaves exact zeros
+            assert_exact(getattr(n, k).grad, g[f'grad_{k}'], f'grad_{k}')
+
+    with torch.no_grad():
+        m = _bind_params(make().to(cuda), g, names, parg, cuda)
+        for i, (t, k) in enumerate(zip(m.dynamics(parg), dyn_keys)):
+            assert_quantised_equal(t, g[f'dyn{i}'], S, k)
+
+        p = make().to(cuda)
+        p.persistent_state = True
+        _bind_params(p, g, names, parg, cuda)
+        a = [t[..., :split].contiguous() for t in plain]
+        b = [t[..., split:].contiguous() for t in plain]
+        s1 = p(a[0] if len(a) == 1 else tuple(a))
+        s2 = p(b[0] if len(b) == 1 else tuple(b))
+        assert_exact(torch.cat([s1, s2], dim=-1), g['spike_split'], 'persistent-state split run')
+        assert_exact(torch.cat([s1, s2], dim=-1), g['spike'], 'split run equals one-shot run')
+        for name, buf in p.named_buffers():
+            if name.endswith('_state'):
+                assert_quantised_equal(buf, g[f'final_{name}'], S, f'final {name}')
+
+
+def test_cuba_shared(cuda, slayer):
+    g = load_golden('neuron_cuba_shared')
+    _check_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03, requires_grad=True), g,
+                  ['current_decay', 'voltage_decay'], ['x'], ['current', 'voltage'], 30, cuda, 'cuba')
+
+
+def test_cuba_per_channel_graded(cuda, slayer):
+    g = load_golden('neuron_cuba_chan_graded')
+    _check_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03, shared_param=False, requires_grad=True,
+                                                    graded_spike=True), g,
+                  ['current_decay', 'voltage_decay'], ['x'], ['current', 'voltage'], 32, cuda, 'cuba')
+
+
+def test_cuba_rank4(cuda, slayer):
+    g = load_golden('neuron_cuba_rank4')
+    _check_neuron(lambda: slayer.neuron.cuba.Neuron(1.25, 0.25, 0.03), g, ['current_decay', 'voltage_decay'],
+                  ['x'], ['current', 'voltage'], 32, cuda, 'cuba')
+
+
+ALIF_P = ['current_decay', 'voltage_decay', 'threshold_decay', 'refractory_decay']
+
+
+def test_alif_shared(cuda, slayer):
+    g = load_golden('neuron_alif_shared')
+    _check_neuron(lambda: slayer.neuron.alif.Neuron(1.0, 0.5, 0.2, 0.05, 0.1, 0.1), g, ALIF_P, ['x'],
+                  ['current', 'voltage', 'threshold', 'refractory'], 40, cuda, 'alif')
+
+
+def test_alif_per_channel(cuda, slayer):
+    g = load_golden('neuron_alif_chan')
+    _check_neuron(lambda: slayer.neuron.alif.Neuron(1.0, 0.5, 0.2, 0.05, 0.1, 0.1, shared_param=False,
+                                                    requires_grad=True), g, ALIF_P, ['x'],
+                  ['current', 'voltage', 'threshold', 'refractory'], 33, cuda, 'alif')
+
+
+def test_rf_shared(cuda, slayer):
+    g = load_golden('neuron_rf_shared')
+    _check_neuron(lambda: slayer.neuron.rf.Neuron(0.5, 10, 0.1, requires_grad=True), g,
+                  ['sin_decay', 'cos_decay'], ['re_in', 'im_in'], ['real', 'imag'], 37, cuda, 'rf')
+
+
+ADRF_P = ['sin_decay', 'cos_decay', 'threshold_decay', 'refractory_decay']
+
+
+def test_adrf_per_channel(cuda, slayer):
+    g = load_golden('neuron_adrf_chan')
+    _check_neuron(lambda: slayer.neuron.adrf.Neuron(0.5, 0.25, [10, 40], 0.1, 0.1, 0.1, shared_param=False,
+                                                    requires_grad=True), g, ADRF_P, ['re_in', 'im_in'],
+                  ['real', 'imag', 'threshold', 'refractory'], 32, cuda, 'adrf')
+
+
+def test_adrf_shared(cuda, slayer):
+    g = load_golden('neuron_adrf_shared')
+    _check_neuron(lambda: slayer.neuron.adrf.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1), g, ADRF_P,
+                  ['re_in', 'im_in'], ['real', 'imag', 'threshold', 'refractory'], 50, cuda, 'adrf')

@@ -1,0 +1,382 @@
+"""CUDA kernels (called through the C ABI via lava_dl_b200._ops) against the CPU
+oracle on seeded random inputs: every op, ragged and tiny shapes, both kernel
+families (TMA-tiled and plain-load), shared and per-channel parameters."""
+
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from _util import (assert_close, assert_exact, assert_quantised_equal, cspike_term_scale, li_scale, pgrad_scale,
+                   res_scale)
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+W = 4096
+
+# (batch, channels, T): tiny, ragged, tile-boundary and TMA-eligible shapes
+SHAPES = [(1, 1, 1), (2, 3, 2), (1, 31, 3), (2, 16, 31), (1, 32, 32), (3, 11, 33), (2, 5, 50), (1, 257, 64),
+          (4, 64, 128), (2, 8, 200), (1, 40, 1000), (2, 33, 36)]
+
+
+@pytest.fixture(scope='module')
+def ops(cuda):
+    from lava_dl_b200 import _ops
+    return _ops
+
+
+def rng_for(*key):
+    return np.random.default_rng(zlib.crc32(repr(key).encode()))
+
+
+def dev(a, cuda, misalign=False):
+    """Upload; with misalign the tensor starts 4 bytes off a 16-byte boundary,
+    which forces the plain-load kernels even when T % 4 == 0."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if not misalign:
+        return torch.tensor(a, device=cuda)
+    buf = torch.empty(a.size + 1, dtype=torch.float32, device=cuda)
+    view = buf[1:].view(a.shape)
+    view.copy_(torch.tensor(a))
+    return view
+
+
+def quant(a):
+    return (np.round(a * W) / W).astype(np.float32)
+
+
+def decays(rng, n, lo=0, hi=4096):
+    return np.round(rng.uniform(lo, hi, size=n)).astype(np.float32)
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+@pytest.mark.parametrize('misalign', [False, True])
+def test_li_fwd_bwd(shape, per_channel, misalign, cuda, ops):
+    rng = rng_for('li', shape, per_channel)
+    B, C, T = shape
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    dec = decays(rng, C if per_channel else 1, 0, 2000)
+    state = quant(rng.normal(0, 0.5, size=shape[:-1]))
+    for thr in (None, 1.25 + 0.01 / W):
+        want = O.li_fwd(x, dec, state, W, thr)
+        got = ops.li_fwd(dev(x, cuda, misalign), dev(dec, cuda), dev(state, cuda), W, thr)
+        assert_quantised_equal(got, want, W, f'li_fwd thr={thr}')
+    go = rng.normal(size=shape).astype(np.float32)
+    gi_want, gd_want = O.li_bwd(go, want, dec)
+    gi, gd = ops.li_bwd(dev(go, cuda, misalign), dev(want, cuda, misalign), dev(dec, cuda), True)
+    assert_close(gi, gi_want, 'li_bwd grad_in', scale=li_scale(go, dec))
+    assert_close(gd, gd_want, 'li_bwd grad_decay', scale=pgrad_scale(dec.size, (gi_want, want)))
+    gi2, none = ops.li_bwd(dev(go, cuda, misalign), None, dev(dec, cuda), False)
+    assert none is None
+    assert_exact(gi2, gi, 'li_bwd with and without decay gradient')
+
+
+def test_li_final_state_and_nonpow2_scale(cuda, ops):
+    rng = rng_for('li_final')
+    shape = (2, 7, 45)
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    for w in (W, 1000, 3):
+        want = O.li_fwd(x, np.array([321.0]), np.array([0.25]), w, 0.9)
+        got, fin = ops.li_fwd(dev(x, cuda), dev([321.0], cuda), dev([0.25], cuda), w, 0.9, want_final=True)
+        assert_exact(got, want, f'li_fwd w_scale={w}')
+        assert_exact(fin, want[..., -1], 'final state')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+def test_ath_apth(shape, per_channel, cuda, ops):
+    rng = rng_for('ath', shape, per_channel)
+    B, C, T = shape
+    n = C if per_channel else 1
+    x = rng.normal(0.5, 1.5, size=shape).astype(np.float32)
+    rd, td = decays(rng, n, 0, 1000), decays(rng, n, 0, 1000)
+    rs = quant(rng.uniform(-0.25, 0.75, size=shape[:-1]))
+    ts = quant(rng.uniform(0.5, 1.5, size=shape[:-1]))
+    th_w, ref_w = O.ath_fwd(x, rs, rd, ts, td, 0.5, 1.0, W)
+    th, ref = ops.ath_fwd(dev(x, cuda), dev(rs, cuda), dev(rd, cuda), dev(ts, cuda), dev(td, cuda), 0.5, 1.0, W)
+    assert_quantised_equal(th, th_w, W, 'ath threshold')
+    assert_quantised_equal(ref, ref_w, W, 'ath refractory')
+
+    re = rng.normal(0, 1.5, size=shape).astype(np.float32)
+    im = rng.normal(0, 1.5, size=shape).astype(np.float32)
+    ims = rng.normal(size=shape[:-1]).astype(np.float32)
+    th_w, ref_w = O.apth_fwd(re, im, ims, rs, rd, ts, td, 0.25, 0.5, W)
+    th, ref = ops.apth_fwd(dev(re, cuda), dev(im, cuda), dev(ims, cuda), dev(rs, cuda), dev(rd, cuda),
+                           dev(ts, cuda), dev(td, cuda), 0.25, 0.5, W)
+    assert_quantised_equal(th, th_w, W, 'apth threshold')
+    assert_quantised_equal(ref, ref_w, W, 'apth refractory')
+
+
+def sincos(rng, n):
+    p = rng.uniform(3.0, 40.0, size=n)
+    d = rng.uniform(0.02, 0.3, size=n)
+    return (np.round(4096 * np.sin(2 * np.pi / p) * (1 - d)).astype(np.float32),
+            np.round(4096 * np.cos(2 * np.pi / p) * (1 - d)).astype(np.float32))
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+@pytest.mark.parametrize('misalign', [False, True])
+def test_resonator(shape, per_channel, misalign, cuda, ops):
+    rng = rng_for('res', shape, per_channel)
+    B, C, T = shape
+    sd, cd = sincos(rng, C if per_channel else 1)
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    rs, ims = quant(rng.normal(0, 0.3, size=shape[:-1])), quant(rng.normal(0, 0.3, size=shape[:-1]))
+    for thr in (None, 0.75, 0.0):
+        re_w, im_w = O.res_fwd(re_in, im_in, sd, cd, rs, ims, W, thr)
+        re, im = ops.res_fwd(dev(re_in, cuda, misalign), dev(im_in, cuda, misalign), dev(sd, cuda), dev(cd, cuda),
+                             dev(rs, cuda), dev(ims, cuda), W, thr)
+        assert_quantised_equal(re, re_w, W, f'res real thr={thr}')
+        assert_quantised_equal(im, im_w, W, f'res imag thr={thr}')
+    g_re = rng.normal(size=shape).astype(np.float32)
+    g_im = rng.normal(size=shape).astype(np.float32)
+    a_w, b_w, gs_w, gc_w = O.res_bwd(g_re, g_im, re_w, im_w, sd, cd)
+    a, b, gs, gc = ops.res_bwd(dev(g_re, cuda, misalign), dev(g_im, cuda, misalign), dev(re_w, cuda, misalign),
+                               dev(im_w, cuda, misalign), dev(sd, cuda), dev(cd, cuda), True)
+    S_re, S_im = res_scale(g_re, g_im, sd, cd)
+    S_p = pgrad_scale(sd.size, (a_w, re_w), (a_w, im_w), (b_w, re_w), (b_w, im_w))
+    assert_close(a, a_w, 'res_bwd grad_re', scale=S_re)
+    assert_close(b, b_w, 'res_bwd grad_im', scale=S_im)
+    assert_close(gs, gs_w, 'res_bwd grad_sin', scale=S_p)
+    assert_close(gc, gc_w, 'res_bwd grad_cos', scale=S_p)
+    a2, b2, _, _ = ops.res_bwd(dev(g_re, cuda), dev(g_im, cuda), None, None, dev(sd, cuda), dev(cd, cuda), False)
+    assert_exact(a2, a, 'res_bwd with and without parameter gradient')
+    assert_exact(b2, b, 'res_bwd with and without parameter gradient')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+def test_adaptive_resonator(shape, per_channel, cuda, ops):
+    rng = rng_for('adres', shape, per_channel)
+    B, C, T = shape
+    n = C if per_channel else 1
+    sd, cd = sincos(rng, n)
+    rd, td = decays(rng, n, 0, 1000), decays(rng, n, 0, 1000)
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    st = [quant(rng.normal(0, 0.3, size=shape[:-1])) for _ in range(2)]
+    refs = quant(rng.uniform(-0.25, 0.75, size=shape[:-1]))
+    ths = quant(rng.uniform(0.25, 1.0, size=shape[:-1]))
+    want = O.adres_fwd(re_in, im_in, sd, cd, rd, td, st[0], st[1], refs, ths, 0.25, 0.5, W)
+    got = ops.adres_fwd(dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cd, cuda), dev(rd, cuda),
+                        dev(td, cuda), dev(st[0], cuda), dev(st[1], cuda), dev(refs, cuda), dev(ths, cuda), 0.25,
+                        0.5, W)
+    for g, w_, k in zip(got, want, ('real', 'imag', 'threshold', 'refractory')):
+        assert_quantised_equal(g, w_, W, f'adres {k}')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('graded', [False, True])
+@pytest.mark.parametrize('tensor_thr', [False, True])
+def test_spike_functions(shape, graded, tensor_thr, cuda, ops):
+    rng = rng_for('spike', shape, graded, tensor_thr)
+    v = quant(rng.normal(0.8, 1.0, size=shape))
+    thr = rng.uniform(0.8, 1.4, size=shape).astype(np.float32) if tensor_thr else 1.25 + 0.01 / W
+    thr_d = dev(thr, cuda) if tensor_thr else thr
+    gs = rng.normal(size=shape).astype(np.float32)
+    assert_exact(ops.spike_fwd(dev(v, cuda), thr_d, graded, 1), O.spike_fwd(v, thr, graded, 1), 'spike')
+    assert_close(ops.spike_bwd(dev(v, cuda), thr_d, dev(gs, cuda), 125.0, 0.1, graded),
+                 O.spike_bwd(v, thr, gs, 125.0, 0.1, graded), 'spike grad')
+
+    re, im = quant(rng.normal(size=shape)), quant(rng.normal(size=shape))
+    last = rng.normal(size=shape[:-1]).astype(np.float32)
+    cthr = rng.uniform(0.2, 0.7, size=shape).astype(np.float32) if tensor_thr else 0.5
+    cthr_d = dev(cthr, cuda) if tensor_thr else cthr
+    assert_exact(ops.cspike_fwd(dev(re, cuda), dev(im, cuda), cthr_d, dev(last, cuda), graded, 1),
+                 O.cspike_fwd(re, im, cthr, last, graded, 1), 'complex spike')
+    gre, gim = ops.cspike_bwd(dev(re, cuda), dev(im, cuda), cthr_d, dev(gs, cuda), 0.25, 10.0, graded)
+    gre_w, gim_w = O.cspike_bwd(re, im, cthr, gs, 0.25, 10.0, graded)
+    t_re, t_im = cspike_term_scale(re, im, cthr, gs, 0.25, 10.0, graded)
+    assert_close(gre, gre_w, 'complex spike grad_re', scale=t_re)
+    assert_close(gim, gim_w, 'complex spike grad_im', scale=t_im)
+
+
+@pytest.mark.parametrize('shape', SHAPES + [(2, 3, 4, 40)])
+def test_shift(shape, cuda, ops):
+    rng = rng_for('shift', shape)
+    x = rng.uniform(size=shape).astype(np.float32)
+    T = shape[-1]
+    for sv in (0, 1, -1, 7, -7, T - 1, T, T + 5, -(T + 5)):
+        assert_exact(ops.shift(dev(x, cuda), sv), O.shift(x, sv), f'shift {sv}')
+    assert_exact(ops.shift(dev(x, cuda), 9, 2.0), O.shift(x, 9, 2.0), 'shift 9 at Ts=2')
+    if len(shape) >= 3 and int(np.prod(shape[1:-1])) > 1:
+        lut = rng.integers(-T - 2, T + 3, size=shape[1:-1]).astype(np.float32) + 0.4
+        assert_exact(ops.shift(dev(x, cuda), dev(lut, cuda)), O.shift(x, lut), 'per-neuron shift')
+        assert_exact(ops.shift(dev(x, cuda), dev(lut, cuda), 2.0), O.shift(x, lut, 2.0), 'per-neuron shift Ts=2')
+
+
+@pytest.mark.parametrize('shape', SHAPES + [(2, 3, 1100), (1, 2, 2050)])
+@pytest.mark.parametrize('K', [1, 2, 16, 50, 64, 100])
+def test_fir(shape, K, cuda, ops):
+    rng = rng_for('fir', shape, K)
+    x = rng.uniform(size=shape).astype(np.float32)
+    f = (np.exp(-np.arange(K) / 8) / 8 * (1 + 0.1 * rng.normal(size=K))).astype(np.float32)
+    for corr in (False, True):
+        for ts in (1.0, 2.0):
+            assert_close(ops.fir(dev(x, cuda), dev(f, cuda), ts, corr), O.fir(x, f, ts, corr), f'fir corr={corr}')
+
+
+@pytest.mark.parametrize('shape', [(2, 5, 50), (3, 16, 200), (2, 4, 1100), (1, 7, 1000)])
+def test_fused_delay_filter(shape, cuda, ops):
+    rng = rng_for('shift_fir', shape)
+    T = shape[-1]
+    x = (rng.uniform(size=shape) < 0.2).astype(np.float32)
+    g = rng.normal(size=shape).astype(np.float32)
+    f = (np.exp(-np.arange(64) / 8) / 8).astype(np.float32)
+    lut = rng.integers(0, 63, size=shape[1:-1]).astype(np.float32)
+    for sv, sv_d in ((lut, dev(lut, cuda)), (5, 5), (-3, -3)):
+        want = O.conv(O.shift(x, sv), f)
+        assert_close(ops.shift_fir(dev(x, cuda), sv_d, 1, dev(f, cuda), 1.0, backward=False), want, 'conv(shift(x))')
+        neg = -sv
+        want_b = O.shift(O.corr(g, f), neg)
+        assert_close(ops.shift_fir(dev(g, cuda), sv_d, 1, dev(f, cuda), 1.0, backward=True), want_b,
+                     'shift(corr(g), -d)')
+
+
+# --------------------------------------------------------------------------
+# fused neuron passes against the oracle's un-fused call sequences
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+@pytest.mark.parametrize('misalign', [False, True])
+def test_cuba_fused(shape, per_channel, misalign, cuda, ops):
+    rng = rng_for('cuba', shape, per_channel)
+    B, C, T = shape
+    n = C if per_channel else 1
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, n, 800, 1300), decays(rng, n, 50, 300)
+    cs, vs = quant(rng.normal(0, 0.5, size=shape[:-1])), quant(rng.normal(0, 0.5, size=shape[:-1]))
+    gs = rng.normal(size=shape).astype(np.float32)
+    for graded in (False, True):
+        want = O.cuba(x, 1.25, cd, vd, cstate=cs, vstate=vs, grad_spike=gs, graded=graded)
+        r = ops.cuba_fwd(dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), dev(cs, cuda), dev(vs, cuda),
+                         1.25 + 0.01 / W, W, want_current=True, want_spike=True, graded=graded)
+        assert_quantised_equal(r['current'], want['current'], W, 'current')
+        assert_quantised_equal(r['voltage'], want['voltage'], W, 'voltage')
+        assert_exact(r['spike'], want['spike'], 'spike')
+        assert_exact(r['final_c'], want['current'][..., -1], 'final current')
+        assert_exact(r['final_v'], want['voltage'][..., -1], 'final voltage')
+        assert_exact(r['final_s'], want['spike'][..., -1], 'final spike')
+        r2 = ops.cuba_fwd(dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), dev(cs, cuda), dev(vs, cuda),
+                          1.25 + 0.01 / W, W, want_current=False, want_spike=True, graded=graded)
+        assert_exact(r2['spike'], want['spike'], 'spike (no current output)')
+        assert_exact(r2['voltage'], r['voltage'], 'voltage (no current output)')
+        gx, gcd, gvd = ops.cuba_bwd(dev(gs, cuda, misalign), r['voltage'], 1.25 + 0.01 / W, r['current'],
+                                    dev(cd, cuda), dev(vd, cuda), 125.0, 0.1, graded, True)
+        g_v = O.spike_bwd(want['voltage'], 1.25 + 0.01 / W, gs, 125.0, 0.1, graded)
+        S_c = li_scale(g_v, vd)
+        g_c, _ = O.li_bwd(g_v, want['voltage'], vd)
+        assert_close(gx, want['grad_x'], 'grad_x', scale=li_scale(S_c, cd))
+        assert_close(gcd, want['grad_current_decay'], 'grad current decay',
+                     scale=pgrad_scale(cd.size, (want['grad_x'], want['current'])))
+        assert_close(gvd, want['grad_voltage_decay'], 'grad voltage decay',
+                     scale=pgrad_scale(vd.size, (g_c, want['voltage'])))
+        gx2, _, _ = ops.cuba_bwd(dev(gs, cuda, misalign), r['voltage'], 1.25 + 0.01 / W, None, dev(cd, cuda),
+                                 dev(vd, cuda), 125.0, 0.1, graded, False)
+        assert_exact(gx2, gx, 'grad_x with and without decay gradients')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+def test_alif_fused(shape, per_channel, cuda, ops):
+    rng = rng_for('alif', shape, per_channel)
+    B, C, T = shape
+    n = C if per_channel else 1
+    x = rng.normal(0.2, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, n, 700, 900), decays(rng, n, 150, 250)
+    td, rd = decays(rng, n, 300, 500), decays(rng, n, 300, 500)
+    st = [quant(rng.normal(0, 0.5, size=shape[:-1])) for _ in range(2)]
+    ths = quant(rng.uniform(0.8, 1.5, size=shape[:-1]))
+    refs = quant(rng.uniform(0.0, 0.5, size=shape[:-1]))
+    gs = rng.normal(size=shape).astype(np.float32)
+    want = O.alif(x, 1.0, 0.5, cd, vd, td, rd, cstate=st[0], vstate=st[1], th_state=ths, ref_state=refs,
+                  grad_spike=gs)
+    args = (dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(rd, cuda), dev(td, cuda), dev(st[0], cuda),
+            dev(st[1], cuda), dev(refs, cuda), dev(ths, cuda), 0.5, 1.0, W)
+    outs, fin = ops.alif_fwd(*args, dynamics_mode=True)
+    for o, k in zip(outs, ('current', 'voltage', 'threshold', 'refractory')):
+        assert_quantised_equal(o, want[k], W, k)
+    (spike, voltage, thsum), fin = ops.alif_fwd(*args, dynamics_mode=False)
+    assert_exact(spike, want['spike'], 'spike')
+    assert_exact(thsum, want['threshold'] + want['refractory'], 'threshold + refractory')
+    assert_exact(fin['final_th'], want['threshold'][..., -1], 'final threshold')
+    assert_exact(fin['final_ref'], want['refractory'][..., -1], 'final refractory')
+    assert_exact(fin['final_s'], want['spike'][..., -1], 'final spike')
+    gx, _, _ = ops.cuba_bwd(dev(gs, cuda), voltage, thsum, None, dev(cd, cuda), dev(vd, cuda), 100.0, 0.1, False,
+                            False)
+    g_v = O.spike_bwd(want['voltage'], want['threshold'] + want['refractory'], gs, 100.0, 0.1, False)
+    assert_close(gx, want['grad_x'], 'grad_x', scale=li_scale(li_scale(g_v, vd), cd))
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+@pytest.mark.parametrize('adaptive', [False, True])
+def test_rf_fused(shape, per_channel, adaptive, cuda, ops):
+    rng = rng_for('rf', shape, per_channel, adaptive)
+    B, C, T = shape
+    n = C if per_channel else 1
+    sd, cd = sincos(rng, n)
+    td, rd = decays(rng, n, 300, 500), decays(rng, n, 300, 500)
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    rs, ims = quant(rng.normal(0, 0.3, size=shape[:-1])), quant(rng.normal(0, 0.3, size=shape[:-1]))
+    ths = quant(rng.uniform(0.3, 0.8, size=shape[:-1]))
+    refs = quant(rng.uniform(0.0, 0.3, size=shape[:-1]))
+    gs = rng.normal(size=shape).astype(np.float32)
+    for graded in (False, True):
+        if adaptive:
+            want = O.adrf(re_in, im_in, 0.5, 0.25, sd, cd, td, rd, re_state=rs, im_state=ims, th_state=ths,
+                          ref_state=refs, grad_spike=gs, graded=graded)
+            ad = dict(ref_decay=dev(rd, cuda), th_decay=dev(td, cuda), ref_state=dev(refs, cuda),
+                      th_state=dev(ths, cuda), th_step=0.25, th0=0.5)
+            tau, srho = 50.0, 0.1
+        else:
+            want = O.rf(re_in, im_in, 0.5, sd, cd, re_state=rs, im_state=ims, grad_spike=gs, graded=graded)
+            ad = None
+            tau, srho = 0.25, 10.0
+        outs, fin = ops.rf_fwd(dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cd, cuda), dev(rs, cuda),
+                               dev(ims, cuda), 0.5, W, graded=graded, adaptive=ad)
+        assert_exact(outs[0], want['spike'], 'spike')
+        assert_quantised_equal(outs[1], want['real'], W, 'real')
+        assert_quantised_equal(outs[2], want['imag'], W, 'imag')
+        assert_exact(fin['final_s'], want['spike'][..., -1], 'final spike')
+        thr = 0.5
+        if adaptive:
+            assert_exact(outs[3], want['threshold'] + want['refractory'], 'threshold + refractory')
+            thr = outs[3]
+            dyn, _ = ops.rf_fwd(dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cd, cuda), dev(rs, cuda),
+                                dev(ims, cuda), 0.5, W, adaptive=ad, dynamics_mode=True)
+            for o, k in zip(dyn, ('real', 'imag', 'threshold', 'refractory')):
+                assert_quantised_equal(o, want[k], W, k)
+        gre, gim, gsn, gcs = ops.rf_bwd(dev(gs, cuda), outs[1], outs[2], thr, dev(sd, cuda), dev(cd, cuda), tau,
+                                        srho, graded, True)
+        thr_np = (want['threshold'] + want['refractory']) if adaptive else 0.5
+        s_re, s_im = cspike_term_scale(want['real'], want['imag'], thr_np, gs, tau, srho, graded)
+        S_re, S_im = res_scale(s_re, s_im, sd, cd)
+        S_p = pgrad_scale(sd.size, (want['grad_re'], want['real']), (want['grad_re'], want['imag']),
+                          (want['grad_im'], want['real']), (want['grad_im'], want['imag']))
+        assert_close(gre, want['grad_re'], 'grad_re', scale=S_re)
+        assert_close(gim, want['grad_im'], 'grad_im', scale=S_im)
+        assert_close(gsn, want['grad_sin_decay'], 'grad_sin', scale=S_p)
+        assert_close(gcs, want['grad_cos_decay'], 'grad_cos', scale=S_p)
+
+
+def test_empty_inputs(cuda, ops):
+    for shape in ((0, 4, 16), (2, 4, 0)):
+        x = torch.empty(shape, device=cuda)
+        st = torch.zeros(shape[:-1], device=cuda)
+        d = torch.tensor([100.0], device=cuda)
+        assert ops.li_fwd(x, d, st, W).shape == x.shape
+        assert ops.shift(x, 3).shape == x.shape
+        assert ops.fir(x, torch.ones(4, device=cuda), 1.0, False).shape == x.shape
+        assert ops.spike_fwd(x, 1.0, False, 1).shape == x.shape
+
+
+def test_device_status_clean(cuda):
+    from lava_dl_b200 import _native
+    assert _native.device_status() == 0
