@@ -84,17 +84,41 @@ bool tma_eligible(const void* const* ptrs, int n, int64_t T) {
 }
 
 // The encode call is a driver-API function and wants a context current on the
-// calling thread.  Threads that have only been handed a device by the runtime
-// (an autograd worker after cudaSetDevice, say) may not have bound the primary
-// context yet; a no-op runtime call does that.
+// calling thread.  A thread that was only handed a device number (an autograd
+// worker, say) may have none bound yet.  The primary context of the device is
+// retained once per device and made current on such threads; nothing is
+// allocated or freed.
+typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+typedef CUresult (*CtxSetCurrentFn)(CUcontext);
+typedef CUresult (*PrimaryRetainFn)(CUcontext*, CUdevice);
+typedef CUresult (*DeviceGetFn)(CUdevice*, int);
+
+static void* driver_fn(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  return p;
+}
+
 static void bind_primary_context() {
-  static thread_local int bound_dev = -1;
+  static CtxGetCurrentFn get_cur = (CtxGetCurrentFn)driver_fn("cuCtxGetCurrent");
+  static CtxSetCurrentFn set_cur = (CtxSetCurrentFn)driver_fn("cuCtxSetCurrent");
+  static PrimaryRetainFn retain = (PrimaryRetainFn)driver_fn("cuDevicePrimaryCtxRetain");
+  static DeviceGetFn dev_get = (DeviceGetFn)driver_fn("cuDeviceGet");
+  static CUcontext primary[kMaxDev] = {nullptr};
+  if (!get_cur || !set_cur || !retain || !dev_get) return;
+  CUcontext cur = nullptr;
+  if (get_cur(&cur) == CUDA_SUCCESS && cur != nullptr) return;
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return;
-  if (dev != bound_dev) {
-    cudaFree(nullptr);
-    bound_dev = dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return;
+  if (!primary[dev]) {
+    CUdevice cd;
+    CUcontext ctx = nullptr;
+    if (dev_get(&cd, dev) != CUDA_SUCCESS || retain(&ctx, cd) != CUDA_SUCCESS) return;
+    primary[dev] = ctx;
   }
+  set_cur(primary[dev]);
 }
 
 int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T) {
