@@ -80,6 +80,21 @@ int sb_li_fwd(const float* x, const float* decay, int64_t n_decay, const float* 
 int sb_li_bwd(const float* grad_y, const float* y, const float* decay, int64_t n_decay, float* grad_x,
               float* grad_decay, void* scratch, const sb_geom* g, void* stream);
 
+/* No counterpart in the reference.  Same computation as sb_li_bwd with
+ * grad_decay, for callers that cannot provide scratch memory because they
+ * cannot allocate (ahead-of-time planned runtimes that give a custom op only
+ * its inputs and outputs, processes whose pool already owns the whole GPU,
+ * latency-bound loops that cannot take the device sync of an allocation).
+ * The scratch is a SB_NOALLOC_SCRATCH_BYTES array inside the library, resident
+ * on every GPU that loads it.  Limits: shared decay up to 32 * (capacity/8 - 64)
+ * rows; per-channel decay rows + 64 * n_decay <= capacity/8.  Larger problems
+ * return SB_ERR_INVALID_ARG.  The first call on a device looks the array up
+ * (do it outside stream capture).  Calls share the array: calls overlapping on
+ * the GPU race.  Allocates nothing. */
+#define SB_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+int sb_li_bwd_noalloc(const float* grad_y, const float* y, const float* decay, int64_t n_decay, float* grad_x,
+                      float* grad_decay, const sb_geom* g, void* stream);
+
 /* ---- adaptive threshold ----------------------------------------------------
  * Replaces adaptive_threshold.cu:81-129 / adaptive_threshold.py:237-274.
  * th_step = int(th_scale * w_scale), th0 = int(th0 * w_scale) (host ints). */

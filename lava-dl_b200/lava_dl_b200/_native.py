@@ -37,6 +37,7 @@ SIGNATURES = {
     'sb_uses_tma': (c_int, [_P, _I64]),
     'sb_li_fwd': (c_int, [_P, _P, _I64, _P, _P, _P, _G, c_float, c_int, _P]),
     'sb_li_bwd': (c_int, [_P, _P, _P, _I64, _P, _P, _P, _G, _P]),
+    'sb_li_bwd_noalloc': (c_int, [_P, _P, _P, _I64, _P, _P, _G, _P]),
     'sb_ath_fwd': (c_int, [_P, _P, _P, _I64, _P, _P, _I64, _P, _P, _G, c_int, c_int, c_int, _P]),
     'sb_apth_fwd': (c_int, [_P, _P, _P, _P, _P, _I64, _P, _P, _I64, _P, _P, _G, c_int, c_int, c_int, _P]),
     'sb_res_fwd': (c_int, [_P, _P, _P, _P, _I64, _P, _P, _P, _P, _G, c_int, c_float, c_int, c_int, _P]),
