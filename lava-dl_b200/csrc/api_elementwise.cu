@@ -139,6 +139,47 @@ __global__ void shift_kernel(const float* __restrict__ x, const float* __restric
   }
 }
 
+// Vector form for T % 4 == 0 and 16-byte aligned tensors: a thread writes two
+// aligned float4; the source window starts (t - d), in general not aligned, so
+// it is assembled from the aligned float4 words that cover it (neighbouring
+// threads read overlapping words: L1 serves the second touch).
+constexpr int kShiftVecPerThread = 2;
+
+__device__ __forceinline__ float4 ld4_or_zero(const float4* p, int q, int nq) {
+  return (q >= 0 && q < nq) ? __ldg(p + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__global__ void __launch_bounds__(128)
+shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ lut, int64_t n_lut, float shift, float ts,
+                 float* __restrict__ out, int64_t rows, int T) {
+  const int nq = T >> 2;  // float4 words per row
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
+    int d = __float2int_rz(__fdiv_rn(sv, ts));
+    d = max(-T - 8, min(T + 8, d));  // beyond +-T everything is zero anyway; keeps the arithmetic below in range
+    const float4* src = reinterpret_cast<const float4*>(x + row * (int64_t)T);
+    float4* dst = reinterpret_cast<float4*>(out + row * (int64_t)T);
+    // source element index of output element 4*q is 4*q - d = 4*(q - dq) + r, 0 <= r < 4
+    const int dq = (d + 3) >> 2;             // ceil(d / 4) for either sign (arithmetic shift floors)
+    const int r = (dq << 2) - d;             // 0..3
+#pragma unroll
+    for (int k = 0; k < kShiftVecPerThread; ++k) {
+      const int q = (blockIdx.x * kShiftVecPerThread + k) * blockDim.x + threadIdx.x;
+      if (q >= nq) break;
+      const int s0 = q - dq;
+      const float4 a = ld4_or_zero(src, s0, nq);
+      float4 o = a;
+      if (r != 0) {
+        const float4 b = ld4_or_zero(src, s0 + 1, nq);
+        if (r == 1) o = make_float4(a.y, a.z, a.w, b.x);
+        else if (r == 2) o = make_float4(a.z, a.w, b.x, b.y);
+        else o = make_float4(a.w, b.x, b.y, b.z);
+      }
+      dst[q] = o;
+    }
+  }
+}
+
 Surrogate surrogate_consts(float tau_rho, float scale_rho, bool graded) {
   Surrogate s;
   s.tau = tau_rho;
@@ -257,6 +298,14 @@ int sb_shift(const float* x, const float* lut, int64_t n_lut, float shift, float
                       (long long)rows);
   cudaStream_t st = (cudaStream_t)stream;
   const int threads = 128;
+  if ((T & 3) == 0 && aligned16(x) && aligned16(out)) {
+    const int per_block = threads * kShiftVecPerThread;
+    const unsigned gx = (unsigned)(((T >> 2) + per_block - 1) / per_block);
+    const unsigned gy = (unsigned)(rows < 65535 ? rows : 65535);
+    shift_vec_kernel<<<dim3(gx, gy), threads, 0, st>>>(x, lut, n_lut, shift, sampling_time, out, rows, (int)T);
+    SB_CUDA(cudaGetLastError());
+    return SB_OK;
+  }
   shift_kernel<<<row_grid(rows, T, threads), threads, 0, st>>>(x, lut, n_lut, shift, sampling_time, out, rows, (int)T);
   SB_CUDA(cudaGetLastError());
   return SB_OK;

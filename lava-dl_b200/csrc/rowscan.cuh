@@ -88,12 +88,14 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // ---------------------------------------------------------------------------
 // TMA-pipelined kernel
 // ---------------------------------------------------------------------------
-template <class Op, int STAGES>
+template <class Op, int STAGES, int NB>
 __global__ void __launch_bounds__(128)
 rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
                    const typename Op::Params p, const RowGeom g, unsigned int* status) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
-  constexpr int kWarpBytes = STAGES * NT * kTileBytes;
+  constexpr int kStageBytes = NT * NB * kTileBytes;  // NB boxes of 32 steps, side by side in time
+  constexpr int kSpan = NB * kTileT;                 // time steps per stage
+  constexpr int kWarpBytes = STAGES * kStageBytes;
   extern __shared__ uint8_t smem_raw[];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -113,17 +115,23 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
   __syncwarp();
 
   const int T = g.T;
-  const int ntiles = (T + kTileT - 1) / kTileT;
+  const int ntiles = (T + kSpan - 1) / kSpan;
   const int y = (int)row0;
 
-  auto tile_t0 = [&](int k) { return (Op::REVERSE ? (ntiles - 1 - k) : k) * kTileT; };
+  auto tile_t0 = [&](int k) { return (Op::REVERSE ? (ntiles - 1 - k) : k) * kSpan; };
   auto issue_load = [&](int k) {  // lane 0 only
     const int s = k % STAGES;
     const uint32_t bar = bar0 + s * 8;
-    mbar_expect_tx(bar, NIN * kTileBytes);
+    const int t0 = tile_t0(k);
+    int nb = (T - t0 + kTileT - 1) / kTileT;  // boxes that start inside the tensor
+    nb = nb > NB ? NB : nb;
+    mbar_expect_tx(bar, NIN * nb * kTileBytes);
+    for (int b = 0; b < nb; ++b) {
 #pragma unroll
-    for (int i = 0; i < NIN; ++i)
-      tma_load_2d(smem_u32(wsm + (s * NT + i) * kTileBytes), &maps.m[i], tile_t0(k), y, bar);
+      for (int i = 0; i < NIN; ++i)
+        tma_load_2d(smem_u32(wsm + s * kStageBytes + (b * NT + i) * kTileBytes), &maps.m[i], t0 + b * kTileT, y,
+                    bar);
+    }
   };
 
   Op op;
@@ -141,18 +149,27 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
   for (; k < ntiles; ++k) {
     const int s = k % STAGES;
     if (!mbar_wait(bar0 + s * 8, (k / STAGES) & 1)) { ok = false; break; }
-    uint8_t* stage = wsm + s * NT * kTileBytes;
+    uint8_t* stage = wsm + s * kStageBytes;
     const int t0 = tile_t0(k);
-    const int nvalid = T - t0;
-    if (nvalid >= kTileT) process_tile<Op, true>(op, stage, lane, kTileT);
-    else process_tile<Op, false>(op, stage, lane, nvalid);
-    op.tile_end();
+#pragma unroll
+    for (int bb = 0; bb < NB; ++bb) {
+      const int b = Op::REVERSE ? NB - 1 - bb : bb;
+      const int nvalid = T - (t0 + b * kTileT);
+      if (nvalid <= 0) continue;
+      uint8_t* box = stage + b * NT * kTileBytes;
+      if (nvalid >= kTileT) process_tile<Op, true>(op, box, lane, kTileT);
+      else process_tile<Op, false>(op, box, lane, nvalid);
+      op.tile_end();
+    }
     fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
+      for (int b = 0; b < NB; ++b) {
+        if (t0 + b * kTileT >= T) break;
 #pragma unroll
-      for (int o = 0; o < NOUT; ++o)
-        tma_store_2d(&maps.m[NIN + o], t0, y, smem_u32(stage + o * kTileBytes));
+        for (int o = 0; o < NOUT; ++o)
+          tma_store_2d(&maps.m[NIN + o], t0 + b * kTileT, y, smem_u32(stage + (b * NT + o) * kTileBytes));
+      }
       tma_commit();
       const int kn = k + STAGES - 1;
       if (kn < ntiles) {
@@ -247,7 +264,21 @@ struct LaunchPlan {
 LaunchPlan plan_rowscan(int64_t rows, size_t bytes_per_warp, size_t fixed_bytes);
 int prepare_kernel(const void* fn, size_t smem);
 
-template <class Op, int STAGES = 3>
+// Pipeline shape of the TMA kernels: stages per warp and 32-step boxes per stage.
+// Shared memory per warp is STAGES * max(NIN, NOUT) * boxes * 4 KB and decides
+// how many warps an SM holds.  Measured on B200 (fraction of copy bandwidth):
+// single-stream ops gain from 256-byte row segments (two boxes: 0.80 -> 0.87),
+// multi-stream ops lose more from the halved occupancy than they gain.
+#ifndef SB_STAGES
+#define SB_STAGES 3
+#endif
+#ifdef SB_BOXES
+constexpr int default_boxes(int) { return SB_BOXES; }
+#else
+constexpr int default_boxes(int streams) { return streams == 1 ? 2 : 1; }
+#endif
+
+template <class Op, int STAGES = SB_STAGES, int NB = default_boxes(cmax(Op::NIN, Op::NOUT))>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
                    cudaStream_t st) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
@@ -267,9 +298,9 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
       int rc = make_row_map(&maps.m[i], all[i], g.rows, g.T);
       if (rc != SB_OK) return rc;
     }
-    const size_t per_warp = (size_t)STAGES * NT * kTileBytes + STAGES * 8;
+    const size_t per_warp = (size_t)STAGES * NT * NB * kTileBytes + STAGES * 8;
     const LaunchPlan lp = plan_rowscan(g.rows, per_warp, 1024);
-    auto fn = rowscan_tma_kernel<Op, STAGES>;
+    auto fn = rowscan_tma_kernel<Op, STAGES, NB>;
     int rc = prepare_kernel((const void*)fn, lp.smem);
     if (rc != SB_OK) return rc;
     fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(maps, p, g, status);

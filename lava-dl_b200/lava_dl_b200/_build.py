@@ -57,22 +57,25 @@ def is_stale():
     return any(os.path.getmtime(d) > built for d in _deps())
 
 
-def build(force=False, verbose=False, ptxas_verbose=False):
+def build(force=False, verbose=False, ptxas_verbose=False, defines=(), out=None):
     """Compile every ``.cu`` under ``csrc/`` and link the shared library.
 
-    Returns the path of the library.  Raises ``RuntimeError`` with the compiler
-    output on failure.
+    ``defines`` adds ``-D`` macros (pipeline-shape experiments), ``out`` writes
+    the library somewhere else than the in-tree default.  Returns the path of
+    the library.  Raises ``RuntimeError`` with the compiler output on failure.
     """
-    if not force and not is_stale():
+    lib_path = out or LIB_PATH
+    obj_dir = OBJ_DIR if out is None else os.path.join(os.path.dirname(out), 'obj_' + os.path.basename(out))
+    if out is None and not force and not is_stale():
         return LIB_PATH
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
-    flags = list(NVCC_FLAGS)
+    flags = list(NVCC_FLAGS) + [f'-D{d}' for d in defines]
     if ptxas_verbose:
         flags += ['-Xptxas', '-v']
 
     def compile_one(src):
-        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + '.o')
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + '.o')
         cmd = [nvcc] + flags + ['-I', INCLUDE_DIR, '-c', src, '-o', obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, obj, r
@@ -85,11 +88,11 @@ def build(force=False, verbose=False, ptxas_verbose=False):
             if r.returncode != 0:
                 raise RuntimeError(f'nvcc failed on {src}:\n{r.stdout}\n{r.stderr}')
             objs.append(obj)
-    cmd = [nvcc, '-shared', '-o', LIB_PATH] + objs + ['-cudart', 'static']
+    cmd = [nvcc, '-shared', '-o', lib_path] + objs + ['-cudart', 'static']
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f'link failed:\n{r.stdout}\n{r.stderr}')
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == '__main__':

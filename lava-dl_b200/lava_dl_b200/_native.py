@@ -69,7 +69,7 @@ SIGNATURES = {
 
 
 def lib_path():
-    return _build.LIB_PATH
+    return os.environ.get('SLAYER_B200_LIB') or _build.LIB_PATH
 
 
 def load():
@@ -77,8 +77,10 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB_PATH
+    path = os.environ.get('SLAYER_B200_LIB') or _build.LIB_PATH  # the variable points at an alternative build
     if not os.path.exists(path):
+        if path != _build.LIB_PATH:
+            raise RuntimeError(f'SLAYER_B200_LIB points at {path}, which does not exist')
         _build.build()
     try:
         lib = ctypes.CDLL(path)
