@@ -404,6 +404,39 @@ def e2e_cuba(shape, device, steps, warmup):
     return {'ms': ms, 'h2d': nbytes, 'd2h': nbytes, 'launches': nchunks, 'rate': float(s_host.mean())}
 
 
+def fwd_bwd_cuba(shape, device, steps, warmup, world):
+    """Training step through the public API: spikes, sum-of-spikes loss, backward
+    with learnable decays, and (N > 1) one NCCL all-reduce of the decay gradients."""
+    import lava_dl_b200.slayer as slayer
+    from lava_dl_b200 import _dist
+    gen = torch.Generator(device=device).manual_seed(4321)
+    x = torch.empty(shape, device=device).normal_(0.3, 1.0, generator=gen).requires_grad_(True)
+    neuron = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03,
+                                       requires_grad=True).to(device)
+    params = list(neuron.parameters())
+
+    def one_step():
+        x.grad = None
+        for p in params:
+            p.grad = None
+        neuron(x).sum().backward()
+        return _dist.allreduce_param_grads(params)
+
+    for _ in range(max(1, warmup)):
+        n_reduced = one_step()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        one_step()
+    t1.record()
+    torch.cuda.synchronize(device)
+    return t0.elapsed_time(t1) / steps, n_reduced
+
+
 # ---------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -515,6 +548,18 @@ def main():
                            'd2h_bytes_per_step': r['d2h'], 'ms_per_step': ms,
                            'path': 'slayer.neuron.cuba.Neuron.forward on pinned host batches, chunked over batch',
                            'spike_rate': r['rate']}
+    if wl.name == 'cuba_fwd' and not args.no_e2e:
+        ms, n_red = fwd_bwd_cuba(shape, device, steps=max(2, min(args.steps, 5)), warmup=2, world=world)
+        if dist is not None:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        # bytes: fwd x in, spike + voltage + current out (16); ones-like grad written + read (8);
+        # bwd g_spike, voltage, current in, g_x out (16)
+        line['fwd_bwd'] = {'value': units * world / (ms * 1e-3), 'unit': wl.unit, 'ms_per_step': ms,
+                           'allreduce_elements': n_red,
+                           'path': 'cuba.Neuron(requires_grad=True)(x).sum().backward() + one all-reduce of decay grads'}
+        torch.cuda.empty_cache()
     if rank == 0 and not args.no_cpu:
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         line['cpu_baseline'] = cpu

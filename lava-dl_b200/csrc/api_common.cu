@@ -128,7 +128,7 @@ static void bind_primary_context() {
 #define SB_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
 #endif
 
-int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T) {
+int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -137,10 +137,11 @@ int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T) {
   bind_primary_context();
   const cuuint64_t dims[2] = {(cuuint64_t)T, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)T * 4};
-  const cuuint32_t box[2] = {(cuuint32_t)kTileT, (cuuint32_t)kTileR};
+  const cuuint32_t box[2] = {(cuuint32_t)tile_steps, (cuuint32_t)kTileR};
+  const CUtensorMapSwizzle swizzle = tile_steps == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, SB_L2_PROMOTION,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, SB_L2_PROMOTION,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld T=%lld base=%p)", (int)r, (long long)rows,

@@ -14,10 +14,11 @@
 // 1024 + K window in shared memory once (every input element is read from HBM
 // once), then each thread produces 16 consecutive outputs from registers, 16
 // taps at a time (a 32-word window per tap group, read as 128-bit words).
-// Shared memory is skewed by 4 words every 32 so that those 128-bit reads,
+// Shared memory is skewed by 4 words every 16 so that those 128-bit reads,
 // 64 bytes apart between neighbouring threads, are bank-conflict free.
 // At 64 taps the kernel does 64 FMAs per 8 bytes of HBM traffic, which puts it
-// at the FP32 issue limit rather than the HBM limit.
+// at the FP32 issue limit rather than the HBM limit.  K is capped at 4096 so the
+// window always fits the default 48 KB of dynamic shared memory.
 #include "api_util.cuh"
 
 using namespace sb;
@@ -29,41 +30,51 @@ constexpr int kFirThreads = 64;
 constexpr int kSeg = kOutPerThread * kFirThreads;  // outputs per block
 constexpr int kTapGroup = 16;
 
-__device__ __forceinline__ int skew(int i) { return i + ((i >> 5) << 2); }
+// 4 pad words after every 16: thread j's 16-output window then starts at word
+// 20 * j, so the eight threads of a 128-bit access phase hit distinct banks, and
+// offsets relative to that start are the same for every thread.
+__host__ __device__ constexpr int skew(int i) { return i + ((i >> 4) << 2); }
 
+template <bool SHIFT_IN, bool SHIFT_OUT>
 __global__ void __launch_bounds__(kFirThreads)
 fir_kernel(const float* __restrict__ x, const float* __restrict__ filt, int K, int Kp, bool reverse_taps, int off,
-           const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, bool shift_in, bool shift_out,
-           float ts, float* __restrict__ out, int64_t rows, int T) {
+           const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, float ts,
+           float* __restrict__ out, int64_t rows, int T) {
   extern __shared__ float sm[];
-  float* h = sm;                 // Kp taps (zero padded)
-  float* win = sm + Kp;          // skewed window of kSeg + Kp words
+  float* h = sm;         // Kp taps (zero padded)
+  float* win = sm + Kp;  // skewed window of kSeg + Kp words
   const int nwin = kSeg + Kp;
+  const int tid = threadIdx.x;
 
-  for (int i = threadIdx.x; i < Kp; i += kFirThreads) {
+  for (int i = tid; i < Kp; i += kFirThreads) {
     float v = 0.f;
     if (i < K) v = __ldg(filt + (reverse_taps ? (K - 1 - i) : i));
     h[i] = v;
   }
+  const int c0 = tid * kOutPerThread;
+  const float* wthread = win + skew(c0);
+  const int t0 = blockIdx.x * kSeg;
 
   for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
     int d = 0;
-    if (shift_in || shift_out) {
+    if (SHIFT_IN || SHIFT_OUT) {
       const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
       d = __float2int_rz(__fdiv_rn(sv, shift_ts));
+      d = max(-T - 8, min(T + 8, d));
     }
-    const int d_in = shift_in ? d : 0;
-    const int d_out = shift_out ? d : 0;
-    const int64_t base = row * (int64_t)T;
-    const int t0 = blockIdx.x * kSeg;
+    const int d_in = SHIFT_IN ? d : 0;
+    const int d_out = SHIFT_OUT ? d : 0;
     const int v0 = t0 + d_out - off;  // S index of window word 0
+    // window word i holds x[v0 + i - d_in] when both v0 + i and v0 + i - d_in lie in [0, T)
+    const int lo = max(0, max(-v0, d_in - v0));
+    const int hi = min(nwin, min(T - v0, T + d_in - v0));
+    const float* src = x + row * (int64_t)T + (v0 - d_in);
 
     __syncthreads();  // previous row's window fully consumed (and taps visible)
-    for (int i = threadIdx.x; i < nwin; i += kFirThreads) {
-      const int v = v0 + i;
-      const int s = v - d_in;
+#pragma unroll 4
+    for (int i = tid; i < nwin; i += kFirThreads) {
       float val = 0.f;
-      if (v >= 0 && v < T && s >= 0 && s < T) val = __ldg(x + base + s);
+      if (i >= lo && i < hi) val = __ldg(src + i);
       win[skew(i)] = val;
     }
     __syncthreads();
@@ -71,9 +82,9 @@ fir_kernel(const float* __restrict__ x, const float* __restrict__ filt, int K, i
     float acc[kOutPerThread];
 #pragma unroll
     for (int c = 0; c < kOutPerThread; ++c) acc[c] = 0.f;
-    const int c0 = threadIdx.x * kOutPerThread;
 
-    for (int m0 = 0; m0 < Kp; m0 += kTapGroup) {
+    const float* wp = wthread;
+    for (int m0 = 0; m0 < Kp; m0 += kTapGroup, wp += skew(kTapGroup)) {
       float hv[kTapGroup];
 #pragma unroll
       for (int q = 0; q < kTapGroup / 4; ++q) {
@@ -83,7 +94,7 @@ fir_kernel(const float* __restrict__ x, const float* __restrict__ filt, int K, i
       float xv[kOutPerThread + kTapGroup];
 #pragma unroll
       for (int q = 0; q < (kOutPerThread + kTapGroup) / 4; ++q) {
-        const float4 x4 = *reinterpret_cast<const float4*>(win + skew(c0 + m0 + 4 * q));
+        const float4 x4 = *reinterpret_cast<const float4*>(wp + skew(4 * q));
         xv[4 * q] = x4.x; xv[4 * q + 1] = x4.y; xv[4 * q + 2] = x4.z; xv[4 * q + 3] = x4.w;
       }
 #pragma unroll
@@ -94,14 +105,17 @@ fir_kernel(const float* __restrict__ x, const float* __restrict__ filt, int K, i
     }
 
     const int t = t0 + c0;
-    float* dst = out + base + t;
-    const bool vec = ((((uintptr_t)dst) & 15u) == 0) && (t + kOutPerThread <= T);
+    if (t >= T) continue;
+    float* dst = out + row * (int64_t)T + t;
 #pragma unroll
     for (int c = 0; c < kOutPerThread; ++c) {
-      const int u = t + c + d_out;
-      acc[c] = (u >= 0 && u < T) ? __fmul_rn(acc[c], ts) : 0.f;
+      acc[c] = __fmul_rn(acc[c], ts);
+      if (SHIFT_OUT) {
+        const int u = t + c + d_out;
+        if (u < 0 || u >= T) acc[c] = 0.f;
+      }
     }
-    if (vec) {
+    if (((((uintptr_t)dst) & 15u) == 0) && (t + kOutPerThread <= T)) {
 #pragma unroll
       for (int q = 0; q < kOutPerThread / 4; ++q)
         reinterpret_cast<float4*>(dst)[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
@@ -128,19 +142,19 @@ int launch_fir(const float* x, const float* filt, int64_t K, bool corr, const fl
   }
   const int Kp = (int)((K + kTapGroup - 1) / kTapGroup) * kTapGroup;
   const int nwin = kSeg + Kp;
-  const size_t smem = sizeof(float) * (size_t)(Kp + nwin + ((nwin >> 5) << 2) + 8);
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute((const void*)fir_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    attr_set[dev] = true;
-  }
+  const size_t smem = sizeof(float) * (size_t)(Kp + skew(nwin) + 8);
   const unsigned gx = (unsigned)((T + kSeg - 1) / kSeg);
   const unsigned gy = (unsigned)(rows < 65535 ? rows : 65535);
-  fir_kernel<<<dim3(gx, gy), kFirThreads, smem, (cudaStream_t)stream>>>(
-      x, filt, (int)K, Kp, !corr, corr ? 0 : (int)K - 1, lut, n_lut, shift, shift_ts, shift_in, shift_out, ts, out,
-      rows, (int)T);
+  const dim3 grid(gx, gy);
+  const int off = corr ? 0 : (int)K - 1;
+  cudaStream_t st = (cudaStream_t)stream;
+#define SB_GO(SI, SO)                                                                                          \
+  fir_kernel<SI, SO><<<grid, kFirThreads, smem, st>>>(x, filt, (int)K, Kp, !corr, off, lut, n_lut, shift, shift_ts, \
+                                                       ts, out, rows, (int)T);
+  if (shift_in) SB_GO(true, false)
+  else if (shift_out) SB_GO(false, true)
+  else SB_GO(false, false)
+#undef SB_GO
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

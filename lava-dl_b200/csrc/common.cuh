@@ -65,9 +65,13 @@ __device__ __forceinline__ int64_t param_index(const RowGeom& g, int64_t row, in
 
 // trunc(a * m / 4096): utils/int_utils.py:9-31 (right_shift_to_zero) applied to
 // the 64-bit product, any sign of a and m.
+// floor((p + bias) / 4096) with bias = 4095 for a negative product equals
+// trunc(p / 4096); the bias depends only on the operand signs, so it is formed
+// off the multiply's critical path and rides in as the 64-bit addend of the
+// widening multiply-add.
 __device__ __forceinline__ int mul_shift12(int a, int m) {
-  long long p = (long long)a * (long long)m;
-  p += (p >> 63) & 4095LL;
+  const long long bias = (long long)(((a ^ m) >> 31) & 4095);
+  const long long p = (long long)a * (long long)m + bias;
   return (int)(p >> 12);
 }
 
@@ -91,15 +95,22 @@ __device__ __forceinline__ float from_fixed(int v, float w, float inv_w) {
 // warp (conflict-free 128-bit accesses), while TMA moves the tile as coalesced
 // 128-byte row segments.
 // ---------------------------------------------------------------------------
+//
+// Ops with three or more streams per stage use 16-step tiles instead (64 B per
+// row, 64-byte swizzle: chunk c of row r at position c ^ ((r >> 1) & 3), again
+// conflict free) to halve shared memory per warp and double resident warps.
 constexpr int kTileT = 32;
 constexpr int kTileR = 32;
 constexpr int kTileBytes = kTileT * kTileR * 4;
 
+template <int TW>
 __device__ __forceinline__ uint32_t swz_chunk(int row, int chunk) {
-  return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
+  static_assert(TW == 32 || TW == 16, "tile width is 16 or 32 steps");
+  if (TW == 32) return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
+  return (uint32_t)(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
 }
 __device__ __forceinline__ uint32_t swz_elem(int row, int t) {
-  return swz_chunk(row, t >> 2) + ((t & 3) << 2);
+  return swz_chunk<32>(row, t >> 2) + ((t & 3) << 2);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -170,7 +181,7 @@ __device__ __forceinline__ void tma_wait_all() {
 // 128-byte swizzle.  Fails (returns non-zero, error text set) when the driver
 // entry point is missing or the tensor violates TMA's alignment rules; callers
 // test tma_eligible() first and take the plain-load kernel otherwise.
-int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T);
+int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps);
 bool tma_eligible(const void* const* ptrs, int n, int64_t T);
 
 // Smallest int k with (float)k >= thr (the reference compares an integer tensor

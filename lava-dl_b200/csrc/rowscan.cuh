@@ -43,18 +43,20 @@ struct RowPtrs {
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
 // ---------------------------------------------------------------------------
-// One tile: 8 chunks of 4 steps.  nvalid < 32 only for the ragged last tile.
+// One tile: TW / 4 chunks of 4 steps.  nvalid < TW only for the ragged last tile.
 // ---------------------------------------------------------------------------
-template <class Op, bool FULL>
+template <class Op, bool FULL, int TW>
 __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, int nvalid) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+  constexpr int kChunks = TW / 4;
+  constexpr int kTileBytes = TW * kTileR * 4;
 #pragma unroll 2
-  for (int cc = 0; cc < 8; ++cc) {
-    const int c = Op::REVERSE ? 7 - cc : cc;
+  for (int cc = 0; cc < kChunks; ++cc) {
+    const int c = Op::REVERSE ? kChunks - 1 - cc : cc;
     if (!FULL && c * 4 >= nvalid) {
       if (Op::REVERSE) continue; else break;
     }
-    const uint32_t off = swz_chunk(lane, c);
+    const uint32_t off = swz_chunk<TW>(lane, c);
     float vin[NIN][4];
 #pragma unroll
     for (int i = 0; i < NIN; ++i) {
@@ -88,12 +90,14 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // ---------------------------------------------------------------------------
 // TMA-pipelined kernel
 // ---------------------------------------------------------------------------
-template <class Op, int STAGES, int NB>
+template <class Op, int STAGES, int NB, int TW>
 __global__ void __launch_bounds__(128)
 rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
                    const typename Op::Params p, const RowGeom g, unsigned int* status) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
-  constexpr int kStageBytes = NT * NB * kTileBytes;  // NB boxes of 32 steps, side by side in time
+  constexpr int kTileT = TW;                         // shadows the 32-step default
+  constexpr int kTileBytes = TW * kTileR * 4;
+  constexpr int kStageBytes = NT * NB * kTileBytes;  // NB boxes of TW steps, side by side in time
   constexpr int kSpan = NB * kTileT;                 // time steps per stage
   constexpr int kWarpBytes = STAGES * kStageBytes;
   extern __shared__ uint8_t smem_raw[];
@@ -157,8 +161,8 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
       const int nvalid = T - (t0 + b * kTileT);
       if (nvalid <= 0) continue;
       uint8_t* box = stage + b * NT * kTileBytes;
-      if (nvalid >= kTileT) process_tile<Op, true>(op, box, lane, kTileT);
-      else process_tile<Op, false>(op, box, lane, nvalid);
+      if (nvalid >= kTileT) process_tile<Op, true, TW>(op, box, lane, kTileT);
+      else process_tile<Op, false, TW>(op, box, lane, nvalid);
       op.tile_end();
     }
     fence_proxy_async();
@@ -234,8 +238,8 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::P
       }
     }
     __syncwarp();
-    if (nvalid >= kTileT) process_tile<Op, true>(op, stage, lane, kTileT);
-    else process_tile<Op, false>(op, stage, lane, nvalid);
+    if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT);
+    else process_tile<Op, false, 32>(op, stage, lane, nvalid);
     op.tile_end();
     __syncwarp();
 #pragma unroll
@@ -277,8 +281,21 @@ constexpr int default_boxes(int) { return SB_BOXES; }
 #else
 constexpr int default_boxes(int streams) { return streams == 1 ? 2 : 1; }
 #endif
+// Tile width in steps: 16 (half the shared memory, twice the resident warps)
+// for ops with four streams per stage, and for three-stream ops that mostly
+// read.  Measured: ADRF forward 0.65 -> 0.72, ADRF backward 0.51 -> 0.79, ALIF
+// backward 0.82 -> 0.83 of copy bandwidth; ALIF forward (one read, three
+// writes) drops 0.75 -> 0.69 with 64-byte row segments and keeps 32.
+#ifdef SB_TILE_STEPS
+constexpr int default_tile_steps(int, int) { return SB_TILE_STEPS; }
+#else
+constexpr int default_tile_steps(int nin, int nout) {
+  return (cmax(nin, nout) >= 4 || (cmax(nin, nout) == 3 && nin > nout)) ? 16 : 32;
+}
+#endif
 
-template <class Op, int STAGES = SB_STAGES, int NB = default_boxes(cmax(Op::NIN, Op::NOUT))>
+template <class Op, int STAGES = SB_STAGES, int NB = default_boxes(cmax(Op::NIN, Op::NOUT)),
+          int TW = default_tile_steps(Op::NIN, Op::NOUT)>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
                    cudaStream_t st) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
@@ -295,12 +312,12 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
   if (tma_eligible(all, NIN + NOUT, g.T)) {
     MapPack<NIN + NOUT> maps;
     for (int i = 0; i < NIN + NOUT; ++i) {
-      int rc = make_row_map(&maps.m[i], all[i], g.rows, g.T);
+      int rc = make_row_map(&maps.m[i], all[i], g.rows, g.T, TW);
       if (rc != SB_OK) return rc;
     }
-    const size_t per_warp = (size_t)STAGES * NT * NB * kTileBytes + STAGES * 8;
+    const size_t per_warp = (size_t)STAGES * NT * NB * (TW * kTileR * 4) + STAGES * 8;
     const LaunchPlan lp = plan_rowscan(g.rows, per_warp, 1024);
-    auto fn = rowscan_tma_kernel<Op, STAGES, NB>;
+    auto fn = rowscan_tma_kernel<Op, STAGES, NB, TW>;
     int rc = prepare_kernel((const void*)fn, lp.smem);
     if (rc != SB_OK) return rc;
     fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(maps, p, g, status);
