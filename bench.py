@@ -46,9 +46,22 @@ import torch  # noqa: E402
 W_SCALE = 4096
 THR = 1.25 + 0.01 / 4096
 
-# dram bytes per launch of the dominant kernel from the committed ncu summary
-# (profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_PER_UNIT = {}
+# DRAM bytes per unit (dram__bytes_read.sum + dram__bytes_write.sum over the units
+# of the launch) of each workload's kernel, from the batch-8 ncu captures
+# summarised under profiles/.  Rows are independent, so traffic grows in
+# proportion to the batch: roofline.traffic = this figure x the units of a launch.
+NCU_TRAFFIC_PER_UNIT = {
+    'cuba_fwd': 11.70,
+    'cuba_bwd': 11.88,
+    'alif_fwd': 15.28,
+    'alif_bwd': 15.84,
+    'adrf_fwd': 24.16,
+    'adrf_bwd': 24.23,
+    'li_fwd': 7.76,
+    'li_bwd': 7.74,
+    'shift': 7.63,
+    'delay_fir_fwd': 7.62,
+}
 
 
 def peaks():
@@ -520,6 +533,13 @@ def main():
                 'traffic': None if tpu is None else tpu * units, 'peak_kind': f'of {peak_kind}',
                 'algorithmic_bytes_per_unit': wl.bpu, 'kernel_ms': kern_ms, 'kernel_ms_min': min(per),
                 'frac_of_nominal_8TBps': achieved / 8000.0}
+    if 'fir' in wl.name:
+        # 64 FMAs per 8-byte unit: the FP32 pipe (SMs x 128 lanes x clock) caps this kernel below the HBM roof
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        clk = (clocks.summary()['sm_mhz'] or 1965.0) * 1e6
+        fma_cap_units = sms * 128 * clk / 64.0
+        roofline['fp32_fma_ceiling_GBps'] = fma_cap_units * wl.bpu / 1e9
+        roofline['frac_of_fp32_fma_ceiling'] = (units / (kern_ms * 1e-3)) / fma_cap_units
 
     line = {
         'metric': f'neuron-steps/sec ({wl.name})' if wl.unit.startswith('neuron') else f'elements/sec ({wl.name})',

@@ -164,7 +164,9 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
   AthParams ap{{ref_decay, n_ref_decay}, {th_decay, n_th_decay}, ref_state, th_state, th_step, th0};
   cudaStream_t st = (cudaStream_t)stream;
   const float* in[1] = {x};
+  // kernel order in forward mode: voltage, threshold + refractory, spike
   float* out[4] = {out0, out1, out2, out3};
+  if (mode == 0) { out[0] = out1; out[1] = out2; out[2] = out0; out[3] = nullptr; }
 #define SB_GO(D, G)                                                                                  \
   {                                                                                                  \
     typename AlifFwd<D, G>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,     \
@@ -203,7 +205,12 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
   const int k_spike = int_threshold_ge_scaled(threshold, sc.w);
   cudaStream_t st = (cudaStream_t)stream;
   const float* in[2] = {re_in, im_in};
+  // kernel order in forward mode: re, im, [threshold + refractory], spike
   float* out[4] = {out0, out1, out2, out3};
+  if (mode == 0) {
+    if (adapt) { out[0] = out1; out[1] = out2; out[2] = out3; out[3] = out0; }
+    else { out[0] = out1; out[1] = out2; out[2] = out0; out[3] = nullptr; }
+  }
 #define SB_GO(A, D, G)                                                                               \
   {                                                                                                  \
     typename RfFwd<A, D, G>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,      \

@@ -9,11 +9,23 @@
 // every state stays inside int32 (Loihi states are 24 bit); fused ops skip the
 // float round trip between stages, which is the identity for |state| < 2^24 and
 // a power-of-two w_scale (the host only fuses in that case).
+//
+// Every op also states the pipeline shape its TMA kernel runs with: STAGES per
+// warp, BOXES of TILE steps per stage (shared memory per warp = STAGES *
+// max(NIN, NOUT - NBIT) * BOXES * TILE * 128 B).  The values were picked by
+// sweeping shapes on a B200 (fractions are of the measured copy bandwidth):
+// light single-stream ops want long row segments and deep prefetch (LI backward
+// 3 x 4 x 32: 0.94), heavier ones more resident warps (CUBA forward 3 x 3 x 32:
+// 0.85, LI forward 0.91), multi-stream ops one box of 32 steps (CUBA backward
+// 0.84) or of 16 steps when four streams would leave too few warps (ADRF
+// backward 0.79 against 0.51 with 32).
 #pragma once
 
 #include "common.cuh"
 
 namespace sb {
+
+#define SB_PIPE(S, B, T) static constexpr int STAGES = S, BOXES = B, TILE = T
 
 // ---------------------------------------------------------------------------
 // Parameter blocks shared by several ops
@@ -106,6 +118,8 @@ template <bool RESET, bool POW2>
 struct LiFwd {
   static constexpr int NIN = 1, NOUT = 1;
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 3, 32);
   struct Params {
     DecayVec decay;
     const float* state;   // [rows]
@@ -145,6 +159,8 @@ template <bool DGRAD>
 struct LiBwd {
   static constexpr int NIN = DGRAD ? 2 : 1, NOUT = 1;
   static constexpr bool REVERSE = true;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, (DGRAD ? 1 : 4), 32);
   struct Params {
     DecayVec decay;
     double* partial;  // scratch, see store_partial()
@@ -207,6 +223,8 @@ template <bool POW2>
 struct AthFwd {
   static constexpr int NIN = 1, NOUT = 2;  // out: threshold, refractory
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 32);
   struct Params {
     AthParams ath;
     Scale sc;
@@ -233,6 +251,8 @@ template <bool POW2>
 struct ApthFwd {
   static constexpr int NIN = 2, NOUT = 2;  // in: re, im; out: threshold, refractory
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 32);
   struct Params {
     AthParams ath;
     const float* im_state;  // [rows]
@@ -293,6 +313,8 @@ template <bool RESET, bool POW2>
 struct ResFwd {
   static constexpr int NIN = 2, NOUT = 2;
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 32);
   struct Params {
     ResParams res;
     int k_thr;     // smallest int whose fp32 value reaches thr * w
@@ -327,6 +349,8 @@ template <bool PGRAD>
 struct ResBwd {
   static constexpr int NIN = PGRAD ? 4 : 2, NOUT = 2;  // in: g_re, g_im, [re, im]
   static constexpr bool REVERSE = true;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, (PGRAD ? 16 : 32));
   struct Params {
     DecayVec sin_decay, cos_decay;
     double* partial_sin;
@@ -370,6 +394,8 @@ template <bool POW2>
 struct AdResFwd {
   static constexpr int NIN = 2, NOUT = 4;  // out: re, im, threshold, refractory
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 16);
   struct Params {
     ResParams res;
     AthParams ath;
@@ -406,6 +432,8 @@ template <bool OUT_CUR, bool OUT_SPK, bool GRADED>
 struct CubaFwd {
   static constexpr int NIN = 1, NOUT = 1 + (OUT_CUR ? 1 : 0) + (OUT_SPK ? 1 : 0);
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = (OUT_SPK && !GRADED) ? 1 : 0;  // binary spikes leave as bits
+  SB_PIPE(3, ((NOUT - NBIT) == 1 ? 3 : 1), 32);
   static constexpr int IV = OUT_CUR ? 1 : 0, IS = IV + 1;
   struct Params {
     DecayVec cdecay, vdecay;
@@ -465,6 +493,8 @@ template <bool TENSOR_THR, bool GRADED, bool DGRAD>
 struct CubaBwd {
   static constexpr int NIN = 2 + (TENSOR_THR ? 1 : 0) + (DGRAD ? 1 : 0), NOUT = 1;
   static constexpr bool REVERSE = true;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, (NIN >= 3 ? 16 : 32));
   static constexpr int ITH = 2, ICUR = 2 + (TENSOR_THR ? 1 : 0);
   struct Params {
     DecayVec cdecay, vdecay;
@@ -511,12 +541,14 @@ struct CubaBwd {
 //   current = LI(x); voltage = LI(current) (no reset); (th, ref) = ATh(voltage)
 //   spike = voltage >= th + ref   (fp32 comparison of the returned series)
 // DYN: outputs current, voltage, threshold, refractory (what dynamics() returns)
-// else: outputs spike, voltage, threshold + refractory (what forward() needs)
+// else: outputs voltage, threshold + refractory, spike (what forward() needs)
 // ===========================================================================
 template <bool DYN, bool GRADED>
 struct AlifFwd {
   static constexpr int NIN = 1, NOUT = DYN ? 4 : 3;
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = 0;  // bit output measured slower here (0.72 against 0.76)
+  SB_PIPE(3, 1, (DYN ? 16 : 32));
   struct Params {
     DecayVec cdecay, vdecay;
     const float* cstate;
@@ -554,7 +586,7 @@ struct AlifFwd {
       const float thsum = __fadd_rn(thf, reff);
       const bool sp = vf >= thsum;
       last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, vf), spike_scale) : (sp ? 1.f : 0.f);
-      b[0] = last_s; b[1] = vf; b[2] = thsum;
+      b[0] = vf; b[1] = thsum; b[2] = last_s;
     }
     s.commit(v >= s.th_new + s.ref_new);
   }
@@ -577,13 +609,15 @@ struct AlifFwd {
 // Complex spike: spike/complex.py:66-92
 //   spike = (re >= thr) * (im[t-1] < 0) * (im >= 0),  im[-1] = imag state
 // DYN (ADAPT only): outputs re, im, threshold, refractory
-// else            : outputs spike, re, im, [threshold + refractory]
+// else            : outputs re, im, [threshold + refractory], spike
 // ===========================================================================
 template <bool ADAPT, bool DYN, bool GRADED>
 struct RfFwd {
   static_assert(ADAPT || !DYN, "DYN needs ADAPT");
   static constexpr int NIN = 2, NOUT = ADAPT ? 4 : 3;
   static constexpr bool REVERSE = false;
+  static constexpr int NBIT = (!DYN && !GRADED) ? 1 : 0;
+  SB_PIPE(3, 1, ((NOUT - NBIT) >= 4 ? 16 : 32));
   struct Params {
     ResParams res;
     AthParams ath;    // ADAPT only
@@ -620,14 +654,14 @@ struct RfFwd {
         const float thsum = __fadd_rn(thf, rff);
         const bool sp = (ref_ >= thsum) && im_prev_neg && (r.im >= 0);
         last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
-        b[0] = last_s; b[1] = ref_; b[2] = imf; b[3] = thsum;
+        b[0] = ref_; b[1] = imf; b[2] = thsum; b[3] = last_s;
       }
       s.commit(r.re >= s.th_new + s.ref_new && r.im >= 0 && im_old_i < 0);
       im_old_i = r.im;
     } else {
       const bool sp = (r.re >= k_spike) && im_prev_neg && (r.im >= 0);
       last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
-      b[0] = last_s; b[1] = ref_; b[2] = imf;
+      b[0] = ref_; b[1] = imf; b[2] = last_s;
     }
     im_prev_neg = r.im < 0;
   }
@@ -651,6 +685,8 @@ template <bool TENSOR_THR, bool GRADED, bool PGRAD>
 struct RfBwd {
   static constexpr int NIN = 3 + (TENSOR_THR ? 1 : 0), NOUT = 2;
   static constexpr bool REVERSE = true;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 16);
   struct Params {
     DecayVec sin_decay, cos_decay;
     CSurrogate sg;

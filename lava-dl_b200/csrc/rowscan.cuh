@@ -20,6 +20,14 @@
 // tile k are issued the stage used by tile k-1 is recycled for tile k+S-1 once
 // its stores have finished reading shared memory (bulk wait_group.read).
 //
+// Outputs that are 0/1 valued (binary spikes) need not occupy a shared-memory
+// tile at all: an op may declare its last NBIT outputs as bit outputs.  Each
+// lane then collects one bit per step in a register and, per stage, the warp
+// writes those rows straight to global memory (a shuffle hands every lane the
+// mask of the row being written: one coalesced row segment per store).  This
+// halves the shared memory of the fused CUBA forward, which buys two boxes per
+// stage, i.e. 256-byte row segments for every stream.
+//
 // When a tensor cannot be described to TMA (T not a multiple of 4, base not
 // 16-byte aligned, T < 32) the same ops run under rowscan_plain_kernel, which
 // fills the same swizzled tiles with plain coalesced loads.
@@ -46,8 +54,9 @@ __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 // One tile: TW / 4 chunks of 4 steps.  nvalid < TW only for the ragged last tile.
 // ---------------------------------------------------------------------------
 template <class Op, bool FULL, int TW>
-__device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, int nvalid) {
-  constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+__device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, int nvalid,
+                                             uint32_t (&bits)[Op::NBIT > 0 ? Op::NBIT : 1]) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NS = Op::NOUT - Op::NBIT;
   constexpr int kChunks = TW / 4;
   constexpr int kTileBytes = TW * kTileR * 4;
 #pragma unroll 2
@@ -63,7 +72,7 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
       const float4 v = *reinterpret_cast<const float4*>(stage + i * kTileBytes + off);
       vin[i][0] = v.x; vin[i][1] = v.y; vin[i][2] = v.z; vin[i][3] = v.w;
     }
-    float vout[NOUT][4];
+    float vout[NS > 0 ? NS : 1][4];
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const int j = Op::REVERSE ? 3 - jj : jj;
@@ -77,12 +86,66 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
         for (int o = 0; o < NOUT; ++o) b[o] = 0.f;
       }
 #pragma unroll
-      for (int o = 0; o < NOUT; ++o) vout[o][j] = b[o];
+      for (int o = 0; o < NS; ++o) vout[o][j] = b[o];
+#pragma unroll
+      for (int d = 0; d < Op::NBIT; ++d)
+        if (b[NS + d] != 0.f) bits[d] |= 1u << (c * 4 + j);
     }
 #pragma unroll
-    for (int o = 0; o < NOUT; ++o) {
+    for (int o = 0; o < NS; ++o) {
       *reinterpret_cast<float4*>(stage + o * kTileBytes + off) =
           make_float4(vout[o][0], vout[o][1], vout[o][2], vout[o][3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Bit outputs: lane r holds, per box, the mask of row r (bit t = step t of the
+// box).  Row by row, every lane fetches that row's masks and the warp writes
+// the row's NB * TW steps as coalesced 0.f / 1.f values.
+// ---------------------------------------------------------------------------
+template <int N>
+struct BitPtrs {
+  float* p[N > 0 ? N : 1];
+};
+
+template <int NB, int TW>
+__device__ __forceinline__ void store_bit_rows(float* __restrict__ base, int64_t T, int nrows, int nvalid,
+                                               const uint32_t (&mask)[NB], int lane, bool vec_ok) {
+  constexpr int kSpan = NB * TW;
+  if (TW == 32 && vec_ok && nrows == kTileR && nvalid >= kSpan) {
+    // 128-bit stores: eight lanes cover one row's 32 steps, four rows per instruction
+    const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll
+    for (int i = 0; i < kTileR / 4; ++i) {
+      const int r = sub + 4 * i;
+      float* dst = base + (int64_t)r * T + chunk * 4;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const uint32_t m = __shfl_sync(0xffffffffu, mask[b], r) >> (chunk * 4);
+        *reinterpret_cast<float4*>(dst + b * TW) =
+            make_float4((m & 1u) ? 1.f : 0.f, (m & 2u) ? 1.f : 0.f, (m & 4u) ? 1.f : 0.f, (m & 8u) ? 1.f : 0.f);
+      }
+    }
+    return;
+  }
+#pragma unroll 4
+  for (int r = 0; r < kTileR; ++r) {
+    uint32_t mrow[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) mrow[b] = __shfl_sync(0xffffffffu, mask[b], r);
+    if (r >= nrows) continue;
+    float* dst = base + (int64_t)r * T;
+#pragma unroll
+    for (int q = 0; q < (kSpan + 31) / 32; ++q) {
+      const int pos = q * 32 + lane;
+      if (pos < kSpan && pos < nvalid) {
+        const int box = pos / TW, bit = pos % TW;
+        uint32_t m = mrow[0];
+#pragma unroll
+        for (int b = 1; b < NB; ++b) m = (box == b) ? mrow[b] : m;
+        dst[pos] = ((m >> bit) & 1u) ? 1.f : 0.f;
+      }
     }
   }
 }
@@ -92,9 +155,10 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // ---------------------------------------------------------------------------
 template <class Op, int STAGES, int NB, int TW>
 __global__ void __launch_bounds__(128)
-rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
-                   const typename Op::Params p, const RowGeom g, unsigned int* status) {
-  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT> maps,
+                   const BitPtrs<Op::NBIT> bitout, const typename Op::Params p, const RowGeom g,
+                   unsigned int* status) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
   constexpr int kTileT = TW;                         // shadows the 32-step default
   constexpr int kTileBytes = TW * kTileR * 4;
   constexpr int kStageBytes = NT * NB * kTileBytes;  // NB boxes of TW steps, side by side in time
@@ -155,15 +219,22 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
     if (!mbar_wait(bar0 + s * 8, (k / STAGES) & 1)) { ok = false; break; }
     uint8_t* stage = wsm + s * kStageBytes;
     const int t0 = tile_t0(k);
+    uint32_t bits[NBIT > 0 ? NBIT : 1][NB];
 #pragma unroll
     for (int bb = 0; bb < NB; ++bb) {
       const int b = Op::REVERSE ? NB - 1 - bb : bb;
+      uint32_t boxbits[NBIT > 0 ? NBIT : 1];
+#pragma unroll
+      for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) boxbits[d] = 0u;
       const int nvalid = T - (t0 + b * kTileT);
-      if (nvalid <= 0) continue;
-      uint8_t* box = stage + b * NT * kTileBytes;
-      if (nvalid >= kTileT) process_tile<Op, true, TW>(op, box, lane, kTileT);
-      else process_tile<Op, false, TW>(op, box, lane, nvalid);
-      op.tile_end();
+      if (nvalid > 0) {
+        uint8_t* box = stage + b * NT * kTileBytes;
+        if (nvalid >= kTileT) process_tile<Op, true, TW>(op, box, lane, kTileT, boxbits);
+        else process_tile<Op, false, TW>(op, box, lane, nvalid, boxbits);
+        op.tile_end();
+      }
+#pragma unroll
+      for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) bits[d][b] = boxbits[d];
     }
     fence_proxy_async();
     __syncwarp();
@@ -182,6 +253,13 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT> maps,
       }
     }
     __syncwarp();
+    if (NBIT > 0) {
+      const int64_t left = g.rows - row0;
+#pragma unroll
+      for (int d = 0; d < NBIT; ++d)
+        store_bit_rows<NB, TW>(bitout.p[d] + row0 * (int64_t)T + t0, T, left < kTileR ? (int)left : kTileR, T - t0,
+                               bits[d], lane, (reinterpret_cast<uintptr_t>(bitout.p[d]) & 15u) == 0);
+    }
   }
 
   if (lane == 0) tma_wait_all<0>();
@@ -205,7 +283,7 @@ template <class Op>
 __global__ void __launch_bounds__(128)
 rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::Params p, const RowGeom g,
                      unsigned int* status) {
-  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
   extern __shared__ uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int64_t wid = (int64_t)blockIdx.x * nwarps + warp;
@@ -238,8 +316,11 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::P
       }
     }
     __syncwarp();
-    if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT);
-    else process_tile<Op, false, 32>(op, stage, lane, nvalid);
+    uint32_t bits[NBIT > 0 ? NBIT : 1];
+#pragma unroll
+    for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) bits[d] = 0u;
+    if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT, bits);
+    else process_tile<Op, false, 32>(op, stage, lane, nvalid, bits);
     op.tile_end();
     __syncwarp();
 #pragma unroll
@@ -250,6 +331,11 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::P
         if (tin && r < nrows)
           dst[(int64_t)r * T] = *reinterpret_cast<const float*>(stage + o * kTileBytes + swz_elem(r, lane));
       }
+    }
+#pragma unroll
+    for (int d = 0; d < NBIT; ++d) {
+      const uint32_t one[1] = {bits[d]};
+      store_bit_rows<1, 32>(ptrs.out[NOUT + d] + row0 * (int64_t)T + t0, T, nrows, nvalid, one, lane, false);
     }
     __syncwarp();
   }
@@ -268,37 +354,30 @@ struct LaunchPlan {
 LaunchPlan plan_rowscan(int64_t rows, size_t bytes_per_warp, size_t fixed_bytes);
 int prepare_kernel(const void* fn, size_t smem);
 
-// Pipeline shape of the TMA kernels: stages per warp and 32-step boxes per stage.
-// Shared memory per warp is STAGES * max(NIN, NOUT) * boxes * 4 KB and decides
-// how many warps an SM holds.  Measured on B200 (fraction of copy bandwidth):
-// single-stream ops gain from 256-byte row segments (two boxes: 0.80 -> 0.87),
-// multi-stream ops lose more from the halved occupancy than they gain.
-#ifndef SB_STAGES
-#define SB_STAGES 3
+// Pipeline shape of the TMA kernels.  Each op names its own (ops.cuh); the
+// macros override all of them at once for sweeps.
+#ifdef SB_STAGES
+template <class Op> constexpr int pipe_stages() { return SB_STAGES; }
+#else
+template <class Op> constexpr int pipe_stages() { return Op::STAGES; }
 #endif
 #ifdef SB_BOXES
-constexpr int default_boxes(int) { return SB_BOXES; }
+template <class Op> constexpr int pipe_boxes() { return SB_BOXES; }
 #else
-constexpr int default_boxes(int streams) { return streams == 1 ? 2 : 1; }
+template <class Op> constexpr int pipe_boxes() { return Op::BOXES; }
 #endif
-// Tile width in steps: 16 (half the shared memory, twice the resident warps)
-// for ops with four streams per stage, and for three-stream ops that mostly
-// read.  Measured: ADRF forward 0.65 -> 0.72, ADRF backward 0.51 -> 0.79, ALIF
-// backward 0.82 -> 0.83 of copy bandwidth; ALIF forward (one read, three
-// writes) drops 0.75 -> 0.69 with 64-byte row segments and keeps 32.
 #ifdef SB_TILE_STEPS
-constexpr int default_tile_steps(int, int) { return SB_TILE_STEPS; }
+template <class Op> constexpr int pipe_tile() { return SB_TILE_STEPS; }
 #else
-constexpr int default_tile_steps(int nin, int nout) {
-  return (cmax(nin, nout) >= 4 || (cmax(nin, nout) == 3 && nin > nout)) ? 16 : 32;
-}
+template <class Op> constexpr int pipe_tile() { return Op::TILE; }
 #endif
 
-template <class Op, int STAGES = SB_STAGES, int NB = default_boxes(cmax(Op::NIN, Op::NOUT)),
-          int TW = default_tile_steps(Op::NIN, Op::NOUT)>
+template <class Op, int STAGES = pipe_stages<Op>(), int NB = pipe_boxes<Op>(), int TW = pipe_tile<Op>()>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
                    cudaStream_t st) {
-  constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NT = cmax(NIN, NOUT);
+  // NOUT counts the outputs that travel through shared memory; the NBIT bit
+  // outputs follow them in `out`.
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
   if (g.rows == 0 || g.T == 0) return SB_OK;
   SB_REQUIRE(g.rows > 0 && g.rows < (int64_t)2147483647 - 64, "rows out of range: %lld", (long long)g.rows);
   SB_REQUIRE(g.T > 0, "T out of range");
@@ -306,6 +385,12 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
   for (int i = 0; i < NIN; ++i) all[i] = in[i];
   for (int o = 0; o < NOUT; ++o) all[NIN + o] = out[o];
   for (int i = 0; i < NIN + NOUT; ++i) SB_REQUIRE(all[i] != nullptr, "null tensor pointer (slot %d)", i);
+  BitPtrs<NBIT> bitout;
+  bitout.p[0] = nullptr;
+  for (int d = 0; d < NBIT; ++d) {
+    SB_REQUIRE(out[NOUT + d] != nullptr, "null tensor pointer (bit output %d)", d);
+    bitout.p[d] = out[NOUT + d];
+  }
   unsigned int* status = status_ptr();
   if (!status) return SB_ERR_CUDA;
 
@@ -320,11 +405,11 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
     auto fn = rowscan_tma_kernel<Op, STAGES, NB, TW>;
     int rc = prepare_kernel((const void*)fn, lp.smem);
     if (rc != SB_OK) return rc;
-    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(maps, p, g, status);
+    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(maps, bitout, p, g, status);
   } else {
-    RowPtrs<NIN, NOUT> ptrs;
+    RowPtrs<NIN, Op::NOUT> ptrs;
     for (int i = 0; i < NIN; ++i) ptrs.in[i] = in[i];
-    for (int o = 0; o < NOUT; ++o) ptrs.out[o] = out[o];
+    for (int o = 0; o < Op::NOUT; ++o) ptrs.out[o] = out[o];
     const size_t per_warp = (size_t)NT * kTileBytes;
     const LaunchPlan lp = plan_rowscan(g.rows, per_warp, 0);
     auto fn = rowscan_plain_kernel<Op>;

@@ -35,10 +35,11 @@ def persistent_real_state(real_state, spike):
     return real_state * (1 - spike)
 
 
-def persistent_imag_state(imag_state, spike, threshold):
-    """Imaginary state to carry over when the last time bin spiked."""
+def persistent_imag_state(imag_state, spike, threshold, scale):
+    """Imaginary state to carry over when the last time bin spiked: one
+    quantisation step below the threshold (``resonator.py:152-174``)."""
     spike = (spike > 0).to(imag_state.dtype)
-    return imag_state * (1 - spike) + spike * (threshold - 1)
+    return spike * (threshold - 1 / scale) + (1 - spike) * imag_state
 
 
 class _ResDynamics(torch.autograd.Function):

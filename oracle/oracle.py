@@ -341,3 +341,40 @@ def adrf(re_in, im_in, threshold, threshold_step, sin_decay, cos_decay, threshol
         a, b, gs, gc = res_bwd(g_re, g_im, re, im, sd, cd)
         out.update(grad_re=a, grad_im=b, grad_sin_decay=gs, grad_cos_decay=gc)
     return out
+
+
+def rf_iz(re_in, im_in, threshold, sin_decay, cos_decay, scale=64, re_state=0., im_state=0., grad_spike=None,
+          tau_grad=1, scale_grad=1, graded=False):
+    """neuron/rf_iz.py:331-520: resonator with Izhikevich reset, threshold spike on the imaginary part."""
+    w_scale, s_scale = scale, scale * 64
+    thr = int(threshold * w_scale) / w_scale
+    sd, cd = quantize(sin_decay), quantize(cos_decay)
+    re, im = res_fwd(re_in, im_in, sd, cd, re_state, im_state, s_scale, thr)
+    spike = spike_fwd(im, thr, graded, 1)
+    out = dict(real=re, imag=im, spike=spike)
+    if grad_spike is not None:
+        g_im = spike_bwd(im, thr, grad_spike, tau_grad * thr * 100, scale_grad * 0.1, graded)
+        a, b, gs, gc = res_bwd(np.zeros_like(g_im), g_im, re, im, sd, cd)
+        out.update(grad_re=a, grad_im=b, grad_sin_decay=gs, grad_cos_decay=gc, grad_imag_series=g_im)
+    return out
+
+
+def adrf_iz(re_in, im_in, threshold, threshold_step, sin_decay, cos_decay, threshold_decay, refractory_decay,
+            scale=64, re_state=0., im_state=0., th_state=None, ref_state=0., grad_spike=None, tau_grad=1,
+            scale_grad=1, graded=False):
+    """neuron/adrf_iz.py:440-650: adaptive resonator, threshold spike on imag >= threshold + refractory."""
+    w_scale, s_scale = scale, scale * 64
+    thr = int(threshold * w_scale) / w_scale
+    step = int(threshold_step * w_scale) / w_scale
+    sd, cd = quantize(sin_decay), quantize(cos_decay)
+    td, rd = quantize(threshold_decay), quantize(refractory_decay)
+    re, im, th, ref = adres_fwd(re_in, im_in, sd, cd, rd, td, re_state, im_state, ref_state,
+                                thr if th_state is None else th_state, step, thr, s_scale)
+    thsum = th + ref
+    spike = spike_fwd(im, thsum, graded, 1)
+    out = dict(real=re, imag=im, threshold=th, refractory=ref, spike=spike)
+    if grad_spike is not None:
+        g_im = spike_bwd(im, thsum, grad_spike, tau_grad * thr * 100, scale_grad * 0.1, graded)
+        a, b, gs, gc = res_bwd(np.zeros_like(g_im), g_im, re, im, sd, cd)
+        out.update(grad_re=a, grad_im=b, grad_sin_decay=gs, grad_cos_decay=gc, grad_imag_series=g_im)
+    return out

@@ -340,6 +340,39 @@ def main():
                    ['sin_decay', 'cos_decay', 'threshold_decay', 'refractory_decay'], split=50)
     save('neuron_adrf_shared', re_in=re_in, im_in=im_in, **r)
 
+    # Izhikevich-reset variants.  adrf_iz.forward raises TypeError in the reference
+    # (adrf_iz.py:669-670), so its golden run calls dynamics() and spike() itself.
+    def iz_case(make, adaptive):
+        res = {}
+        n = make()
+        ins = [re_in.clone().requires_grad_(True), im_in.clone().requires_grad_(True)]
+        dyn = n.dynamics(tuple(ins))
+        spike = n.spike(*dyn)
+        g = randn(*spike.shape)
+        (spike * g).sum().backward()
+        res.update(spike=spike, grad_spike=g, grad_in0=ins[0].grad, grad_in1=ins[1].grad)
+        for i, t in enumerate(dyn):
+            res[f'dyn{i}'] = t
+        for k in ['sin_decay', 'cos_decay']:
+            res[f'param_{k}'] = getattr(n, k).data
+            res[f'grad_{k}'] = getattr(n, k).grad
+        with torch.no_grad():
+            p = make()
+            p.persistent_state = True
+            outs = []
+            for a, b in ((re_in[..., :41], im_in[..., :41]), (re_in[..., 41:], im_in[..., 41:])):
+                outs.append(p.spike(*p.dynamics((a, b))))
+            res['spike_split'] = torch.cat(outs, dim=-1)
+            for name, buf in p.named_buffers():
+                if name.endswith('_state'):
+                    res[f'final_{name}'] = buf
+        return res
+
+    save('neuron_rfiz_shared', re_in=re_in, im_in=im_in,
+         **iz_case(lambda: slayer.neuron.rf_iz.Neuron(0.5, 10, 0.1, requires_grad=True), False))
+    save('neuron_adrfiz_shared', re_in=re_in, im_in=im_in,
+         **iz_case(lambda: slayer.neuron.adrf_iz.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1, requires_grad=True), True))
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

@@ -306,3 +306,55 @@ def test_adrf_shared(cuda, slayer):
     g = load_golden('neuron_adrf_shared')
     _check_neuron(lambda: slayer.neuron.adrf.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1), g, ADRF_P,
                   ['re_in', 'im_in'], ['real', 'imag', 'threshold', 'refractory'], 50, cuda, 'adrf')
+
+
+# --------------------------------------------------------------------------
+# Izhikevich-reset variants: dynamics() + spike() (the reference's adrf_iz.forward is broken)
+# --------------------------------------------------------------------------
+def _check_iz(make, g, oracle_run, cuda):
+    ins = [T(g['re_in'], cuda, True), T(g['im_in'], cuda, True)]
+    n = make().to(cuda)
+    dyn = n.dynamics(tuple(ins))
+    spike = n.spike(*dyn)
+    assert_exact(spike, g['spike'], 'spike')
+    for i, t in enumerate(dyn):
+        assert_quantised_equal(t, g[f'dyn{i}'], S, f'dyn{i}')
+    (spike * T(g['grad_spike'], cuda)).sum().backward()
+    want = oracle_run()
+    S_re, S_im = res_scale(np.zeros_like(want['grad_imag_series']), want['grad_imag_series'],
+                           np.round(g['param_sin_decay']), np.round(g['param_cos_decay']))
+    S_p = pgrad_scale(1, (g['grad_in0'], g['dyn0']), (g['grad_in0'], g['dyn1']), (g['grad_in1'], g['dyn0']),
+                      (g['grad_in1'], g['dyn1']))
+    assert_close(ins[0].grad, g['grad_in0'], 'grad_re', scale=S_re)
+    assert_close(ins[1].grad, g['grad_in1'], 'grad_im', scale=S_im)
+    assert_close(n.sin_decay.grad, g['grad_sin_decay'], 'grad_sin', scale=S_p)
+    assert_close(n.cos_decay.grad, g['grad_cos_decay'], 'grad_cos', scale=S_p)
+    with torch.no_grad():
+        p = make().to(cuda)
+        p.persistent_state = True
+        outs = []
+        for sl in (slice(None, 41), slice(41, None)):
+            a = T(g['re_in'][..., sl], cuda)
+            b = T(g['im_in'][..., sl], cuda)
+            outs.append(p.spike(*p.dynamics((a, b))))
+        assert_exact(torch.cat(outs, dim=-1), g['spike_split'], 'persistent-state split run')
+        for name, buf in p.named_buffers():
+            if name.endswith('_state'):
+                assert_quantised_equal(buf, g[f'final_{name}'], S, f'final {name}')
+
+
+def test_rf_iz(cuda, slayer):
+    g = load_golden('neuron_rfiz_shared')
+    _check_iz(lambda: slayer.neuron.rf_iz.Neuron(0.5, 10, 0.1, requires_grad=True), g,
+              lambda: O.rf_iz(g['re_in'], g['im_in'], 0.5, g['param_sin_decay'], g['param_cos_decay'],
+                              grad_spike=g['grad_spike']), cuda)
+
+
+def test_adrf_iz(cuda, slayer):
+    g = load_golden('neuron_adrfiz_shared')
+    _check_iz(lambda: slayer.neuron.adrf_iz.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1, requires_grad=True), g,
+              lambda: O.adrf_iz(g['re_in'], g['im_in'], 0.5, 0.25, g['param_sin_decay'], g['param_cos_decay'],
+                                410.0, 410.0, grad_spike=g['grad_spike']), cuda)
+    n = slayer.neuron.adrf_iz.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1).to(cuda)
+    out = n((T(g['re_in'], cuda), T(g['im_in'], cuda)))  # forward() works here (TypeError in the reference)
+    assert_exact(out, g['spike'], 'forward')

@@ -133,7 +133,7 @@ def test_delay_filter_chain():
 S = 4096
 
 
-@pytest.mark.parametrize('name', golden_cases('neuron_cuba'))
+@pytest.mark.parametrize('name', golden_cases('neuron_cuba_'))
 def test_cuba_neuron(name):
     g = load_golden(name)
     graded = 'graded' in name
@@ -148,7 +148,7 @@ def test_cuba_neuron(name):
         assert_close(r['grad_voltage_decay'], g['grad_voltage_decay'], 'grad voltage decay')
 
 
-@pytest.mark.parametrize('name', golden_cases('neuron_alif'))
+@pytest.mark.parametrize('name', golden_cases('neuron_alif_'))
 def test_alif_neuron(name):
     g = load_golden(name)
     r = O.alif(g['x'], 1.0, 0.5, g['param_current_decay'], g['param_voltage_decay'], g['param_threshold_decay'],
@@ -174,7 +174,7 @@ def test_rf_neuron():
     assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
 
 
-@pytest.mark.parametrize('name', golden_cases('neuron_adrf'))
+@pytest.mark.parametrize('name', golden_cases('neuron_adrf_'))
 def test_adrf_neuron(name):
     g = load_golden(name)
     r = O.adrf(g['re_in'], g['im_in'], 0.5, 0.25, g['param_sin_decay'], g['param_cos_decay'],
@@ -187,3 +187,28 @@ def test_adrf_neuron(name):
     if 'grad_sin_decay' in g:
         assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
         assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
+
+
+def test_rf_iz_neuron():
+    g = load_golden('neuron_rfiz_shared')
+    r = O.rf_iz(g['re_in'], g['im_in'], 0.5, g['param_sin_decay'], g['param_cos_decay'], grad_spike=g['grad_spike'])
+    assert_exact(r['spike'], g['spike'], 'spike')
+    assert_quantised_equal(r['real'], g['dyn0'], S, 'real')
+    assert_quantised_equal(r['imag'], g['dyn1'], S, 'imag')
+    assert_close(r['grad_re'], g['grad_in0'], 'grad_re')
+    assert_close(r['grad_im'], g['grad_in1'], 'grad_im')
+    assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
+    assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
+
+
+def test_adrf_iz_neuron():
+    g = load_golden('neuron_adrfiz_shared')
+    r = O.adrf_iz(g['re_in'], g['im_in'], 0.5, 0.25, g['param_sin_decay'], g['param_cos_decay'], 410.0, 410.0,
+                  grad_spike=g['grad_spike'])
+    assert_exact(r['spike'], g['spike'], 'spike')
+    for i, k in enumerate(('real', 'imag', 'threshold', 'refractory')):
+        assert_quantised_equal(r[k], g[f'dyn{i}'], S, k)
+    assert_close(r['grad_re'], g['grad_in0'], 'grad_re')
+    assert_close(r['grad_im'], g['grad_in1'], 'grad_im')
+    assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
+    assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
