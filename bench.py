@@ -127,6 +127,10 @@ WORKLOADS = {
     'delay_fir_fwd': Workload('delay_fir_fwd', (128, 16384, 1000), 8, 'elements/s'),
     'delay_fir_bwd': Workload('delay_fir_bwd', (128, 16384, 1000), 8, 'elements/s'),
 }
+# plain streaming kernel at the read:write mixes of the kernels above (sb_probe_stream): the HBM
+# ceiling a kernel with that mix can be held against.  One unit = one element of one stream.
+for _r, _w in ((1, 1), (1, 2), (1, 3), (2, 1), (3, 1), (2, 4), (4, 2)):
+    WORKLOADS[f'stream_{_r}r{_w}w'] = Workload(f'stream_{_r}r{_w}w', (64, 8192, 2000), 4 * (_r + _w), 'elements/s')
 
 
 def build_step(name, shape, device, seed):
@@ -139,6 +143,16 @@ def build_step(name, shape, device, seed):
     one = lambda v: torch.tensor([float(v)], device=device)  # noqa: E731
     zeros = torch.zeros(lead, device=device)
 
+    if name.startswith('stream_'):
+        from lava_dl_b200 import _native as N
+        r, w = int(name[7]), int(name[9])
+        n = int(np.prod(shape))
+        src = torch.zeros(r * n, device=device)
+        dst = torch.empty(w * n, device=device)
+
+        def step():
+            N.call('sb_probe_stream', src, N.ptr(src), N.ptr(dst), n, r, w, N.stream_of(src))
+        return step, 1, (src, dst)
     if name.startswith('cuba_fwd'):
         cd, vd = one(1024), one(123)
 
@@ -475,6 +489,9 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
+        if wl.name.startswith('stream_'):
+            print(json.dumps({'impl': 'reference', 'unavailable': 'the streaming probe has no CPU counterpart'}))
+            return
         cpu, sec = time_cpu(wl, max(1, args.steps), max(1, args.warmup))
         line = {
             'impl': 'reference', 'metric': f'neuron-steps/sec ({wl.name})' if wl.unit.startswith('neuron') else
@@ -580,7 +597,7 @@ def main():
                            'allreduce_elements': n_red,
                            'path': 'cuba.Neuron(requires_grad=True)(x).sum().backward() + one all-reduce of decay grads'}
         torch.cuda.empty_cache()
-    if rank == 0 and not args.no_cpu:
+    if rank == 0 and not args.no_cpu and not wl.name.startswith('stream_'):
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         line['cpu_baseline'] = cpu
     if dist is not None:

@@ -217,6 +217,13 @@ int sb_shift_fir_bwd(const float* grad_out, const float* lut, int64_t n_lut, flo
                      const float* filter, int64_t K, float sampling_time, float* grad_x, int64_t rows,
                      int64_t T, void* stream);
 
+/* ---- measurement aid ------------------------------------------------------------
+ * No counterpart in the reference and not on the hot path: a plain streaming
+ * kernel that reads `reads` streams of n floats (laid out back to back in `in`)
+ * and writes `writes` streams of n floats (back to back in `out`).  bench.py
+ * uses it to show what HBM delivers for the read:write mix of each kernel. */
+int sb_probe_stream(const float* in, float* out, int64_t n, int reads, int writes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
