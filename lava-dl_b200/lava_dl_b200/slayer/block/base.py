@@ -1,0 +1,129 @@
+"""Block scaffolding (``src/lava/lib/dl/slayer/block/base.py``): a block is
+``synapse -> neuron -> one-step delay -> optional learnable axonal delay``,
+optionally returning the mean event rate of its output."""
+
+import numpy as np
+import torch
+
+from ..axon import delay
+
+
+def step_delay(module, x):
+    """One time step of inter-layer communication delay (``block/base.py:15-39``).
+    With a persistent-state neuron the spike that falls off the end is kept and
+    re-enters at t = 0 of the next call."""
+    if not hasattr(module, 'delay_buffer'):
+        module.delay_buffer = None
+    persistent_state = hasattr(module, 'neuron') and module.neuron.persistent_state is True
+    if module.delay_buffer is not None and module.delay_buffer.shape[0] != x.shape[0]:
+        module.delay_buffer = None  # batch size changed
+    if persistent_state:
+        delay_buffer = 0 if module.delay_buffer is None else module.delay_buffer
+        module.delay_buffer = x[..., -1]
+    x = delay(x, 1)
+    if persistent_state:
+        x[..., 0] = delay_buffer
+    return x
+
+
+class _Block(torch.nn.Module):
+    """Common forward of every synapse + neuron block."""
+
+    def _init_block(self, neuron_params, synapse_params, delay_shift, count_log):
+        self.neuron_params = neuron_params
+        self.synapse_params = synapse_params
+        self.count_log = count_log
+        self.neuron = None
+        self.synapse = None
+        self.delay = None
+        self.delay_shift = delay_shift
+
+    def forward(self, x):
+        """``NCT`` or ``NCHWT`` input -> spikes (and event rate when ``count_log``)."""
+        mask = getattr(self, 'mask', None)
+        if mask is not None:
+            self.synapse.weight.data *= mask
+        z = self.synapse(x)
+        x = self.neuron(z)
+        if self.delay_shift is True:
+            x = step_delay(self, x)
+        if self.delay is not None:
+            x = self.delay(x)
+        if self.count_log is True:
+            return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    @property
+    def shape(self):
+        return self.neuron.shape
+
+
+class AbstractDense(_Block):
+    """Dense block; see ``synapse.Dense`` for the synapse arguments.
+
+    Parameters
+    ----------
+    neuron_params : dict
+    in_neurons, out_neurons : int
+    weight_scale, weight_norm, pre_hook_fx : synapse options
+    delay : bool
+        add a learnable axonal delay.
+    delay_shift : bool
+        apply the one-step inter-layer delay.
+    mask : bool tensor or None
+        synapse mask.
+    count_log : bool
+    """
+
+    def __init__(self, neuron_params, in_neurons, out_neurons, weight_scale=1, weight_norm=False,
+                 pre_hook_fx=None, delay=False, delay_shift=True, mask=None, count_log=False):
+        super().__init__()
+        self._init_block(neuron_params, dict(in_neurons=in_neurons, out_neurons=out_neurons,
+                                             weight_scale=weight_scale, weight_norm=weight_norm,
+                                             pre_hook_fx=pre_hook_fx), delay_shift, count_log)
+        if mask is None:
+            self.mask = None
+        else:
+            self.register_buffer('mask', mask.reshape(mask.shape[0], mask.shape[1], 1, 1, 1))
+
+
+class AbstractConv(_Block):
+    """Convolution block; see ``synapse.Conv`` for the synapse arguments."""
+
+    def __init__(self, neuron_params, in_features, out_features, kernel_size, stride=1, padding=0, dilation=1,
+                 groups=1, weight_scale=1, weight_norm=False, pre_hook_fx=None, delay=False, delay_shift=True,
+                 count_log=False):
+        super().__init__()
+        self._init_block(neuron_params, dict(in_features=in_features, out_features=out_features,
+                                             kernel_size=kernel_size, stride=stride, padding=padding,
+                                             dilation=dilation, groups=groups, weight_scale=weight_scale,
+                                             weight_norm=weight_norm, pre_hook_fx=pre_hook_fx), delay_shift,
+                         count_log)
+
+
+class AbstractPool(_Block):
+    """Sum-pooling block; see ``synapse.Pool`` for the synapse arguments."""
+
+    def __init__(self, neuron_params, kernel_size, stride=None, padding=0, dilation=1, weight_scale=1,
+                 weight_norm=False, pre_hook_fx=None, delay=False, delay_shift=True, count_log=False):
+        super().__init__()
+        if 'norm' in neuron_params.keys():
+            neuron_params['norm'] = None
+        self._init_block(neuron_params, dict(kernel_size=kernel_size, stride=stride, padding=padding,
+                                             dilation=dilation, weight_scale=weight_scale, weight_norm=weight_norm,
+                                             pre_hook_fx=pre_hook_fx), delay_shift, count_log)
+
+
+class AbstractFlatten(torch.nn.Module):
+    """Flattens the spatial dimensions: ``NCHWT -> N(CHW)T``."""
+
+    def __init__(self, count_log=False):
+        super().__init__()
+        self.count_log = count_log
+        self.shape = None
+
+    def forward(self, x):
+        if self.shape is None:
+            self.shape = [int(np.prod(x.shape[1:-1])), 1, 1]
+        flat = x.reshape((x.shape[0], -1, x.shape[-1]))
+        return (flat, None) if self.count_log is True else flat

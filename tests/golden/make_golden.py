@@ -373,6 +373,44 @@ def main():
     save('neuron_adrfiz_shared', re_in=re_in, im_in=im_in,
          **iz_case(lambda: slayer.neuron.adrf_iz.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1, requires_grad=True), True))
 
+    # ------------------------------------------------------------------
+    # a small CUBA conv network built from the reference's blocks (the layer
+    # sequence of the full-network benchmark config, scaled down)
+    # ------------------------------------------------------------------
+    neuron_p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03, requires_grad=True)
+    blk = slayer.block.cuba
+    torch.manual_seed(99)
+    net = torch.nn.ModuleList([
+        blk.Pool(neuron_p, 4), blk.Conv(neuron_p, 2, 16, 5, padding=2, weight_scale=4), blk.Pool(neuron_p, 2),
+        blk.Conv(neuron_p, 16, 32, 3, padding=1, weight_scale=3), blk.Pool(neuron_p, 2), blk.Flatten(),
+        blk.Dense(neuron_p, 128, 64, weight_scale=3), blk.Dense(neuron_p, 64, 11, weight_scale=3, delay=True),
+    ])
+    x_net = (rand(2, 2, 32, 32, 40) < 0.08).float()
+    with torch.no_grad():  # first call: binds shapes, samples the random axonal delays
+        y = x_net
+        for layer in net:
+            y = layer(y)
+        net[7].delay.delay.data = torch.tensor([0., 1., 2., 3., 5., 7., 0., 4., 6., 1., 2.])
+    xin = x_net.clone().requires_grad_(True)
+    acts, y = {}, xin
+    for i, layer in enumerate(net):
+        y = layer(y)
+        acts[f'act{i}'] = y
+    g_net = randn(*y.shape)
+    (y * g_net).sum().backward()
+    net_arrays = dict(x=x_net, grad_out=g_net, grad_x=xin.grad, delay=net[7].delay.delay.data,
+                      grad_delay=net[7].delay.delay.grad, **acts)
+    for i, layer in enumerate(net):
+        if hasattr(layer, 'synapse'):
+            net_arrays[f'weight{i}'] = layer.synapse.weight.data
+            if layer.synapse.weight.grad is not None:
+                net_arrays[f'grad_weight{i}'] = layer.synapse.weight.grad
+        if hasattr(layer, 'neuron'):
+            for k in ('current_decay', 'voltage_decay'):
+                net_arrays[f'grad_{k}{i}'] = getattr(layer.neuron, k).grad
+    print('network spike counts per layer:', [int(acts[f'act{i}'].sum()) for i in range(len(net))])
+    save('network_cuba_conv', **net_arrays)
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

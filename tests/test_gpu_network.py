@@ -1,0 +1,87 @@
+"""A small CUBA conv network assembled from the block mirror, against the same
+network built from lava-dl's own blocks (tests/golden/network_cuba_conv.npz).
+
+Synaptic weights are quantised to multiples of 1/32 and the inputs of every
+synapse are 0/1 spikes, so every dendritic sum is exactly representable whatever
+the convolution algorithm or summation order: cuDNN on the GPU and the
+reference's CPU convolution feed identical values to the neurons, and the spike
+tensors of all eight layers must match bit for bit.  Gradients pass through
+cuDNN's backward kernels, whose summation order differs from the CPU's; they are
+compared with a relative L2 criterion (1e-4) instead of element-wise.  The decay
+gradients of the early layers are sums of ~10^5 signed products that cancel to
+values orders of magnitude below the products themselves (5e-13 in layer 0);
+they get 5e-3 here, while test_gpu_parity.py holds the same sums to 1e-5 of
+their term magnitudes on the kernels in isolation."""
+
+import numpy as np
+import pytest
+import torch
+
+from _util import assert_exact, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a = a.detach().cpu().numpy().astype(np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+
+
+def build(slayer, cuda):
+    p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03, requires_grad=True)
+    blk = slayer.block.cuba
+    return torch.nn.ModuleList([
+        blk.Pool(p, 4), blk.Conv(p, 2, 16, 5, padding=2, weight_scale=4), blk.Pool(p, 2),
+        blk.Conv(p, 16, 32, 3, padding=1, weight_scale=3), blk.Pool(p, 2), blk.Flatten(),
+        blk.Dense(p, 128, 64, weight_scale=3), blk.Dense(p, 64, 11, weight_scale=3, delay=True),
+    ]).to(cuda)
+
+
+def test_network_matches_reference_blocks(cuda):
+    import lava_dl_b200.slayer as slayer
+    g = load_golden('network_cuba_conv')
+    net = build(slayer, cuda)
+    x = torch.tensor(g['x'], device=cuda)
+    with torch.no_grad():
+        y = x
+        for layer in net:  # binds shapes and creates the delay parameter
+            y = layer(y)
+        for i, layer in enumerate(net):
+            if hasattr(layer, 'synapse'):
+                layer.synapse.weight.data = torch.tensor(g[f'weight{i}'], device=cuda)
+        net[7].delay.delay.data = torch.tensor(g['delay'], device=cuda)
+
+    xin = x.clone().requires_grad_(True)
+    y = xin
+    for i, layer in enumerate(net):
+        y = layer(y)
+        assert_exact(y, g[f'act{i}'], f'layer {i} output')
+    (y * torch.tensor(g['grad_out'], device=cuda)).sum().backward()
+
+    assert rel_l2(xin.grad, g['grad_x']) < 1e-4
+    for i, layer in enumerate(net):
+        if f'grad_weight{i}' in g:
+            assert rel_l2(layer.synapse.weight.grad, g[f'grad_weight{i}']) < 1e-4, f'weight grad of layer {i}'
+        if hasattr(layer, 'neuron'):
+            for k in ('current_decay', 'voltage_decay'):
+                assert rel_l2(getattr(layer.neuron, k).grad, g[f'grad_{k}{i}']) < 5e-3, f'{k} grad of layer {i}'
+    assert rel_l2(net[7].delay.delay.grad, g['grad_delay']) < 1e-4
+
+
+def test_count_log_and_persistent_step_delay(cuda):
+    import lava_dl_b200.slayer as slayer
+    p = dict(threshold=1.0, current_decay=0.5, voltage_decay=0.1, persistent_state=True)
+    block = slayer.block.cuba.Dense(p, 6, 4, weight_scale=8, count_log=True).to(cuda)
+    gen = torch.Generator().manual_seed(3)
+    x = (torch.rand(2, 6, 64, generator=gen) < 0.3).float().to(cuda)
+    with torch.no_grad():
+        full, rate = block(x)
+        assert 0 <= float(rate) <= 1 and abs(float(rate) - float((full > 0).float().mean())) < 1e-7
+        for name, buf in block.neuron.named_buffers():
+            if name.endswith('_state'):
+                buf.zero_()
+        block.delay_buffer = None
+        a, _ = block(x[..., :30].contiguous())
+        b, _ = block(x[..., 30:].contiguous())
+    assert_exact(torch.cat([a, b], dim=-1), full, 'chunked run with carried state and delay buffer')
