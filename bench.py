@@ -82,6 +82,8 @@ class Workload:
         self.name, self.shape, self.bpu, self.unit = name, shape, bytes_per_unit, unit
 
     def units(self, shape):
+        if self.name.startswith('cfg4'):
+            return shape[0] * shape[-1] * CFG4_NEURONS
         return int(np.prod(shape))
 
 
@@ -127,6 +129,12 @@ WORKLOADS = {
     'delay_fir_fwd': Workload('delay_fir_fwd', (128, 16384, 1000), 8, 'elements/s'),
     'delay_fir_bwd': Workload('delay_fir_bwd', (128, 16384, 1000), 8, 'elements/s'),
 }
+# full CUBA conv network of the last benchmark config (blocks = cuDNN synapse + fused neuron kernel +
+# one-step delay); units = neuron-steps over all seven spiking layers (33291 neurons per sample)
+WORKLOADS['cfg4_fwd'] = Workload('cfg4_fwd', (32, 2, 128, 128, 300), 0)
+WORKLOADS['cfg4_train'] = Workload('cfg4_train', (32, 2, 128, 128, 300), 0)
+CFG4_NEURONS = 2048 + 16384 + 4096 + 8192 + 2048 + 512 + 11
+
 # plain streaming kernel at the read:write mixes of the kernels above (sb_probe_stream): the HBM
 # ceiling a kernel with that mix can be held against.  One unit = one element of one stream.
 for _r, _w in ((1, 1), (1, 2), (1, 3), (2, 1), (3, 1), (2, 4), (4, 2)):
@@ -143,6 +151,43 @@ def build_step(name, shape, device, seed):
     one = lambda v: torch.tensor([float(v)], device=device)  # noqa: E731
     zeros = torch.zeros(lead, device=device)
 
+    if name.startswith('cfg4'):
+        import lava_dl_b200.slayer as slayer
+        from lava_dl_b200 import _dist
+        train = name == 'cfg4_train'
+        p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03)
+        blk = slayer.block.cuba
+        torch.manual_seed(seed)
+        net = torch.nn.ModuleList([
+            blk.Pool(p, 4), blk.Conv(p, 2, 16, 5, padding=2), blk.Pool(p, 2), blk.Conv(p, 16, 32, 3, padding=1),
+            blk.Pool(p, 2), blk.Flatten(), blk.Dense(p, 2048, 512), blk.Dense(p, 512, 11),
+        ]).to(device)
+        for layer in net:
+            if hasattr(layer, 'synapse') and layer.synapse.weight.requires_grad:
+                torch.nn.init.normal_(layer.synapse.weight, 0.0, 0.1)
+        gen = torch.Generator(device=device).manual_seed(seed)
+        x = (torch.rand(shape, device=device, generator=gen) < 0.02).float()
+        params = [q for q in net.parameters() if q.requires_grad]
+
+        def forward():
+            y = x
+            for layer in net:
+                y = layer(y)
+            return y
+
+        if not train:
+            def step():
+                with torch.no_grad():
+                    return forward()
+            return step, 14, (net, x)
+
+        def step():
+            for q in params:
+                q.grad = None
+            forward().sum().backward()
+            _dist.allreduce_param_grads(params)
+        # 7 fused forward + 7 one-step shifts, 7 fused backward + 7 reverse shifts
+        return step, 28, (net, x)
     if name.startswith('stream_'):
         from lava_dl_b200 import _native as N
         r, w = int(name[7]), int(name[9])
@@ -489,8 +534,8 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        if wl.name.startswith('stream_'):
-            print(json.dumps({'impl': 'reference', 'unavailable': 'the streaming probe has no CPU counterpart'}))
+        if wl.name.startswith(('stream_', 'cfg4')):
+            print(json.dumps({'impl': 'reference', 'unavailable': 'no CPU port of this workload (probe / full network)'}))
             return
         cpu, sec = time_cpu(wl, max(1, args.steps), max(1, args.warmup))
         line = {
@@ -543,7 +588,7 @@ def main():
     value = units * world / (ms_per_step * 1e-3)
 
     peak, peak_kind = peaks()
-    kern_ms = statistics.mean(per) / launches_per_step
+    kern_ms = statistics.mean(per) / (1 if wl.name.startswith('cfg4') else launches_per_step)
     achieved = wl.bpu * units / (kern_ms * 1e-3) / 1e9
     tpu = NCU_TRAFFIC_PER_UNIT.get(wl.name)
     roofline = {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
@@ -597,7 +642,10 @@ def main():
                            'allreduce_elements': n_red,
                            'path': 'cuba.Neuron(requires_grad=True)(x).sum().backward() + one all-reduce of decay grads'}
         torch.cuda.empty_cache()
-    if rank == 0 and not args.no_cpu and not wl.name.startswith('stream_'):
+    if wl.name.startswith('cfg4'):
+        line['roofline'] = None  # a network of cuDNN synapses and neuron kernels has no single roof
+        line['config']['network'] = 'Pool4-Conv(2,16,5)-Pool2-Conv(16,32,3)-Pool2-Flatten-Dense(2048,512)-Dense(512,11), CUBA'
+    if rank == 0 and not args.no_cpu and not wl.name.startswith(('stream_', 'cfg4')):
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         line['cpu_baseline'] = cpu
     if dist is not None:

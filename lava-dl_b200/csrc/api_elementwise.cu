@@ -182,7 +182,7 @@ shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ lut, int
 
 Surrogate surrogate_consts(float tau_rho, float scale_rho, bool graded) {
   Surrogate s;
-  s.tau = tau_rho;
+  s.k2 = (float)(1.4426950408889634 / (double)tau_rho);
   volatile float half = scale_rho / 2.0f;
   volatile float c = half / tau_rho;
   s.c0 = graded ? scale_rho : c;
@@ -191,7 +191,7 @@ Surrogate surrogate_consts(float tau_rho, float scale_rho, bool graded) {
 
 CSurrogate csurrogate_consts(float tau_rho, float scale_rho) {
   CSurrogate s;
-  s.tau = tau_rho;
+  s.k2 = (float)(1.4426950408889634 / (double)tau_rho);
   s.scale_rho = scale_rho;
   volatile float a = 0.5f / tau_rho;
   volatile float b = 2.0f * tau_rho;

@@ -23,7 +23,7 @@ static bool counts_ok(std::initializer_list<int64_t> v, int64_t nmax) {
 static Surrogate make_surrogate(float tau_rho, float scale_rho, bool graded) {
   // fp32 arithmetic in the order spike/spike.py:10-23 applies it to 0-dim fp32 tensors
   Surrogate s;
-  s.tau = tau_rho;
+  s.k2 = (float)(1.4426950408889634 / (double)tau_rho);
   volatile float half = scale_rho / 2.0f;
   volatile float c = half / tau_rho;
   s.c0 = graded ? scale_rho : c;
@@ -33,7 +33,7 @@ static Surrogate make_surrogate(float tau_rho, float scale_rho, bool graded) {
 static CSurrogate make_csurrogate(float tau_rho, float scale_rho) {
   // spike/complex.py:144-167, again in fp32
   CSurrogate s;
-  s.tau = tau_rho;
+  s.k2 = (float)(1.4426950408889634 / (double)tau_rho);
   s.scale_rho = scale_rho;
   volatile float a = 0.5f / tau_rho;
   volatile float b = 2.0f * tau_rho;

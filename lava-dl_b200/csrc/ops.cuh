@@ -47,20 +47,25 @@ __device__ __forceinline__ float load_decay(const DecayVec& d, const RowGeom& g,
 // Surrogate gradient of the spike function, spike/spike.py:10-23.
 //   binary: scale_rho / 2 / tau_rho * exp(-|v - thr| / tau_rho)
 //   graded: scale_rho * exp(min(v - thr, 0) / tau_rho)
+// exp(x / tau) is evaluated as 2^(x * log2(e) / tau) with the constant folded
+// on the host: one multiply and one MUFU.EX2 instead of an IEEE divide plus
+// expf.  The result differs from the divide-then-exp form by at most
+// (2 + |x / tau|) ulp, far inside the 1e-5 relative bound on gradients, and
+// the backward kernels drop from 36 to about 24 instructions per step.
 struct Surrogate {
-  float c0;    // binary: (scale_rho / 2) / tau_rho ; graded: scale_rho
-  float tau;
+  float c0;        // binary: (scale_rho / 2) / tau_rho ; graded: scale_rho
+  float k2;        // log2(e) / tau_rho
 };
 template <bool GRADED>
 __device__ __forceinline__ float surrogate(const Surrogate& s, float v, float thr) {
   const float d = __fsub_rn(v, thr);
-  if (GRADED) return __fmul_rn(s.c0, expf(__fdiv_rn(fminf(d, 0.f), s.tau)));
-  return __fmul_rn(s.c0, expf(__fdiv_rn(-fabsf(d), s.tau)));
+  const float x = GRADED ? fminf(d, 0.f) : -fabsf(d);
+  return __fmul_rn(s.c0, exp2f(__fmul_rn(x, s.k2)));
 }
 
 // Gradients of the phase-threshold (complex) spike, spike/complex.py:144-167.
 struct CSurrogate {
-  float tau;
+  float k2;             // log2(e) / tau_rho
   float scale_rho;
   float half_over_tau;  // (1 / 2) / tau_rho
   float two_tau;        // 2 * tau_rho
@@ -71,9 +76,9 @@ template <bool GRADED>
 __device__ __forceinline__ void csurrogate(const CSurrogate& s, float re, float im, float thr, float& d_re,
                                            float& d_im) {
   float delta_real;
-  if (GRADED) delta_real = expf(__fdiv_rn(-fmaxf(__fsub_rn(thr, re), 0.f), s.tau));
-  else delta_real = __fmul_rn(s.half_over_tau, expf(__fdiv_rn(-fabsf(__fsub_rn(re, thr)), s.tau)));
-  const float delta_imag = __fmul_rn(s.half_over_tau, expf(__fdiv_rn(-fabsf(im), s.tau)));
+  if (GRADED) delta_real = exp2f(__fmul_rn(-fmaxf(__fsub_rn(thr, re), 0.f), s.k2));
+  else delta_real = __fmul_rn(s.half_over_tau, exp2f(__fmul_rn(-fabsf(__fsub_rn(re, thr)), s.k2)));
+  const float delta_imag = __fmul_rn(s.half_over_tau, exp2f(__fmul_rn(-fabsf(im), s.k2)));
   const float step_real = __fmul_rn(
       0.5f, __fadd_rn(1.f, __fmul_rn(sgnf(__fsub_rn(re, thr)), __fsub_rn(1.f, __fmul_rn(s.two_tau, delta_real)))));
   d_re = __fmul_rn(__fmul_rn(s.scale_rho, delta_real), delta_imag);
