@@ -217,6 +217,18 @@ int sb_shift_fir_bwd(const float* grad_out, const float* lut, int64_t n_lut, flo
                      const float* filter, int64_t K, float sampling_time, float* grad_x, int64_t rows,
                      int64_t T, void* stream);
 
+/* ---- sum-pooling synapse (next to the path: what feeds the neurons in conv networks) ----
+ * Replaces the Conv3d call of synapse/layer.py:438-508 for the default pooling
+ * geometry (stride = kernel, no padding, no dilation).  x is [NC, H, W, T] with
+ * NC = batch * channels, y is [NC, Ho, Wo, T], weight is the (kh, kw) kernel
+ * (after the pre-hook), row-major.  Windows reaching past H or W read zeros,
+ * as the reference's zero padding of odd sizes does.
+ * y[nc,ho,wo,t] = sum_ij w[i,j] * x[nc, ho*kh+i, wo*kw+j, t]; bwd is its adjoint. */
+int sb_pool_fwd(const float* x, const float* weight, float* y, int64_t NC, int64_t H, int64_t W, int64_t Ho,
+                int64_t Wo, int64_t kh, int64_t kw, int64_t T, void* stream);
+int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t NC, int64_t H, int64_t W,
+                int64_t Ho, int64_t Wo, int64_t kh, int64_t kw, int64_t T, void* stream);
+
 /* ---- measurement aid ------------------------------------------------------------
  * No counterpart in the reference and not on the hot path: a plain streaming
  * kernel that reads `reads` streams of n floats (laid out back to back in `in`)

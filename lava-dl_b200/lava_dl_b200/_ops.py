@@ -430,3 +430,38 @@ def rf_bwd(grad_spike, re, im, threshold, sin_decay, cos_decay, tau_rho, scale_r
     if need_param_grad:
         return gre, gim, gs.reshape(sin_decay.shape), gc.reshape(cos_decay.shape)
     return gre, gim, None, None
+
+
+# --------------------------------------------------------------------------
+# sum-pooling synapse
+# --------------------------------------------------------------------------
+def pool_out_size(size, k):
+    """Output length of the reference's pooling: it pads ``size % k`` zeros when the
+    size is not a multiple of the window and then strides by the window."""
+    padded = size + (size % k)
+    return (padded - k) // k + 1 if padded >= k else 0
+
+
+def pool_fwd(x, weight):
+    """x: [N, C, H, W, T]; weight: [..., kh, kw, 1] kernel (already hooked)."""
+    N.require_cuda(x)
+    x = _c(x)
+    n, c, h, w, t = x.shape
+    kh, kw = int(weight.shape[-3]), int(weight.shape[-2])
+    wgt = _c(weight.detach().to(device=x.device, dtype=torch.float32).reshape(-1))
+    ho, wo = pool_out_size(h, kh), pool_out_size(w, kw)
+    y = torch.empty((n, c, ho, wo, t), device=x.device, dtype=torch.float32)
+    N.call('sb_pool_fwd', x, N.ptr(x), N.ptr(wgt), N.ptr(y), n * c, h, w, ho, wo, kh, kw, t, N.stream_of(x))
+    return y
+
+
+def pool_bwd(grad_y, weight, in_shape):
+    N.require_cuda(grad_y)
+    grad_y = _c(grad_y)
+    n, c, h, w, t = in_shape
+    kh, kw = int(weight.shape[-3]), int(weight.shape[-2])
+    wgt = _c(weight.detach().to(device=grad_y.device, dtype=torch.float32).reshape(-1))
+    gx = torch.empty(in_shape, device=grad_y.device, dtype=torch.float32)
+    N.call('sb_pool_bwd', grad_y, N.ptr(grad_y), N.ptr(wgt), N.ptr(gx), n * c, h, w, grad_y.shape[2], grad_y.shape[3],
+           kh, kw, t, N.stream_of(grad_y))
+    return gx

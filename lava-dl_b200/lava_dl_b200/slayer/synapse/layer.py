@@ -7,6 +7,8 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
+from ... import _ops
+
 
 def _hw(value, what, third):
     """int or (h, w) -> (h, w, third)."""
@@ -114,6 +116,22 @@ class Conv(torch.nn.Conv3d, GenericLayer):
                         self.groups)
 
 
+class _SumPool(torch.autograd.Function):
+    """Sum pooling with stride = window through the gather-and-add kernel; the
+    (fixed) pooling weights get no gradient."""
+
+    @staticmethod
+    def forward(ctx, input, weight):
+        ctx.save_for_backward(weight)
+        ctx.in_shape = tuple(input.shape)
+        return _ops.pool_fwd(input, weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (weight,) = ctx.saved_tensors
+        return _ops.pool_bwd(grad_output, weight, ctx.in_shape), None
+
+
 class Pool(torch.nn.Conv3d, GenericLayer):
     """Sum pooling with a fixed all-``weight_scale`` kernel, applied per channel."""
 
@@ -130,7 +148,14 @@ class Pool(torch.nn.Conv3d, GenericLayer):
         if weight_norm is True:
             self.enable_weight_norm()
 
+    def _plain_geometry(self):
+        return (tuple(self.stride) == tuple(self.kernel_size) and tuple(self.padding) == (0, 0, 0)
+                and tuple(self.dilation) == (1, 1, 1) and self.kernel_size[0] * self.kernel_size[1] <= 64)
+
     def forward(self, input):
+        if input.is_cuda and input.dim() == 5 and self._plain_geometry() and not self.weight.requires_grad \
+                and not self.weight_norm_enabled:
+            return _SumPool.apply(input, self._hooked_weight())
         # the reference pads odd spatial sizes with (size % kernel) zero rows / columns
         # (synapse/layer.py:438-460); kept as is
         for dim in (2, 3):

@@ -85,3 +85,32 @@ def test_count_log_and_persistent_step_delay(cuda):
         a, _ = block(x[..., :30].contiguous())
         b, _ = block(x[..., 30:].contiguous())
     assert_exact(torch.cat([a, b], dim=-1), full, 'chunked run with carried state and delay buffer')
+
+
+@pytest.mark.parametrize('shape,k', [((2, 3, 8, 8, 40), 2), ((1, 2, 5, 7, 12), 2), ((2, 1, 6, 9, 33), 4),
+                                     ((1, 1, 12, 12, 7), (3, 2)), ((2, 2, 4, 4, 1), 4)])
+def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
+    """The gather-and-add pooling kernel against the Conv3d formulation it replaces
+    (same module, fall-back path), forward and backward, odd sizes included.  (Sizes
+    whose padded height is still not a multiple of the window make the reference's
+    own reshape fail, synapse/layer.py:493-507, so they are not comparable.)"""
+    import lava_dl_b200.slayer as slayer
+    gen = torch.Generator().manual_seed(sum(shape))
+    pool = slayer.synapse.Pool(k, weight_scale=2).to(cuda)
+    with torch.no_grad():  # non-uniform multiples of 1/32 so every sum is exact in fp32
+        pool.weight.copy_(torch.randint(-64, 64, pool.weight.shape, generator=gen).float().to(cuda) / 32)
+    x = (torch.rand(shape, generator=gen) < 0.3).float().to(cuda)
+    xa = x.clone().requires_grad_(True)
+    xb = x.clone().requires_grad_(True)
+    fast = pool(xa)
+    assert fast.grad_fn is not None and 'SumPool' in type(fast.grad_fn).__name__
+    pool.padding = (0, 0, 0)
+    pool.weight.requires_grad_(True)  # makes forward() take the Conv3d path
+    slow = pool(xb)
+    pool.weight.requires_grad_(False)
+    assert 'SumPool' not in type(slow.grad_fn).__name__
+    assert_exact(fast, slow, 'pooled sums')
+    g = torch.randint(-8, 8, fast.shape, generator=gen).float().to(cuda) / 4
+    fast.backward(g)
+    slow.backward(g)
+    assert_exact(xa.grad, xb.grad, 'pool input gradient')
