@@ -179,15 +179,15 @@ def build_step(name, shape, device, seed):
             def step():
                 with torch.no_grad():
                     return forward()
-            return step, 14, (net, x)
+            return step, 10, (net, x)  # 7 fused neuron kernels (delay folded in) + 3 pooling kernels
 
         def step():
             for q in params:
                 q.grad = None
             forward().sum().backward()
             _dist.allreduce_param_grads(params)
-        # 7 fused forward + 7 one-step shifts, 7 fused backward + 7 reverse shifts
-        return step, 28, (net, x)
+        # forward as above, backward: 7 fused neuron kernels + 3 pooling adjoints
+        return step, 20, (net, x)
     if name.startswith('stream_'):
         from lava_dl_b200 import _native as N
         r, w = int(name[7]), int(name[9])

@@ -155,18 +155,26 @@ int sb_cspike_bwd(const float* re, const float* im, const float* thr_tensor, flo
  * CUBA (neuron/cuba.py:274-421): thr = fp32(threshold + eps).
  * Outputs: current (nullable), voltage, spike (nullable);
  * final_c/final_v/final_s (nullable float[rows]) = last time bin of
- * current, voltage (before reset) and spike. */
+ * current, voltage (before reset) and spike.
+ * spike_delay = 1 (binary spikes only) writes the spike series one step late,
+ * spike_out[t] = spike[t-1], which is the one-step inter-layer delay of the
+ * blocks (block/base.py:15-39) at no extra memory traffic; delay_head
+ * (nullable float[rows]) supplies spike_out[0], else 0.  final_s stays the
+ * undelayed last spike. */
 int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
                 float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
-                int w_scale, int graded, float spike_scale, void* stream);
+                int w_scale, int graded, float spike_scale, int spike_delay, const float* delay_head,
+                void* stream);
 /* Backward of CUBA and ALIF forward: surrogate gradient + both integrators.
  * thr_tensor (nullable): per-element threshold (ALIF passes th + ref).
- * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch. */
+ * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch.
+ * spike_delay = 1: grad_spike is the gradient of the one-step-late series. */
 int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
                 const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
                 int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,
-                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream);
+                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, int spike_delay,
+                void* stream);
 
 /* ALIF (neuron/alif.py:383-591).  mode 0: forward() -> spike, voltage,
  * thsum = threshold + refractory.  mode 1: dynamics() -> current, voltage,

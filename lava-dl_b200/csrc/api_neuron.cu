@@ -49,8 +49,12 @@ extern "C" {
 int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
                 float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
-                int w_scale, int graded, float spike_scale, void* stream) {
+                int w_scale, int graded, float spike_scale, int spike_delay, const float* delay_head,
+                void* stream) {
   RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || (spike_delay == 1 && spike != nullptr && !graded),
+             "the fused one-step delay needs binary spike output");
+  const BitDelay bd{spike_delay, delay_head};
   SB_TRY(check_count(n_cdecay, "current decay"));
   SB_TRY(check_count(n_vdecay, "voltage decay"));
   const int64_t nmax = maxn({n_cdecay, n_vdecay});
@@ -77,7 +81,7 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
     if (C) out[no++] = current;                                                                     \
     out[no++] = voltage;                                                                            \
     if (S) out[no++] = spike;                                                                       \
-    return launch_rowscan<CubaFwd<C, S, G>>(p, rg, in, out, st);                                    \
+    return launch_rowscan<CubaFwd<C, S, G>>(p, rg, in, out, st, bd);                                \
   }
   if (current) {
     if (spike) { if (graded) SB_GO(true, true, true) else SB_GO(true, true, false) }
@@ -92,8 +96,10 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
 int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
                 const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
                 int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,
-                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream) {
+                void* scratch_v, const sb_geom* g, float tau_rho, float scale_rho, int graded, int spike_delay,
+                void* stream) {
   RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || spike_delay == 1, "spike_delay is 0 or 1");
   SB_TRY(check_count(n_cdecay, "current decay"));
   SB_TRY(check_count(n_vdecay, "voltage decay"));
   const int64_t nmax = maxn({n_cdecay, n_vdecay});
@@ -116,7 +122,7 @@ int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_
 #define SB_GO(TT, G, D)                                                                             \
   {                                                                                                 \
     typename CubaBwd<TT, G, D>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, sg, thr,           \
-                                         (double*)scratch_c, (double*)scratch_v};                   \
+                                         (double*)scratch_c, (double*)scratch_v, spike_delay};      \
     const float* in[4];                                                                             \
     int ni = 0;                                                                                     \
     in[ni++] = grad_spike;                                                                          \

@@ -507,13 +507,16 @@ struct CubaBwd {
     float thr;            // scalar threshold (fp32), ignored with a tensor threshold
     double* partial_c;    // scratch for grad of current decay
     double* partial_v;    // scratch for grad of voltage decay
+    int spike_delay;      // 1: the forward wrote spikes one step late, so g_spike[t] is read from t + 1
   };
-  float ac, av, gv, gx, thr;
+  float ac, av, gv, gx, thr, gnext;
+  bool delayed;
   Surrogate sg;
   GradAcc accc, accv;
 
   __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
     gv = gx = 0.f; ac = av = 0.f; thr = p.thr; sg = p.sg; accc.reset(); accv.reset();
+    gnext = 0.f; delayed = p.spike_delay != 0;
     if (valid) {
       ac = __fsub_rn(1.f, __fdiv_rn(load_decay(p.cdecay, g, row), 4096.f));
       av = __fsub_rn(1.f, __fdiv_rn(load_decay(p.vdecay, g, row), 4096.f));
@@ -522,7 +525,10 @@ struct CubaBwd {
   __device__ __forceinline__ void step(const float (&a)[NIN], float (&b)[1]) {
     const float vol = a[1];
     const float th = TENSOR_THR ? a[ITH] : thr;
-    const float gs = __fmul_rn(surrogate<GRADED>(sg, vol, th), a[0]);
+    // the scan runs backwards, so the gradient of the delayed spike (time t + 1) was the previous input
+    const float gin = delayed ? gnext : a[0];
+    gnext = a[0];
+    const float gs = __fmul_rn(surrogate<GRADED>(sg, vol, th), gin);
     if (DGRAD) {
       accv.add(__fmul_rn(gv, vol));
       accc.add(__fmul_rn(gx, a[ICUR]));

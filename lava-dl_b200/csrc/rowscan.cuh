@@ -104,9 +104,20 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // box).  Row by row, every lane fetches that row's masks and the warp writes
 // the row's NB * TW steps as coalesced 0.f / 1.f values.
 // ---------------------------------------------------------------------------
+// delay = 1 writes every bit output one step late (out[t] = bit[t - 1]): the
+// one-step inter-layer delay of lava-dl's blocks (block/base.py:15-39) folded
+// into the store.  The bit that enters at t = 0 is head[row] != 0 (the spike a
+// persistent-state block carried over from its previous call), 0 without head.
 template <int N>
 struct BitPtrs {
   float* p[N > 0 ? N : 1];
+  const float* head;
+  int delay;
+};
+
+struct BitDelay {
+  int steps;          // 0 or 1
+  const float* head;  // [rows] or null
 };
 
 template <int NB, int TW>
@@ -207,6 +218,9 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
   const bool valid = row < g.rows;
   op.init(p, g, row, valid);
 
+  uint32_t carry = 0u;  // last bit of the previous box when bit outputs are delayed by one step
+  if (NBIT > 0 && bitout.delay && bitout.head != nullptr && valid) carry = (__ldg(bitout.head + row) != 0.f) ? 1u : 0u;
+
   int issued = 0;
   if (lane == 0) {
     for (; issued < STAGES - 1 && issued < ntiles; ++issued) issue_load(issued);
@@ -232,6 +246,11 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
         if (nvalid >= kTileT) process_tile<Op, true, TW>(op, box, lane, kTileT, boxbits);
         else process_tile<Op, false, TW>(op, box, lane, nvalid, boxbits);
         op.tile_end();
+      }
+      if (NBIT > 0 && bitout.delay) {  // forward ops only: boxes come in time order
+        const uint32_t m = boxbits[0];
+        boxbits[0] = (m << 1) | carry;
+        carry = (m >> (TW - 1)) & 1u;
       }
 #pragma unroll
       for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) bits[d][b] = boxbits[d];
@@ -281,8 +300,8 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
 // ---------------------------------------------------------------------------
 template <class Op>
 __global__ void __launch_bounds__(128)
-rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::Params p, const RowGeom g,
-                     unsigned int* status) {
+rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, const typename Op::Params p,
+                     const RowGeom g, unsigned int* status) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
   extern __shared__ uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -300,6 +319,9 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::P
   const int64_t row = row0 + lane;
   const bool valid = row < g.rows;
   op.init(p, g, row, valid);
+
+  uint32_t carry = 0u;
+  if (NBIT > 0 && bd.steps && bd.head != nullptr && valid) carry = (__ldg(bd.head + row) != 0.f) ? 1u : 0u;
 
   for (int k = 0; k < ntiles; ++k) {
     const int t0 = (Op::REVERSE ? (ntiles - 1 - k) : k) * kTileT;
@@ -322,6 +344,11 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const typename Op::P
     if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT, bits);
     else process_tile<Op, false, 32>(op, stage, lane, nvalid, bits);
     op.tile_end();
+    if (NBIT > 0 && bd.steps) {
+      const uint32_t m = bits[0];
+      bits[0] = (m << 1) | carry;
+      carry = (m >> 31) & 1u;
+    }
     __syncwarp();
 #pragma unroll
     for (int o = 0; o < NOUT; ++o) {
@@ -374,7 +401,7 @@ template <class Op> constexpr int pipe_tile() { return Op::TILE; }
 
 template <class Op, int STAGES = pipe_stages<Op>(), int NB = pipe_boxes<Op>(), int TW = pipe_tile<Op>()>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
-                   cudaStream_t st) {
+                   cudaStream_t st, BitDelay bit_delay = BitDelay{0, nullptr}) {
   // NOUT counts the outputs that travel through shared memory; the NBIT bit
   // outputs follow them in `out`.
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
@@ -385,8 +412,12 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
   for (int i = 0; i < NIN; ++i) all[i] = in[i];
   for (int o = 0; o < NOUT; ++o) all[NIN + o] = out[o];
   for (int i = 0; i < NIN + NOUT; ++i) SB_REQUIRE(all[i] != nullptr, "null tensor pointer (slot %d)", i);
+  SB_REQUIRE(bit_delay.steps == 0 || (bit_delay.steps == 1 && NBIT == 1 && !Op::REVERSE),
+             "a one-step output delay exists only for ops with one bit output");
   BitPtrs<NBIT> bitout;
   bitout.p[0] = nullptr;
+  bitout.head = bit_delay.head;
+  bitout.delay = bit_delay.steps;
   for (int d = 0; d < NBIT; ++d) {
     SB_REQUIRE(out[NOUT + d] != nullptr, "null tensor pointer (bit output %d)", d);
     bitout.p[d] = out[NOUT + d];
@@ -415,7 +446,7 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
     auto fn = rowscan_plain_kernel<Op>;
     int rc = prepare_kernel((const void*)fn, lp.smem);
     if (rc != SB_OK) return rc;
-    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(ptrs, p, g, status);
+    fn<<<(unsigned)lp.ctas, lp.warps_per_cta * 32, lp.smem, st>>>(ptrs, bit_delay, p, g, status);
   }
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -318,8 +318,9 @@ def _vec(shape_like):
 
 
 def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current, want_spike, graded=False,
-             spike_scale=1.0):
-    """Returns dict with current/voltage/spike series and final_c/final_v/final_s."""
+             spike_scale=1.0, spike_delay=0, delay_head=None):
+    """Returns dict with current/voltage/spike series and final_c/final_v/final_s.
+    ``spike_delay=1`` returns the spike series one step late (``delay_head`` fills t = 0)."""
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
@@ -330,13 +331,15 @@ def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current
     fc, fv = _vec(x), _vec(x)
     fs = _vec(x) if want_spike else None
     g = geom(x, cd.numel(), vd.numel())
+    head = None if delay_head is None else row_state(delay_head, x)
     N.call('sb_cuba_fwd', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(cs), N.ptr(vs),
            N.ptr(cur), N.ptr(vol), N.ptr(spk), N.ptr(fc), N.ptr(fv), N.ptr(fs), g, float(threshold), int(w_scale),
-           int(bool(graded)), float(spike_scale), N.stream_of(x))
+           int(bool(graded)), float(spike_scale), int(spike_delay), N.ptr(head), N.stream_of(x))
     return dict(current=cur, voltage=vol, spike=spk, final_c=fc, final_v=fv, final_s=fs)
 
 
-def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_decay_grad):
+def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_decay_grad,
+             spike_delay=0):
     N.require_cuda(grad_spike, voltage)
     grad_spike, voltage = _c(grad_spike), _c(voltage)
     cd, vd = _param(cdecay, voltage), _param(vdecay, voltage)
@@ -353,7 +356,7 @@ def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, s
     N.call('sb_cuba_bwd', voltage, N.ptr(grad_spike), N.ptr(voltage), N.ptr(tt), ts,
            N.ptr(current) if need_decay_grad else None, N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(gx),
            N.ptr(gcd), N.ptr(gvd), N.ptr(sc), N.ptr(sv), g, f32(tau_rho), f32(scale_rho), int(bool(graded)),
-           N.stream_of(voltage))
+           int(spike_delay), N.stream_of(voltage))
     if need_decay_grad:
         return gx, gcd.reshape(cdecay.shape), gvd.reshape(vdecay.shape)
     return gx, None, None

@@ -44,13 +44,31 @@ class _Block(torch.nn.Module):
         if mask is not None:
             self.synapse.weight.data *= mask
         z = self.synapse(x)
-        x = self.neuron(z)
-        if self.delay_shift is True:
-            x = step_delay(self, x)
+        if self.delay_shift is True and getattr(self.neuron, 'fuses_step_delay', False):
+            x = self._neuron_with_step_delay(z)
+        else:
+            x = self.neuron(z)
+            if self.delay_shift is True:
+                x = step_delay(self, x)
         if self.delay is not None:
             x = self.delay(x)
         if self.count_log is True:
             return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    def _neuron_with_step_delay(self, z):
+        """``step_delay(self, self.neuron(z))`` in one kernel: the neuron writes its
+        spikes one step late; the spike carried over between calls of a
+        persistent-state neuron enters at t = 0."""
+        if not hasattr(self, 'delay_buffer'):
+            self.delay_buffer = None
+        persistent_state = self.neuron.persistent_state is True
+        if self.delay_buffer is not None and self.delay_buffer.shape[0] != z.shape[0]:
+            self.delay_buffer = None
+        head = self.delay_buffer if persistent_state else None
+        x, last_spike = self.neuron.forward_step_delayed(z, head)
+        if persistent_state:
+            self.delay_buffer = last_spike
         return x
 
     @property

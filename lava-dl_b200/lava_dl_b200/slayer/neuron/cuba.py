@@ -62,26 +62,29 @@ class _FusedForward(torch.autograd.Function):
     series and the last-bin current / voltage / spike for state hand-over."""
 
     @staticmethod
-    def forward(ctx, input, cdecay, vdecay, cstate, vstate, threshold, w_scale, tau_rho, scale_rho, graded):
+    def forward(ctx, input, cdecay, vdecay, cstate, vstate, threshold, w_scale, tau_rho, scale_rho, graded,
+                spike_delay=0, delay_head=None):
         need_dgrad = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
         r = _ops.cuba_fwd(input, cdecay, vdecay, cstate, vstate, threshold, w_scale,
-                          want_current=need_dgrad, want_spike=True, graded=graded, spike_scale=1.0)
+                          want_current=need_dgrad, want_spike=True, graded=graded, spike_scale=1.0,
+                          spike_delay=spike_delay, delay_head=delay_head)
         saved = [r['voltage'], cdecay, vdecay]
         if need_dgrad:
             saved.append(r['current'])
         ctx.save_for_backward(*saved)
-        ctx.consts = (threshold, tau_rho, scale_rho, graded, need_dgrad)
+        ctx.consts = (threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay)
         ctx.mark_non_differentiable(r['voltage'], r['final_c'], r['final_v'], r['final_s'])
         return r['spike'], r['voltage'], r['final_c'], r['final_v'], r['final_s']
 
     @staticmethod
     def backward(ctx, grad_spike, *_):
-        threshold, tau_rho, scale_rho, graded, need_dgrad = ctx.consts
+        threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay = ctx.consts
         voltage, cdecay, vdecay = ctx.saved_tensors[:3]
         current = ctx.saved_tensors[3] if need_dgrad else None
         g_in, g_cdecay, g_vdecay = _ops.cuba_bwd(
-            grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_dgrad)
-        return (g_in, g_cdecay, g_vdecay) + (None,) * 7
+            grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_dgrad,
+            spike_delay=spike_delay)
+        return (g_in, g_cdecay, g_vdecay) + (None,) * 9
 
 
 class Neuron(base.Neuron):
@@ -229,15 +232,33 @@ class Neuron(base.Neuron):
         if self.norm is not None or not self._fusable:
             _, voltage = self.dynamics(input)
             return self.spike(voltage)
+        spike, _ = self._fused_forward(input, 0, None)
+        if self.drop is not None:
+            spike = self.drop(spike)
+        return spike
+
+    @property
+    def fuses_step_delay(self):
+        """True when ``forward_step_delayed`` can write the spikes one step late
+        inside the kernel (binary spikes, no normalisation, no dropout)."""
+        return self.norm is None and self._fusable and self.graded_spike is not True and self.drop is None
+
+    def forward_step_delayed(self, input, delay_head=None):
+        """``forward`` with the blocks' one-step delay folded in: returns
+        ``(delayed_spike, last_spike)`` where ``delayed_spike[..., t] = spike[..., t - 1]``,
+        ``delayed_spike[..., 0] = delay_head`` (0 when ``None``), and ``last_spike``
+        is the undelayed spike of the last time bin."""
+        return self._fused_forward(input, 1, delay_head)
+
+    def _fused_forward(self, input, spike_delay, delay_head):
         self._prepare(input)
         spike, _, final_c, final_v, final_s = _FusedForward.apply(
             input, quantize(self.current_decay), quantize(self.voltage_decay),
             self.current_state, self.voltage_state, self.threshold + self.threshold_eps, self.s_scale,
-            self.tau_rho * TAU_RHO_MULT, self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True)
+            self.tau_rho * TAU_RHO_MULT, self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True,
+            spike_delay, delay_head)
         if self.persistent_state:
             with torch.no_grad():
                 self.current_state = final_c
                 self.voltage_state = leaky_integrator.persistent_state(final_v, final_s)
-        if self.drop is not None:
-            spike = self.drop(spike)
-        return spike
+        return spike, final_s

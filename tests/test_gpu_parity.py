@@ -282,6 +282,41 @@ def test_cuba_fused(shape, per_channel, misalign, cuda, ops):
 
 
 @pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('misalign', [False, True])
+def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
+    """Spikes written one step late inside the kernel == shift(spike, 1) with the head
+    value at t = 0, and the backward reads the gradient of the late series."""
+    rng = rng_for('cuba_delay', shape)
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    cd, vd = np.array([1024.0], np.float32), np.array([123.0], np.float32)
+    gs = rng.normal(size=shape).astype(np.float32)
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    want = O.cuba(x, 1.25, cd, vd)
+    late = O.shift(want['spike'], 1)
+    for h, h_dev in ((None, None), (head, dev(head, cuda))):
+        r = ops.cuba_fwd(dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), dev(np.zeros(shape[:-1]), cuda),
+                         dev(np.zeros(shape[:-1]), cuda), 1.25 + 0.01 / W, W, want_current=True, want_spike=True,
+                         spike_delay=1, delay_head=h_dev)
+        expect = late.copy()
+        if h is not None:
+            expect[..., 0] = h
+        assert_exact(r['spike'], expect, 'late spikes')
+        assert_exact(r['final_s'], want['spike'][..., -1], 'undelayed last spike')
+        assert_quantised_equal(r['voltage'], want['voltage'], W, 'voltage')
+    # gradient of the late series: g_spike[t] = g_late[t + 1]
+    g_early = O.shift(gs, -1)
+    ref = O.cuba(x, 1.25, cd, vd, grad_spike=g_early)
+    gx, gcd, gvd = ops.cuba_bwd(dev(gs, cuda, misalign), r['voltage'], 1.25 + 0.01 / W, r['current'], dev(cd, cuda),
+                                dev(vd, cuda), 125.0, 0.1, False, True, spike_delay=1)
+    g_v = O.spike_bwd(want['voltage'], 1.25 + 0.01 / W, g_early, 125.0, 0.1, False)
+    assert_close(gx, ref['grad_x'], 'grad_x', scale=li_scale(li_scale(g_v, vd), cd))
+    g_c, _ = O.li_bwd(g_v, want['voltage'], vd)
+    assert_close(gcd, ref['grad_current_decay'], 'grad current decay',
+                 scale=pgrad_scale(1, (ref['grad_x'], want['current'])))
+    assert_close(gvd, ref['grad_voltage_decay'], 'grad voltage decay', scale=pgrad_scale(1, (g_c, want['voltage'])))
+
+
+@pytest.mark.parametrize('shape', SHAPES)
 @pytest.mark.parametrize('per_channel', [False, True])
 def test_alif_fused(shape, per_channel, cuda, ops):
     rng = rng_for('alif', shape, per_channel)
