@@ -237,6 +237,12 @@ int sb_pool_fwd(const float* x, const float* weight, float* y, int64_t NC, int64
 int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t NC, int64_t H, int64_t W,
                 int64_t Ho, int64_t Wo, int64_t kh, int64_t kw, int64_t T, void* stream);
 
+/* Convolution synapse, forward (replaces the Conv3d call of synapse/layer.py:297-323
+ * for stride 1, dilation 1, one group).  x [N, Ci, H, W, T], weight [Co, Ci, kh, kw]
+ * (after the pre-hook), y [N, Co, H+2ph-kh+1, W+2pw-kw+1, T].  Needs N * Ho <= 65535. */
+int sb_conv_fwd(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co, int64_t H,
+                int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, void* stream);
+
 /* ---- measurement aid ------------------------------------------------------------
  * No counterpart in the reference and not on the hot path: a plain streaming
  * kernel that reads `reads` streams of n floats (laid out back to back in `in`)

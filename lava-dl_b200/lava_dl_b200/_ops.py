@@ -468,3 +468,27 @@ def pool_bwd(grad_y, weight, in_shape):
     N.call('sb_pool_bwd', grad_y, N.ptr(grad_y), N.ptr(wgt), N.ptr(gx), n * c, h, w, grad_y.shape[2], grad_y.shape[3],
            kh, kw, t, N.stream_of(grad_y))
     return gx
+
+
+def conv_fwd_supported(x, weight, stride, padding, dilation, groups):
+    """The direct convolution kernel covers stride 1, dilation 1, one group."""
+    if not (x.is_cuda and x.dim() == 5 and x.dtype == torch.float32):
+        return False
+    if tuple(stride) != (1, 1, 1) or tuple(dilation) != (1, 1, 1) or groups != 1 or padding[2] != 0:
+        return False
+    n, ci, h, w, t = x.shape
+    ho = h + 2 * padding[0] - weight.shape[2] + 1
+    return 0 < n * ho <= 65535 and ci * weight.shape[2] * weight.shape[3] * 16 * 4 <= 96 * 1024
+
+
+def conv_fwd(x, weight, padding):
+    """x: [N, Ci, H, W, T]; weight: [Co, Ci, kh, kw, 1] (already hooked); padding (ph, pw)."""
+    N.require_cuda(x)
+    x = _c(x)
+    n, ci, h, w, t = x.shape
+    co, _, kh, kw = weight.shape[:4]
+    wgt = _c(weight.detach().to(device=x.device, dtype=torch.float32).reshape(co, -1))
+    ph, pw = int(padding[0]), int(padding[1])
+    y = torch.empty((n, co, h + 2 * ph - kh + 1, w + 2 * pw - kw + 1, t), device=x.device, dtype=torch.float32)
+    N.call('sb_conv_fwd', x, N.ptr(x), N.ptr(wgt), N.ptr(y), n, ci, co, h, w, kh, kw, ph, pw, t, N.stream_of(x))
+    return y

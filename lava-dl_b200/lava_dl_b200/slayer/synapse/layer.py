@@ -101,6 +101,25 @@ class Dense(torch.nn.Conv3d, GenericLayer):
         return F.conv3d(input, weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
 
 
+class _SpikeConv(torch.autograd.Function):
+    """Forward through the direct convolution kernel (time stays the vector axis,
+    no layout change); backward through ATen's convolution backward."""
+
+    @staticmethod
+    def forward(ctx, input, weight, padding):
+        ctx.save_for_backward(input, weight)
+        ctx.padding = tuple(padding)
+        return _ops.conv_fwd(input, weight, padding)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight = ctx.saved_tensors
+        grad_input, grad_weight, _ = torch.ops.aten.convolution_backward(
+            grad_output.contiguous(), input, weight, None, [1, 1, 1], list(ctx.padding), [1, 1, 1], False, [0, 0, 0],
+            1, [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        return grad_input, grad_weight, None
+
+
 class Conv(torch.nn.Conv3d, GenericLayer):
     """Spatial convolution synapse over ``NCHWT`` input (time kernel 1).
     ``kernel_size``, ``stride``, ``padding``, ``dilation``: int or (height, width)."""
@@ -112,8 +131,10 @@ class Conv(torch.nn.Conv3d, GenericLayer):
         self._finish_init(weight_scale, weight_norm, pre_hook_fx)
 
     def forward(self, input):
-        return F.conv3d(input, self._hooked_weight(), self.bias, self.stride, self.padding, self.dilation,
-                        self.groups)
+        weight = self._hooked_weight()
+        if _ops.conv_fwd_supported(input, weight, self.stride, self.padding, self.dilation, self.groups):
+            return _SpikeConv.apply(input, weight, self.padding)
+        return F.conv3d(input, weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
 
 
 class _SumPool(torch.autograd.Function):

@@ -114,3 +114,34 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
     fast.backward(g)
     slow.backward(g)
     assert_exact(xa.grad, xb.grad, 'pool input gradient')
+
+
+@pytest.mark.parametrize('shape,co,k,pad', [((2, 2, 8, 8, 40), 16, 5, 2), ((1, 3, 7, 9, 12), 5, 3, 1),
+                                            ((2, 16, 6, 6, 33), 32, 3, 1), ((1, 4, 5, 6, 8), 20, (3, 1), (0, 0)),
+                                            ((3, 1, 4, 4, 1), 2, 1, 0)])
+def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
+    """The direct convolution synapse kernel against F.conv3d: exact on spikes with
+    weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
+    backward (ATen) against autograd of conv3d."""
+    import torch.nn.functional as F
+    import lava_dl_b200.slayer as slayer
+    from _util import assert_close
+    gen = torch.Generator().manual_seed(sum(shape) + co)
+    conv = slayer.synapse.Conv(shape[1], co, k, padding=pad).to(cuda)
+    with torch.no_grad():
+        conv.weight.copy_(torch.randint(-128, 127, conv.weight.shape, generator=gen).float().to(cuda) / 32)
+    x = (torch.rand(shape, generator=gen) < 0.3).float().to(cuda)
+    xa = x.clone().requires_grad_(True)
+    xb = x.clone().requires_grad_(True)
+    fast = conv(xa)
+    assert 'SpikeConv' in type(fast.grad_fn).__name__
+    slow = F.conv3d(xb, conv.weight, None, conv.stride, conv.padding, conv.dilation, conv.groups)
+    assert_exact(fast, slow, 'convolution of spikes')
+    g = torch.randint(-8, 8, fast.shape, generator=gen).float().to(cuda) / 4
+    w_fast = torch.autograd.grad(fast, [xa, conv.weight], g)
+    w_slow = torch.autograd.grad(slow, [xb, conv.weight], g)
+    assert rel_l2(w_fast[0], w_slow[0].cpu().numpy()) < 1e-6 and rel_l2(w_fast[1], w_slow[1].cpu().numpy()) < 1e-6
+    xf = torch.randn(shape, generator=gen).to(cuda)
+    with torch.backends.cudnn.flags(allow_tf32=False):
+        want = F.conv3d(xf, conv.weight, None, conv.stride, conv.padding)
+    assert_close(conv(xf), want, 'convolution of floats')
