@@ -50,43 +50,63 @@ conv_fwd_kernel(const float* __restrict__ x, const float* __restrict__ wgt, floa
 #pragma unroll
     for (int v = 0; v < V; ++v) acc[c][v] = 0.f;
 
+  if (KW > 0) {
+    // Software pipeline over the Ci * kh kernel rows: the KW input words of row
+    // r + 1 are requested before the FMAs of row r run (one register set in
+    // flight), so the loads' L1/L2 latency hides behind 64 * KW FMAs.
+    constexpr int KWc = KW > 0 ? KW : 1;
+    const int rows = g.Ci * g.kh;
+    auto load_row = [&](int r, float (&xv)[KWc][V]) -> bool {
+      const int ci = r / g.kh, i = r - ci * g.kh;
+      const int h = ho + i - g.ph;
+      const bool row_in = r < rows && h >= 0 && h < g.H;
+      const float* row = x + (((int64_t)n * g.Ci + ci) * g.H + (row_in ? h : 0)) * (int64_t)g.W * g.T + (int64_t)tv * V;
+#pragma unroll
+      for (int j = 0; j < KWc; ++j) {
+        const int wsrc = wo + j - g.pw;
+        const bool in = row_in && wsrc >= 0 && wsrc < g.W;
+        if (VEC) {
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (in) a = __ldg(reinterpret_cast<const float4*>(row + (int64_t)wsrc * g.T));
+          xv[j][0] = a.x; xv[j][1 % V] = a.y; xv[j][2 % V] = a.z; xv[j][3 % V] = a.w;
+        } else {
+          xv[j][0] = in ? __ldg(row + (int64_t)wsrc * g.T) : 0.f;
+        }
+      }
+      return row_in;  // uniform over the block
+    };
+    auto fma_row = [&](int r, const float (&xv)[KWc][V]) {
+      const float* wrow = ws + r * KWc * kCoTile;
+#pragma unroll
+      for (int j = 0; j < KWc; ++j) {
+#pragma unroll
+        for (int c4 = 0; c4 < kCoTile / 4; ++c4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(wrow + j * kCoTile + 4 * c4);
+#pragma unroll
+          for (int v = 0; v < V; ++v) {
+            acc[4 * c4 + 0][v] = fmaf(w4.x, xv[j][v], acc[4 * c4 + 0][v]);
+            acc[4 * c4 + 1][v] = fmaf(w4.y, xv[j][v], acc[4 * c4 + 1][v]);
+            acc[4 * c4 + 2][v] = fmaf(w4.z, xv[j][v], acc[4 * c4 + 2][v]);
+            acc[4 * c4 + 3][v] = fmaf(w4.w, xv[j][v], acc[4 * c4 + 3][v]);
+          }
+        }
+      }
+    };
+    float xa[KWc][V], xb[KWc][V];
+    bool in_a = load_row(0, xa), in_b = false;
+    for (int r = 0; r < rows; r += 2) {
+      in_b = load_row(r + 1, xb);
+      if (in_a) fma_row(r, xa);
+      in_a = load_row(r + 2, xa);
+      if (in_b) fma_row(r + 1, xb);
+    }
+  } else
   for (int ci = 0; ci < g.Ci; ++ci) {
     for (int i = 0; i < g.kh; ++i) {
       const int h = ho + i - g.ph;
       if (h < 0 || h >= g.H) continue;
       const float* row = x + (((int64_t)n * g.Ci + ci) * g.H + h) * (int64_t)g.W * g.T + (int64_t)tv * V;
       const float* wrow = ws + (ci * g.kh + i) * g.kw * kCoTile;
-      if (KW > 0) {
-        float xv[KW > 0 ? KW : 1][V];
-#pragma unroll
-        for (int j = 0; j < KW; ++j) {
-          const int wsrc = wo + j - g.pw;
-          const bool in = wsrc >= 0 && wsrc < g.W;
-          if (VEC) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (in) a = __ldg(reinterpret_cast<const float4*>(row + (int64_t)wsrc * g.T));
-            xv[j][0] = a.x; xv[j][1 % V] = a.y; xv[j][2 % V] = a.z; xv[j][3 % V] = a.w;
-          } else {
-            xv[j][0] = in ? __ldg(row + (int64_t)wsrc * g.T) : 0.f;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < KW; ++j) {
-          const float* wt = wrow + j * kCoTile;
-#pragma unroll
-          for (int c4 = 0; c4 < kCoTile / 4; ++c4) {
-            const float4 w4 = *reinterpret_cast<const float4*>(wt + 4 * c4);
-#pragma unroll
-            for (int v = 0; v < V; ++v) {
-              acc[4 * c4 + 0][v] = fmaf(w4.x, xv[j][v], acc[4 * c4 + 0][v]);
-              acc[4 * c4 + 1][v] = fmaf(w4.y, xv[j][v], acc[4 * c4 + 1][v]);
-              acc[4 * c4 + 2][v] = fmaf(w4.z, xv[j][v], acc[4 * c4 + 2][v]);
-              acc[4 * c4 + 3][v] = fmaf(w4.w, xv[j][v], acc[4 * c4 + 3][v]);
-            }
-          }
-        }
-        continue;
-      }
       for (int j = 0; j < g.kw; ++j) {
         const int wsrc = wo + j - g.pw;
         if (wsrc < 0 || wsrc >= g.W) continue;
