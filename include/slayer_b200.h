@@ -214,6 +214,11 @@ int sb_shift(const float* x, const float* lut, int64_t n_lut, float shift, float
  * conv: out[r,t] = Ts * sum_{i<K} f[i] * in[r, t-i];  corr: ... in[r, t+i]. */
 int sb_fir_conv(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
                 int64_t T, void* stream);
+/* 1 when a filter call of this size (bases 16-byte aligned) runs as a banded
+ * matrix product on the tensor cores (tcgen05, three TF32 products per term:
+ * K <= 64, T % 4 == 0, T >= 32, rows >= 128), 0 when it runs the FP32 sliding
+ * window kernel.  The reference has one kernel (conv.cu:24-78). */
+int sb_fir_uses_tensor_cores(int64_t K, int64_t rows, int64_t T);
 int sb_fir_corr(const float* x, const float* filter, int64_t K, float sampling_time, float* out, int64_t rows,
                 int64_t T, void* stream);
 /* Fused delay + filter (forward): conv(shift(x, lut), f); and its adjoint

@@ -129,6 +129,10 @@ static void bind_primary_context() {
 #endif
 
 int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps) {
+  return make_row_map_box(out, base, rows, T, tile_steps, kTileR);
+}
+
+int make_row_map_box(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -137,7 +141,7 @@ int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, in
   bind_primary_context();
   const cuuint64_t dims[2] = {(cuuint64_t)T, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)T * 4};
-  const cuuint32_t box[2] = {(cuuint32_t)tile_steps, (cuuint32_t)kTileR};
+  const cuuint32_t box[2] = {(cuuint32_t)tile_steps, (cuuint32_t)box_rows};
   const CUtensorMapSwizzle swizzle = tile_steps == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,

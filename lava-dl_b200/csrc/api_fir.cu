@@ -23,6 +23,13 @@
 
 using namespace sb;
 
+namespace sb {
+// api_fir_tc.cu: tensor-core path for K <= 64, T % 4 == 0, rows >= 128.
+int fir_tc_try(const float* x, const float* filt, int64_t K, bool corr, const float* lut, int64_t n_lut, float shift,
+               float shift_ts, int mode, float ts, float* out, int64_t rows, int64_t T, cudaStream_t st,
+               bool* taken);
+}
+
 namespace {
 
 constexpr int kOutPerThread = 16;
@@ -286,6 +293,12 @@ int launch_fir(const float* x, const float* filt, int64_t K, bool corr, const fl
   const unsigned gx = (unsigned)((T + kSeg - 1) / kSeg);
   const int off = corr ? 0 : (int)K - 1;
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    bool taken = false;
+    const int rc = fir_tc_try(x, filt, K, corr, lut, n_lut, shift, shift_ts, shift_in ? 1 : (shift_out ? -1 : 0), ts,
+                              out, rows, T, st, &taken);
+    if (rc != SB_OK || taken) return rc;
+  }
   // The packed two-row kernel needs twice the shared memory; filters too long
   // for its 48 KB take the one-row kernel (as does a single row).
   const size_t smem2 = sizeof(float) * (size_t)(2 * Kp + skew2(nwin) + 8);

@@ -1,0 +1,574 @@
+// Temporal filter (utils/filter/conv.py:48-97) on the 5th-generation tensor
+// cores: conv / corr of a [rows, T] tensor with K <= 64 taps as a banded
+// (Toeplitz) matrix product, with fp32-level accuracy from three TF32 products.
+//
+//   y[r, t0 + n] = Ts * sum_k  W[r, k] * B[n, k]        n in [0, 32), k in [0, 96)
+//   W[r, k]      = x[r, w0 + k]   (w0 = t0 - 64 for conv, t0 for corr; zero outside [0, T))
+//   B[n, k]      = h[n + 64 - k]  (conv)   |   h[k - n]  (corr)       zero outside [0, K)
+//
+// A tile is 128 rows x 32 outputs: M = 128, N = 32, K = 96 in three 32-step
+// boxes.  The SIMT kernel (api_fir.cu) spends 64 FMAs per output and is bound by
+// the FP32 pipe at 0.43 of the HBM roof; here the multiply-adds run on
+// tcgen05.mma (kind::tf32) and the kernel streams x once and out once.
+//
+// Accuracy: every operand is split as v = hi + lo with hi = v rounded to TF32
+// (10 mantissa bits, cvt.rna) and lo = (v - hi) rounded to TF32; the tile
+// accumulates hi*hi + hi*lo + lo*hi in fp32 (TMEM).  |v - hi - lo| <= 2^-22 |v|
+// and the dropped lo*lo term is <= 2^-22 of the product.  A box of x whose
+// values are all exact in TF32 (spike trains) skips its lo products.
+//
+// Data flow per CTA (persistent over 128-row blocks, 1 CTA per SM, 10 warps):
+//   producer (1 thread): TMA boxes (32 steps x 128 rows, SWIZZLE_128B) into a
+//     ring of 11 landing slots in shared memory; a slot is free again as soon as
+//     the split warps have read it, so ~10 boxes (160 KB) are in flight per SM.
+//   split (4 warps, one row per thread): box -> registers -> hi / lo -> TMEM
+//     (tcgen05.st) into a ring of 6 operand slots.  The A operand of the MMAs is
+//     read from TMEM, which is what frees the shared memory for the deep ring.
+//   issue (1 thread): per tile 3 boxes x 4 K-steps x {A_hi x [B_hi; B_lo] as one
+//     N = 64 product, A_lo x B_hi with N = 32} into one of two 64-column TMEM
+//     accumulators; B (the Toeplitz factor, 24 KB) stays in shared memory.  An
+//     MMA costs ~46 cycles to issue whatever its N <= 64, so merging the two B
+//     factors along N saves a third of the instructions.
+//   drain (4 warps, one row per thread): tcgen05.ld, add the two halves, scale,
+//     stage the row's eight 128-bit words in shared memory (4 KB per warp) and
+//     write them with a (4 rows x 128 bytes) per instruction mapping -- one row
+//     per lane would cost 32 L1 wavefronts per store instruction.
+//   TMEM columns: 2 x 64 accumulators, 6 x 32 A_hi, 6 x 32 A_lo = 512.
+// Fused delay (axon.delay): shift(corr(g), -d) shifts the output, and
+// conv(shift(x, d)) equals shift(conv(x), d) for d >= 0 (a delay only prepends
+// zeros), so both are the same tiles written at a per-row offset: the drain
+// re-groups the row's 32 values into aligned 128-bit words with a 3-value carry
+// between tiles and zero-fills what the shift uncovers.  A negative delay on the
+// input side (an advance) drops the first |d| samples before the filter sees
+// them; then every row takes two more tiles past T, and advanced rows subtract
+// the dropped samples' contribution from their first K - 1 outputs.
+// Every mbarrier wait is bounded; a wait that runs out sets a CTA-wide flag that
+// ends all other waits at once, SB_DEV_TMA_TIMEOUT is recorded, and the CTA
+// waits (bounded) for loads and MMAs in flight, frees its TMEM and returns.
+#include "api_util.cuh"
+#ifdef FIRTC_PROF
+#include <cstdio>
+#endif
+
+using namespace sb;
+
+namespace {
+
+constexpr int kM = 128;                  // rows per block = MMA M
+constexpr int kN = 32;                   // outputs per tile = steps per box
+constexpr int kThreads = 2 * kM + 96;    // split warps 0-3, drain warps 4-7, issue warps 8-9, producer warp 10
+constexpr int kIssueWarp = 8, kProdWarp = 10;
+constexpr int kBoxBytes = kM * kN * 4;   // 16 KB
+constexpr int kRing = 11;                // landing slots in shared memory
+constexpr int kARing = 6;                // operand slots in TMEM: 3 in use + 3 ahead
+constexpr int kBBoxBytes = 2 * kN * 128; // one 64 x 32 box of the Toeplitz factor: rows 0-31 hi, 32-63 lo
+constexpr int kAccCols = 2 * kN;         // hi*hi + lo*hi | hi*lo
+constexpr int kColAhi = 2 * kAccCols;            // 128
+constexpr int kColAlo = kColAhi + kARing * kN;   // 320
+constexpr int kTmemCols = 512;
+constexpr uint32_t kTf32Mask = 0xffffe000u;
+
+constexpr int kOffRaw = 0;
+constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
+constexpr int kOffStage = kOffB + 3 * kBBoxBytes;     // output staging, 4 KB private to each drain warp
+constexpr int kOffSq = kOffStage + kBoxBytes;         // 128 row shifts (>> 2)
+constexpr int kOffBar = kOffSq + kM * 4;
+// barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
+// then the TMEM base word, the dead flag, has_lo[kARing]
+constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
+constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+static_assert(kColAlo + kARing * kN == kTmemCols, "TMEM column budget");
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address and
+// offsets in 16-byte units, 8-row groups 1024 bytes apart, descriptor version 1.
+// Only the low word depends on the address.
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3ffffu) >> 4) | (1u << 16); }
+// Instruction descriptor: D = f32, A = B = tf32, both K-major, M = 128.
+__host__ __device__ constexpr uint32_t idesc_n(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]^T: A is 128 lanes x 8 columns of TF32.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Bounded wait that also gives up as soon as any thread of the CTA has given up
+// (the dead flag), so that one lost transfer costs one time-out, not one per wait.
+__device__ __forceinline__ bool wait_or_dead(uint32_t bar, uint32_t parity, volatile int* dead) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) {
+      if (*dead) return false;
+      __nanosleep(it > 4096 ? 256 : 32);
+    }
+  }
+  *dead = 1;
+  return false;
+}
+
+#define SB_R32(r)                                                                                                  \
+  r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15], r[16],     \
+      r[17], r[18], r[19], r[20], r[21], r[22], r[23], r[24], r[25], r[26], r[27], r[28], r[29], r[30], r[31]
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Nearest TF32 value, low 13 bits zero (so the tensor core reads it exactly).
+__device__ __forceinline__ uint32_t tf32_rn(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r & kTf32Mask;
+}
+
+// The eight aligned 128-bit words that one tile contributes to a row shifted by
+// 4 * sq + E: word g holds tile values 4g - E .. 4g + 3 - E, the negative
+// indices coming from the previous tile (carry[0..2] = its values 29..31).
+// They go to the staging tile of the row, chunk-swizzled like a TMA box.
+template <int E>
+__device__ __forceinline__ void stage_groups(uint8_t* stage_row, int rsw, const float (&v)[32],
+                                             const float (&carry)[3]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float w[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int j = 4 * g + r - E;
+      w[r] = j >= 0 ? v[j >= 0 ? j : 0] : carry[j < 0 ? 3 + j : 0];
+    }
+    *reinterpret_cast<float4*>(stage_row + ((g ^ rsw) << 4)) = make_float4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ x, const float* __restrict__ filt,
+              int K, int corr, const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, int mode,
+              float ts, float* __restrict__ out, int64_t rows, int T, unsigned int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_full = base + kOffBar;
+  const uint32_t bar_rawfree = bar_full + 8 * kRing;
+  const uint32_t bar_aready = bar_rawfree + 8 * kRing;
+  const uint32_t bar_afree = bar_aready + 8 * kARing;
+  const uint32_t bar_mma = bar_afree + 8 * kARing;
+  const uint32_t bar_free = bar_mma + 16;
+  volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(sm + kOffBar + 8 * kNumBars);
+  volatile int* dead = reinterpret_cast<volatile int*>(sm + kOffBar + 8 * kNumBars + 4);
+  volatile int* has_lo = reinterpret_cast<volatile int*>(sm + kOffBar + 8 * kNumBars + 8);  // [kARing]
+
+  if (tid == 0) {
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_rawfree + 8 * i, kM);
+    }
+    for (int i = 0; i < kARing; ++i) {
+      mbar_init(bar_aready + 8 * i, kM);
+      mbar_init(bar_afree + 8 * i, 2);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_mma + 8 * i, 1);
+      mbar_init(bar_free + 8 * i, kM);
+    }
+    *dead = 0;
+    fence_mbar_init();
+  }
+  if (warp == kIssueWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(base + kOffBar + 8 * kNumBars), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  // Is any input-side delay negative?  Then filter outputs past T reach the
+  // result and two more tiles are computed there.  Every CTA scans the whole
+  // table so that all agree without a second kernel or scratch.
+  int wrong = 0;
+  if (mode > 0) {
+    const int64_t n = lut ? n_lut : 1;
+    for (int64_t i = tid; i < n; i += kThreads) {
+      const float sv = lut ? __ldg(lut + i) : shift;
+      wrong |= __float2int_rz(__fdiv_rn(sv, shift_ts)) < 0;
+    }
+  }
+  // Toeplitz factor, split, in the swizzled K-major layout: row n holds the hi
+  // part for output n, row 32 + n the lo part.
+  for (int e = tid; e < kN * 96; e += kThreads) {
+    const int n = e / 96, k = e - n * 96;
+    const int m = corr ? (k - n) : (n + 64 - k);
+    const float v = (m >= 0 && m < K) ? __ldg(filt + m) : 0.f;
+    const uint32_t hi = tf32_rn(v), lo = tf32_rn(__fsub_rn(v, __uint_as_float(hi)));
+    const int kk = k & 31;
+    const int off = (k >> 5) * kBBoxBytes + n * 128 + ((((kk >> 2) ^ (n & 7))) << 4) + ((kk & 3) << 2);
+    *reinterpret_cast<uint32_t*>(sm + kOffB + off) = hi;
+    *reinterpret_cast<uint32_t*>(sm + kOffB + off + kN * 128) = lo;  // row n + 32: same swizzle phase
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  wrong = __syncthreads_or(wrong);
+  tc_fence_after();
+  const uint32_t tmem = *tmem_word;
+
+  const int nt = (T + kN - 1) / kN;
+  const int ntile = nt + (wrong ? 2 : 0);
+  const int narr = ntile + 2;                 // boxes per block
+  const int qoff = corr ? 2 : 0;
+  const int ngroups = T >> 2;
+  const int64_t nblk = (rows + kM - 1) / kM;
+  const int64_t my_nblk = blockIdx.x < nblk ? (nblk - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int64_t total = my_nblk * narr;
+
+  if (warp == kProdWarp) {
+    // ---------------- producer: TMA requests (one thread) ----------------
+    if (lane == 0) {
+      int slot = 0, a = 0, row0 = (int)(blockIdx.x * kM);
+      uint32_t use = 0;
+      int64_t f = 0;
+      for (; f < total; ++f) {
+        if (use >= 1 && !wait_or_dead(bar_rawfree + 8 * slot, (use - 1u) & 1u, dead)) break;
+        const uint32_t bar = bar_full + 8 * slot;
+        mbar_expect_tx(bar, kBoxBytes);
+        tma_load_2d(base + kOffRaw + slot * kBoxBytes, &xmap, kN * (a - 2 + qoff), row0, bar);
+        if (++a == narr) { a = 0; row0 += (int)(gridDim.x * kM); }
+        if (++slot == kRing) { slot = 0; ++use; }
+      }
+      if (*dead) {
+        // loads still in flight must land before the shared memory is given back
+        for (int i = 0; i < kRing; ++i) { mbar_wait(bar_full + 8 * i, 0); mbar_wait(bar_full + 8 * i, 1); }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kIssueWarp || warp == kIssueWarp + 1) {
+    // ---------------- issue: the MMAs of every other tile (one thread per warp) ----------------
+    // One thread issues an MMA every ~46 cycles whatever its size; two threads do twice that.
+    const uint32_t me = (uint32_t)(warp - kIssueWarp);   // this thread's accumulator
+    if (lane == 0) {
+      const uint32_t b0 = desc_lo(base + kOffB);
+      int a = 0, as = 0, as1 = 0, as2 = 0;    // operand slots of this arrival and the two before it
+      uint32_t ause = 0, tcount = 0;
+#ifdef FIRTC_PROF
+      long long t_ready = 0, t_free = 0, t_issue = 0, t_all = clock64();
+#define PROF_T(var, stmt) { long long _t = clock64(); stmt; var += clock64() - _t; }
+#else
+#define PROF_T(var, stmt) stmt;
+#endif
+      for (int64_t f = 0; f < total; ++f) {
+        if (a >= 2) {
+          if ((tcount & 1u) == me) {
+            const uint32_t acc = me;
+            bool ok2;
+            PROF_T(t_ready, ok2 = wait_or_dead(bar_aready + 8 * as, ause & 1u, dead))
+            if (tcount >= 2) PROF_T(t_free, ok2 = wait_or_dead(bar_free + 8 * acc, ((tcount >> 1) - 1u) & 1u, dead) && ok2)
+            tc_fence_after();
+#ifdef FIRTC_PROF
+            long long _ti = clock64();
+#endif
+#ifdef FIRTC_NO_MMA
+            ok2 = false;
+#endif
+            if (ok2) {
+              const uint32_t d_tmem = tmem + acc * kAccCols;
+              const int slots[3] = {as2, as1, as};
+#pragma unroll
+              for (int c = 0; c < 3; ++c) {
+                const uint32_t ah = tmem + kColAhi + (uint32_t)slots[c] * kN;
+                const uint32_t al = tmem + kColAlo + (uint32_t)slots[c] * kN;
+                const uint32_t bb = b0 + c * (kBBoxBytes >> 4);
+                const bool lo = has_lo[slots[c]] != 0;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  // columns 0-31 += A_hi B_hi, columns 32-63 += A_hi B_lo; then columns 0-31 += A_lo B_hi
+                  umma_ts(d_tmem, ah + 8 * ks, bb + 2 * ks, idesc_n(2 * kN), (c | ks) ? 1u : 0u);
+                  if (lo) umma_ts(d_tmem, al + 8 * ks, bb + 2 * ks, idesc_n(kN), 1u);
+                }
+              }
+            }
+            umma_commit(bar_mma + 8 * acc);
+#ifdef FIRTC_PROF
+            t_issue += clock64() - _ti;
+#endif
+          }
+          // Operand slots nobody reads after the tile of this arrival: its oldest
+          // box, and at the end of a block the two newer ones as well.  Both issue
+          // threads commit (the barrier counts 2): each covers the tiles it issued.
+          umma_commit(bar_afree + 8 * as2);
+          if (a == narr - 1) {
+            umma_commit(bar_afree + 8 * as1);
+            umma_commit(bar_afree + 8 * as);
+          }
+          ++tcount;
+        }
+        if (++a == narr) a = 0;
+        as2 = as1; as1 = as;
+        if (++as == kARing) { as = 0; ++ause; }
+      }
+#ifdef FIRTC_PROF
+      if (blockIdx.x == 0 && me == 0)
+        printf("issuer: tiles %u total %lld  wait_ready %lld  wait_free %lld  issue %lld (cycles per tile: %lld %lld %lld %lld)\n",
+               tcount, clock64() - t_all, t_ready, t_free, t_issue, (clock64() - t_all) / tcount, t_ready / tcount,
+               t_free / tcount, t_issue / tcount);
+#endif
+      // nothing may still be writing TMEM when it is freed: wait for this thread's last tile
+      if (tcount > me) {
+        const uint32_t last = ((tcount - 1u - me) & ~1u) + me;
+        mbar_wait(bar_mma + 8 * me, (last >> 1) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ---------------- split warps: landing slot -> hi / lo in TMEM ----------------
+    int slot = 0, as = 0;
+    uint32_t use = 0, ause = 0;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int64_t f = 0; f < total; ++f) {
+      wait_or_dead(bar_full + 8 * slot, use & 1u, dead);
+      const uint8_t* rowp = sm + kOffRaw + slot * kBoxBytes + tid * 128;
+      uint32_t xr[32];
+      uint32_t low = 0;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 q = *reinterpret_cast<const uint4*>(rowp + ((c ^ (tid & 7)) << 4));
+        xr[4 * c] = q.x; xr[4 * c + 1] = q.y; xr[4 * c + 2] = q.z; xr[4 * c + 3] = q.w;
+        low |= q.x | q.y | q.z | q.w;
+      }
+      // Does any value of the box need a lo part?  (Spike trains do not.)  The
+      // barrier also orders every thread's reads of the slot before its release.
+      int any;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 q, %1, 0;\n\t"
+          "bar.red.or.pred p, 1, %2, q;\n\t"
+          "selp.s32 %0, 1, 0, p;\n\t}"
+          : "=r"(any)
+          : "r"(low & ~kTf32Mask), "n"(kM)
+          : "memory");
+      mbar_arrive(bar_rawfree + 8 * slot);
+#ifdef FIRTC_NO_SPLIT
+      any = 0;
+#endif
+      // the MMAs that read this operand slot's previous box have completed?
+      if (ause >= 1) wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
+      tc_fence_after();
+      if (any) {
+        uint32_t lo[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float v = __uint_as_float(xr[j]);
+          const uint32_t h = tf32_rn(v);
+          lo[j] = tf32_rn(__fsub_rn(v, __uint_as_float(h)));
+          xr[j] = h;
+        }
+#ifndef FIRTC_NO_TST
+        tmem_st32(tmem + lane_base + kColAlo + as * kN, lo);
+#endif
+      }
+#ifndef FIRTC_NO_TST
+      tmem_st32(tmem + lane_base + kColAhi + as * kN, xr);
+      tmem_st_wait();
+#else
+      if (xr[0] == 0x12345678u && xr[5] == 77u) *dead = 2;
+#endif
+      tc_fence_before();
+      if (tid == 0) has_lo[as] = any;
+      mbar_arrive(bar_aready + 8 * as);
+      if (++slot == kRing) { slot = 0; ++use; }
+      if (++as == kARing) { as = 0; ++ause; }
+    }
+  } else {
+    // ---------------- drain warps: accumulator -> rows of the result ----------------
+    const int et = tid - kM, ew = warp - 4;      // row inside the block, TMEM lane quarter
+    int s_row = 0, e_row = 0;
+    float carry[3] = {0.f, 0.f, 0.f};
+    int64_t blk = blockIdx.x;
+    uint32_t tcount = 0;
+    uint8_t* stage = sm + kOffStage;                        // rows 32 ew .. 32 ew + 31 are this warp's
+    int* sq_s = reinterpret_cast<int*>(sm + kOffSq);
+    for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
+      const int64_t row = blk * kM + et;
+      for (int tile = 0; tile < ntile; ++tile, ++tcount) {
+        const int acc = (int)(tcount & 1u);
+        const bool ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead);
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccCols);
+#ifndef FIRTC_NO_TLD
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + kN, r1);
+        tmem_ld_wait();
+#else
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { r0[j] = taddr + j; r1[j] = tcount; }
+#endif
+        tc_fence_before();
+        mbar_arrive(bar_free + 8 * acc);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
+
+        const bool live = row < rows && ok;
+        float* rowp = out + (live ? row : 0) * (int64_t)T;
+        if (tile == 0) {
+          s_row = 0;
+          if (mode != 0 && live) {
+            const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
+            s_row = max(-T, min(T, __float2int_rz(__fdiv_rn(sv, shift_ts)))) * mode;
+          }
+          e_row = s_row & 3;
+          sq_s[et] = s_row >> 2;
+          carry[0] = carry[1] = carry[2] = 0.f;
+          if (live) {
+            const int gfirst = min(ngroups, s_row >> 2);
+            for (int G = 0; G < gfirst; ++G) reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        if (mode > 0 && s_row < 0 && live) {
+          // advance by nd: outputs 0 .. K-2 must not see x[0 .. nd)
+          const int nd = -s_row, tbase = kN * tile;
+          if (tbase < nd + K - 1 && tbase + kN > nd) {
+            const float* xrow = x + row * (int64_t)T;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int po = tbase + j - nd;
+              if (po >= 0 && po <= K - 2) {
+                float c = 0.f;
+                for (int q = max(0, po + nd - K + 1); q < nd; ++q)
+                  c = fmaf(__ldg(filt + (po + nd - q)), __ldg(xrow + q), c);
+                v[j] = __fsub_rn(v[j], c);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ts);
+        uint8_t* stage_row = stage + et * 128;
+        switch (e_row) {
+          case 0: stage_groups<0>(stage_row, et & 7, v, carry); break;
+          case 1: stage_groups<1>(stage_row, et & 7, v, carry); break;
+          case 2: stage_groups<2>(stage_row, et & 7, v, carry); break;
+          default: stage_groups<3>(stage_row, et & 7, v, carry); break;
+        }
+        carry[0] = v[29]; carry[1] = v[30]; carry[2] = v[31];
+        if (tile == ntile - 1 && live) {
+          // the word that holds the carried values, then zeros up to T
+          const int gl = 8 * ntile + (s_row >> 2);
+          if (gl >= 0 && gl < ngroups) {
+            const float w0 = e_row == 1 ? carry[2] : (e_row == 2 ? carry[1] : (e_row == 3 ? carry[0] : 0.f));
+            const float w1 = e_row == 2 ? carry[2] : (e_row == 3 ? carry[1] : 0.f);
+            const float w2 = e_row == 3 ? carry[2] : 0.f;
+            reinterpret_cast<float4*>(rowp)[gl] = make_float4(w0, w1, w2, 0.f);
+          }
+          for (int G = max(gl + 1, 0); G < ngroups; ++G)
+            reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncwarp();
+        // coalesced write-out of the warp's 32 rows: an instruction covers 4 rows x 128 bytes
+#ifdef FIRTC_NO_STORE
+        if (ok && v[0] == 123.456f) {
+#else
+        if (ok) {
+#endif
+          const int g = lane & 7;
+          const int rl0 = ew * 32 + (lane >> 3);
+          float* orow = out + (blk * kM + rl0) * (int64_t)T;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int rl = rl0 + 4 * k;
+            const float4 w = *reinterpret_cast<const float4*>(stage + rl * 128 + ((g ^ (rl & 7)) << 4));
+            const int G = 8 * tile + sq_s[rl] + g;
+            if (blk * kM + rl < rows && G >= 0 && G < ngroups)
+              reinterpret_cast<float4*>(orow + (int64_t)(4 * k) * T)[G] = w;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  if (*dead && tid == 0) dev_flag(status, SB_DEV_TMA_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kIssueWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+static bool tc_shape_ok(int64_t K, int64_t rows, int64_t T) {
+  return K >= 1 && K <= 64 && T >= kN && (T & 3) == 0 && rows >= kM && T <= (1 << 30);
+}
+
+namespace sb {
+
+// Runs the tensor-core filter when the problem fits it; *taken says whether it
+// did.  mode: 0 plain, +1 output shifted by +delay (conv of a delayed input),
+// -1 output shifted by -delay (adjoint).
+int fir_tc_try(const float* x, const float* filt, int64_t K, bool corr, const float* lut, int64_t n_lut, float shift,
+               float shift_ts, int mode, float ts, float* out, int64_t rows, int64_t T, cudaStream_t st,
+               bool* taken) {
+  *taken = false;
+  if (!tc_shape_ok(K, rows, T)) return SB_OK;
+  if ((mode > 0 && corr) || (mode < 0 && !corr)) return SB_OK;
+  if ((((uintptr_t)x) | ((uintptr_t)out)) & 15u) return SB_OK;
+  if (lut && n_lut > (1 << 22)) return SB_OK;
+  CUtensorMap xmap;
+  int rc = make_row_map_box(&xmap, x, rows, T, kN, kM);
+  if (rc != SB_OK) return rc;
+  static bool configured[64] = {false};
+  int dev = 0;
+  SB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured[dev] = true;
+  }
+  const int64_t nblk = (rows + kM - 1) / kM;
+  const int grid = (int)(nblk < sm_count() ? nblk : sm_count());
+  fir_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut, shift, shift_ts, mode, ts,
+                                              out, rows, (int)T, status_ptr());
+  SB_CUDA(cudaGetLastError());
+  *taken = true;
+  return SB_OK;
+}
+
+}  // namespace sb
+
+extern "C" int sb_fir_uses_tensor_cores(int64_t K, int64_t rows, int64_t T) { return tc_shape_ok(K, rows, T) ? 1 : 0; }

@@ -182,6 +182,8 @@ __device__ __forceinline__ void tma_wait_all() {
 // entry point is missing or the tensor violates TMA's alignment rules; callers
 // test tma_eligible() first and take the plain-load kernel otherwise.
 int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps);
+// Same with a box of box_rows rows (<= 256).
+int make_row_map_box(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps, int box_rows);
 bool tma_eligible(const void* const* ptrs, int n, int64_t T);
 
 // Smallest int k with (float)k >= thr (the reference compares an integer tensor

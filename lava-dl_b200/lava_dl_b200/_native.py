@@ -63,6 +63,7 @@ SIGNATURES = {
     'sb_shift': (c_int, [_P, _P, _I64, c_float, c_float, _P, _I64, _I64, _P]),
     'sb_fir_conv': (c_int, [_P, _P, _I64, c_float, _P, _I64, _I64, _P]),
     'sb_fir_corr': (c_int, [_P, _P, _I64, c_float, _P, _I64, _I64, _P]),
+    'sb_fir_uses_tensor_cores': (c_int, [_I64, _I64, _I64]),
     'sb_shift_fir_fwd': (c_int, [_P, _P, _I64, c_float, c_float, _P, _I64, c_float, _P, _I64, _I64, _P]),
     'sb_pool_fwd': (c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P]),
     'sb_pool_bwd': (c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P]),

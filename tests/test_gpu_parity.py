@@ -238,6 +238,78 @@ def test_fused_delay_filter(shape, cuda, ops):
                      'shift(corr(g), -d)')
 
 
+def _fir_scale(x, f, ts, corr, shift=None):
+    """Sum of the magnitudes of the terms each output adds up: the forward-error
+    scale of the filter sum (equals |output| where nothing cancels), floored at
+    1 % of its maximum like every other comparison.  With ``shift`` the filter
+    runs on the unshifted input and its output is shifted: the tensor-core kernel
+    computes an advanced row that way and subtracts what the dropped head of the
+    row contributed, so those samples belong to the error scale."""
+    s = O.fir(np.abs(x), np.abs(f), abs(ts), corr)
+    if shift is not None:
+        s = O.shift(s, shift)
+    return np.maximum(s, 0.01 * s.max() + 1e-30)
+
+
+# Shapes that take the tensor-core kernel (rows >= 128, T % 4 == 0, T >= 32, K <= 64):
+# rows off the 128 grid, T off the 32 grid, single tile, many tiles.
+TC_SHAPES = [(1, 128, 32), (1, 129, 36), (2, 100, 1000), (4, 64, 96), (3, 50, 260)]
+
+
+@pytest.mark.parametrize('shape', TC_SHAPES)
+@pytest.mark.parametrize('K', [1, 7, 32, 33, 64])
+def test_fir_tensor_core(shape, K, cuda, ops):
+    from lava_dl_b200 import _native as native
+    rows = int(np.prod(shape[:-1]))
+    assert native.load().sb_fir_uses_tensor_cores(K, rows, shape[-1]) == 1
+    rng = rng_for('fir_tc', shape, K)
+    f = (np.exp(-np.arange(K) / 8) / 8 * (1 + 0.3 * rng.normal(size=K))).astype(np.float32)
+    for kind in ('uniform', 'normal', 'spikes'):
+        if kind == 'uniform':
+            x = rng.uniform(size=shape).astype(np.float32)
+        elif kind == 'normal':
+            x = rng.normal(size=shape).astype(np.float32)
+        else:
+            x = (rng.uniform(size=shape) < 0.05).astype(np.float32)
+        for corr in (False, True):
+            for ts in (1.0, 2.0):
+                got = ops.fir(dev(x, cuda), dev(f, cuda), ts, corr)
+                assert_close(got, O.fir(x, f, ts, corr), f'fir tc {kind} corr={corr} ts={ts}',
+                             scale=_fir_scale(x, f, ts, corr))
+    assert native.device_status() == 0
+
+
+@pytest.mark.parametrize('shape', [(2, 130, 200), (1, 128, 1000), (2, 64, 36)])
+def test_fused_delay_filter_tensor_core(shape, cuda, ops):
+    from lava_dl_b200 import _native as native
+    rng = rng_for('shift_fir_tc', shape)
+    T = shape[-1]
+    rows = int(np.prod(shape[:-1]))
+    assert native.load().sb_fir_uses_tensor_cores(64, rows, T) == 1
+    x = (rng.uniform(size=shape) < 0.2).astype(np.float32)
+    g = rng.normal(size=shape).astype(np.float32)
+    f = (np.exp(-np.arange(64) / 8) / 8).astype(np.float32)
+    lut = rng.integers(0, 63, size=shape[1:-1]).astype(np.float32)
+    mixed = rng.integers(-70, 71, size=shape[1:-1]).astype(np.float32)
+    cases = [(lut, dev(lut, cuda)), (mixed, dev(mixed, cuda)), (0, 0), (5, 5), (-3, -3), (70, 70), (-70, -70),
+             (T + 5, T + 5), (-(T + 5), -(T + 5))]
+    for sv, sv_d in cases:
+        shifted = O.shift(x, sv)
+        want = O.conv(shifted, f)
+        assert_close(ops.shift_fir(dev(x, cuda), sv_d, 1, dev(f, cuda), 1.0, backward=False), want,
+                     f'conv(shift(x, {sv if np.isscalar(sv) else "lut"}))', scale=_fir_scale(x, f, 1.0, False, sv))
+        neg = -sv
+        cg = O.corr(g, f)
+        want_b = O.shift(cg, neg)
+        assert_close(ops.shift_fir(dev(g, cuda), sv_d, 1, dev(f, cuda), 1.0, backward=True), want_b,
+                     'shift(corr(g), -d)', scale=_fir_scale(g, f, 1.0, True, neg))
+    # Ts = 2 on the delay: d = int(shift / 2)
+    want = O.conv(O.shift(x, lut, 2.0), f)
+    assert_close(ops.shift_fir(dev(x, cuda), dev(lut, cuda), 2.0, dev(f, cuda), 1.0, backward=False), want,
+                 'conv(shift(x, lut, Ts=2))')
+    assert native.device_status() == 0
+
+
 # --------------------------------------------------------------------------
 # fused neuron passes against the oracle's un-fused call sequences
 # --------------------------------------------------------------------------
