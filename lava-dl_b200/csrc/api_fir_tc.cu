@@ -478,8 +478,9 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
             }
           }
         }
+        const float ts_row = s_row <= -T ? 0.f : ts;   // a row advanced by T or more is empty
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ts);
+        for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ts_row);
         uint8_t* stage_row = stage + et * 128;
         switch (e_row) {
           case 0: stage_groups<0>(stage_row, et & 7, v, carry); break;
