@@ -52,14 +52,17 @@
 
 using namespace sb;
 
+#ifdef FIRTC_PROF
+#define PROF_T(var, stmt) { long long _t = clock64(); stmt; var += clock64() - _t; }
+#else
+#define PROF_T(var, stmt) stmt;
+#endif
+
 namespace {
 
 constexpr int kM = 128;                  // rows per block = MMA M
 constexpr int kN = 32;                   // outputs per tile = steps per box
-constexpr int kThreads = 2 * kM + 96;    // split warps 0-3, drain warps 4-7, issue warps 8-9, producer warp 10
-constexpr int kIssueWarp = 8, kProdWarp = 10;
 constexpr int kBoxBytes = kM * kN * 4;   // 16 KB
-constexpr int kRing = 11;                // landing slots in shared memory
 constexpr int kARing = 6;                // operand slots in TMEM: 3 in use + 3 ahead
 constexpr int kBBoxBytes = 2 * kN * 128; // one 64 x 32 box of the Toeplitz factor: rows 0-31 hi, 32-63 lo
 constexpr int kAccCols = 2 * kN;         // hi*hi + lo*hi | hi*lo
@@ -68,16 +71,25 @@ constexpr int kColAlo = kColAhi + kARing * kN;   // 320
 constexpr int kTmemCols = 512;
 constexpr uint32_t kTf32Mask = 0xffffe000u;
 
-constexpr int kOffRaw = 0;
-constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
-constexpr int kOffStage = kOffB + 3 * kBBoxBytes;     // output staging, 4 KB private to each drain warp
-constexpr int kOffSq = kOffStage + kBoxBytes;         // 128 row shifts (>> 2)
-constexpr int kOffBar = kOffSq + kM * 4;
-// barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
-// then the TMEM base word, the dead flag, has_lo[kARing]
-constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
-constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
-static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+// Thread and shared-memory layout for DG drain groups (1 or 2).
+template <int DG>
+struct Cfg {
+  // warps: split 0-3, drain 4 .. 4 + 4 DG - 1, two issue warps, producer warp
+  static constexpr int kIssueWarp = 4 * (1 + DG), kProdWarp = kIssueWarp + 2;
+  static constexpr int kThreads = 32 * (kProdWarp + 1);
+  static constexpr int kRing = DG == 1 ? 11 : 10;                 // landing slots in shared memory
+  static constexpr int kOffRaw = 0;
+  static constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
+  static constexpr int kOffStage = kOffB + 3 * kBBoxBytes;        // output staging, 4 KB private to each drain warp
+  static constexpr int kOffSq = kOffStage + DG * kBoxBytes;       // 128 row shifts (>> 2) per drain group
+  static constexpr int kOffCarry = kOffSq + DG * kM * 4;          // 2 x 128 x 4 floats: a tile's last three values per row
+  static constexpr int kOffBar = kOffCarry + 2 * kM * 16;
+  // barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
+  // then the TMEM base word, the dead flag, has_lo[kARing]
+  static constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
+  static constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
 static_assert(kColAlo + kARing * kN == kTmemCols, "TMEM column budget");
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address and
@@ -180,10 +192,15 @@ __device__ __forceinline__ void stage_groups(uint8_t* stage_row, int rsw, const 
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int DG>
+__global__ void __launch_bounds__(Cfg<DG>::kThreads, 1)
 fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ x, const float* __restrict__ filt,
               int K, int corr, const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, int mode,
               float ts, float* __restrict__ out, int64_t rows, int T, unsigned int* status) {
+  using C = Cfg<DG>;
+  constexpr int kThreads = C::kThreads, kIssueWarp = C::kIssueWarp, kProdWarp = C::kProdWarp, kRing = C::kRing;
+  constexpr int kOffRaw = C::kOffRaw, kOffB = C::kOffB, kOffStage = C::kOffStage, kOffSq = C::kOffSq;
+  constexpr int kOffCarry = C::kOffCarry, kOffBar = C::kOffBar, kNumBars = C::kNumBars;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
@@ -236,7 +253,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
   for (int e = tid; e < kN * 96; e += kThreads) {
     const int n = e / 96, k = e - n * 96;
     const int m = corr ? (k - n) : (n + 64 - k);
-    const float v = (m >= 0 && m < K) ? __ldg(filt + m) : 0.f;
+    const float v = (m >= 0 && m < K) ? __fmul_rn(__ldg(filt + m), ts) : 0.f;   // Ts folded into the factor
     const uint32_t hi = tf32_rn(v), lo = tf32_rn(__fsub_rn(v, __uint_as_float(hi)));
     const int kk = k & 31;
     const int off = (k >> 5) * kBBoxBytes + n * 128 + ((((kk >> 2) ^ (n & 7))) << 4) + ((kk & 3) << 2);
@@ -288,9 +305,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       uint32_t ause = 0, tcount = 0;
 #ifdef FIRTC_PROF
       long long t_ready = 0, t_free = 0, t_issue = 0, t_all = clock64();
-#define PROF_T(var, stmt) { long long _t = clock64(); stmt; var += clock64() - _t; }
-#else
-#define PROF_T(var, stmt) stmt;
 #endif
       for (int64_t f = 0; f < total; ++f) {
         if (a >= 2) {
@@ -416,18 +430,31 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     }
   } else {
     // ---------------- drain warps: accumulator -> rows of the result ----------------
-    const int et = tid - kM, ew = warp - 4;      // row inside the block, TMEM lane quarter
+    // DG groups of four warps; with two, group g drains the tiles with (tile counter & 1) == g,
+    // i.e. accumulator g, and the three values a shifted row carries from one tile to the next
+    // travel between the groups through shared memory under a pair of named barriers.
+    const int dg = (warp - 4) >> 2;              // drain group
+    const int et = (tid - kM) & (kM - 1);        // row inside the block
+    const int ew = warp & 3;                     // TMEM lane quarter
     int s_row = 0, e_row = 0;
     float carry[3] = {0.f, 0.f, 0.f};
     int64_t blk = blockIdx.x;
     uint32_t tcount = 0;
-    uint8_t* stage = sm + kOffStage;                        // rows 32 ew .. 32 ew + 31 are this warp's
-    int* sq_s = reinterpret_cast<int*>(sm + kOffSq);
+    uint8_t* stage = sm + kOffStage + dg * kBoxBytes;       // rows 32 ew .. 32 ew + 31 are this warp's
+    int* sq_s = reinterpret_cast<int*>(sm + kOffSq) + dg * kM;
+    float4* carry_s = reinterpret_cast<float4*>(sm + kOffCarry);   // [2][128]
+    const uint32_t n_tiles = (uint32_t)(my_nblk * ntile);
+#ifdef FIRTC_PROF
+    long long d_mma = 0, d_all = clock64();
+#endif
     for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
       const int64_t row = blk * kM + et;
+      bool fresh = true;                          // first tile of this block drained by this group
       for (int tile = 0; tile < ntile; ++tile, ++tcount) {
+        if (DG == 2 && (int)(tcount & 1u) != dg) continue;
         const int acc = (int)(tcount & 1u);
-        const bool ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead);
+        bool ok;
+        PROF_T(d_mma, ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead))
         tc_fence_after();
         uint32_t r0[32], r1[32];
         const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccCols);
@@ -447,7 +474,8 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
 
         const bool live = row < rows && ok;
         float* rowp = out + (live ? row : 0) * (int64_t)T;
-        if (tile == 0) {
+        if (fresh) {
+          fresh = false;
           s_row = 0;
           if (mode != 0 && live) {
             const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
@@ -455,8 +483,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
           }
           e_row = s_row & 3;
           sq_s[et] = s_row >> 2;
-          carry[0] = carry[1] = carry[2] = 0.f;
-          if (live) {
+          if (live && tile == 0) {
             const int gfirst = min(ngroups, s_row >> 2);
             for (int G = 0; G < gfirst; ++G) reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
@@ -473,14 +500,31 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
                 float c = 0.f;
                 for (int q = max(0, po + nd - K + 1); q < nd; ++q)
                   c = fmaf(__ldg(filt + (po + nd - q)), __ldg(xrow + q), c);
-                v[j] = __fsub_rn(v[j], c);
+                v[j] = __fsub_rn(v[j], __fmul_rn(c, ts));
               }
             }
           }
-        }
-        const float ts_row = s_row <= -T ? 0.f : ts;   // a row advanced by T or more is empty
+          if (s_row <= -T) {   // a row advanced by T or more is empty
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ts_row);
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+        }
+        if (tile == 0) carry[0] = carry[1] = carry[2] = 0.f;
+        if (DG == 2 && mode != 0) {
+          // take the previous tile's tail from the other group, then hand over this tile's (in
+          // this order: the slot written here is the one the other group read two tiles ago)
+          if (tcount > 0u) {
+            asm volatile("bar.sync %0, %1;" ::"r"(4 + (int)((tcount - 1u) & 1u)), "n"(2 * kM) : "memory");
+            if (tile > 0) {
+              const float4 c4 = carry_s[((tcount - 1u) & 1u) * kM + et];
+              carry[0] = c4.x; carry[1] = c4.y; carry[2] = c4.z;
+            }
+          }
+          if (tcount + 1u < n_tiles) {
+            carry_s[(tcount & 1u) * kM + et] = make_float4(v[29], v[30], v[31], 0.f);
+            asm volatile("bar.arrive %0, %1;" ::"r"(4 + (int)(tcount & 1u)), "n"(2 * kM) : "memory");
+          }
+        }
         uint8_t* stage_row = stage + et * 128;
         switch (e_row) {
           case 0: stage_groups<0>(stage_row, et & 7, v, carry); break;
@@ -490,12 +534,12 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         }
         carry[0] = v[29]; carry[1] = v[30]; carry[2] = v[31];
         if (tile == ntile - 1 && live) {
-          // the word that holds the carried values, then zeros up to T
+          // the word that holds this tile's last values, then zeros up to T
           const int gl = 8 * ntile + (s_row >> 2);
           if (gl >= 0 && gl < ngroups) {
-            const float w0 = e_row == 1 ? carry[2] : (e_row == 2 ? carry[1] : (e_row == 3 ? carry[0] : 0.f));
-            const float w1 = e_row == 2 ? carry[2] : (e_row == 3 ? carry[1] : 0.f);
-            const float w2 = e_row == 3 ? carry[2] : 0.f;
+            const float w0 = e_row == 1 ? v[31] : (e_row == 2 ? v[30] : (e_row == 3 ? v[29] : 0.f));
+            const float w1 = e_row == 2 ? v[31] : (e_row == 3 ? v[30] : 0.f);
+            const float w2 = e_row == 3 ? v[31] : 0.f;
             reinterpret_cast<float4*>(rowp)[gl] = make_float4(w0, w1, w2, 0.f);
           }
           for (int G = max(gl + 1, 0); G < ngroups; ++G)
@@ -523,6 +567,11 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         __syncwarp();
       }
     }
+#ifdef FIRTC_PROF
+    if (blockIdx.x == 0 && et == 0)
+      printf("drain %d: tiles %u, cycles per tile: total %lld wait_mma %lld\n", dg, tcount, (clock64() - d_all) / tcount,
+             d_mma / tcount);
+#endif
   }
   if (*dead && tid == 0) dev_flag(status, SB_DEV_TMA_TIMEOUT);
   tc_fence_before();
@@ -558,13 +607,21 @@ int fir_tc_try(const float* x, const float* filt, int64_t K, bool corr, const fl
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::kSmemBytes));
+    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
     configured[dev] = true;
   }
   const int64_t nblk = (rows + kM - 1) / kM;
   const int grid = (int)(nblk < sm_count() ? nblk : sm_count());
-  fir_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut, shift, shift_ts, mode, ts,
-                                              out, rows, (int)T, status_ptr());
+  // A shifted write-out is the longer drain: it gets two drain groups.
+  if (mode == 0)
+    fir_tc_kernel<1><<<grid, Cfg<1>::kThreads, Cfg<1>::kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut,
+                                                                        shift, shift_ts, mode, ts, out, rows, (int)T,
+                                                                        status_ptr());
+  else
+    fir_tc_kernel<2><<<grid, Cfg<2>::kThreads, Cfg<2>::kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut,
+                                                                        shift, shift_ts, mode, ts, out, rows, (int)T,
+                                                                        status_ptr());
   SB_CUDA(cudaGetLastError());
   *taken = true;
   return SB_OK;
