@@ -11,10 +11,12 @@
 // the FP32 pipe at 0.43 of the HBM roof; here the multiply-adds run on
 // tcgen05.mma (kind::tf32) and the kernel streams x once and out once.
 //
-// Accuracy: every operand is split as v = hi + lo with hi = v rounded to TF32
-// (10 mantissa bits, cvt.rna) and lo = (v - hi) rounded to TF32; the tile
-// accumulates hi*hi + hi*lo + lo*hi in fp32 (TMEM).  |v - hi - lo| <= 2^-22 |v|
-// and the dropped lo*lo term is <= 2^-22 of the product.  A box of x whose
+// Accuracy: every operand is split as v = hi + lo with hi a TF32 value (10
+// mantissa bits) and lo = v - hi; the tile accumulates hi*hi + hi*lo + lo*hi in
+// fp32 (TMEM).  The filter is split once with round-to-nearest (cvt.rna); x is
+// split per box by truncation (hi = v & mask, lo = v - hi exactly), and the
+// tensor core keeps the top 11 bits of lo.  What is lost per product -- the tail
+// of lo and the lo*lo term -- is below 2^-20 of the product.  A box of x whose
 // values are all exact in TF32 (spike trains) skips its lo products.
 //
 // Data flow per CTA (persistent over 128-row blocks, 1 CTA per SM, 10 warps):
@@ -36,12 +38,14 @@
 //   TMEM columns: 2 x 64 accumulators, 6 x 32 A_hi, 6 x 32 A_lo = 512.
 // Fused delay (axon.delay): shift(corr(g), -d) shifts the output, and
 // conv(shift(x, d)) equals shift(conv(x), d) for d >= 0 (a delay only prepends
-// zeros), so both are the same tiles written at a per-row offset: the drain
-// re-groups the row's 32 values into aligned 128-bit words with a 3-value carry
-// between tiles and zero-fills what the shift uncovers.  A negative delay on the
-// input side (an advance) drops the first |d| samples before the filter sees
-// them; then every row takes two more tiles past T, and advanced rows subtract
-// the dropped samples' contribution from their first K - 1 outputs.
+// zeros), so both are the same tiles written at a per-row offset s = 4 sq + e.
+// The split warps delay the row's operand by e (0..3 steps, the leading values
+// carried over from the row's previous box), so the accumulator already holds
+// the row shifted by e and the drain moves whole 128-bit words by sq and
+// zero-fills what the shift uncovers.  A negative delay on the input side (an
+// advance) drops the first |d| samples before the filter sees them; then every
+// row takes two more tiles past T, and advanced rows subtract the dropped
+// samples' contribution from their first K - 1 outputs.
 // Every mbarrier wait is bounded; a wait that runs out sets a CTA-wide flag that
 // ends all other waits at once, SB_DEV_TMA_TIMEOUT is recorded, and the CTA
 // waits (bounded) for loads and MMAs in flight, frees its TMEM and returns.
@@ -71,25 +75,20 @@ constexpr int kColAlo = kColAhi + kARing * kN;   // 320
 constexpr int kTmemCols = 512;
 constexpr uint32_t kTf32Mask = 0xffffe000u;
 
-// Thread and shared-memory layout for DG drain groups (1 or 2).
-template <int DG>
-struct Cfg {
-  // warps: split 0-3, drain 4 .. 4 + 4 DG - 1, two issue warps, producer warp
-  static constexpr int kIssueWarp = 4 * (1 + DG), kProdWarp = kIssueWarp + 2;
-  static constexpr int kThreads = 32 * (kProdWarp + 1);
-  static constexpr int kRing = DG == 1 ? 11 : 10;                 // landing slots in shared memory
-  static constexpr int kOffRaw = 0;
-  static constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
-  static constexpr int kOffStage = kOffB + 3 * kBBoxBytes;        // output staging, 4 KB private to each drain warp
-  static constexpr int kOffSq = kOffStage + DG * kBoxBytes;       // 128 row shifts (>> 2) per drain group
-  static constexpr int kOffCarry = kOffSq + DG * kM * 4;          // 2 x 128 x 4 floats: a tile's last three values per row
-  static constexpr int kOffBar = kOffCarry + 2 * kM * 16;
-  // barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
-  // then the TMEM base word, the dead flag, has_lo[kARing]
-  static constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
-  static constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-};
+// warps: split 0-3, drain 4-7, two issue warps, producer warp
+constexpr int kIssueWarp = 8, kProdWarp = 10;
+constexpr int kThreads = 32 * (kProdWarp + 1);
+constexpr int kRing = 11;                                // landing slots in shared memory
+constexpr int kOffRaw = 0;
+constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
+constexpr int kOffStage = kOffB + 3 * kBBoxBytes;        // output staging, 4 KB private to each drain warp
+constexpr int kOffSq = kOffStage + kBoxBytes;            // 128 row shifts (>> 2)
+constexpr int kOffBar = kOffSq + kM * 4;
+// barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
+// then the TMEM base word, the dead flag, has_lo[kARing]
+constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
+constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(kColAlo + kARing * kN == kTmemCols, "TMEM column budget");
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address and
@@ -173,34 +172,10 @@ __device__ __forceinline__ uint32_t tf32_rn(float v) {
   return r & kTf32Mask;
 }
 
-// The eight aligned 128-bit words that one tile contributes to a row shifted by
-// 4 * sq + E: word g holds tile values 4g - E .. 4g + 3 - E, the negative
-// indices coming from the previous tile (carry[0..2] = its values 29..31).
-// They go to the staging tile of the row, chunk-swizzled like a TMA box.
-template <int E>
-__device__ __forceinline__ void stage_groups(uint8_t* stage_row, int rsw, const float (&v)[32],
-                                             const float (&carry)[3]) {
-#pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    float w[4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int j = 4 * g + r - E;
-      w[r] = j >= 0 ? v[j >= 0 ? j : 0] : carry[j < 0 ? 3 + j : 0];
-    }
-    *reinterpret_cast<float4*>(stage_row + ((g ^ rsw) << 4)) = make_float4(w[0], w[1], w[2], w[3]);
-  }
-}
-
-template <int DG>
-__global__ void __launch_bounds__(Cfg<DG>::kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ x, const float* __restrict__ filt,
               int K, int corr, const float* __restrict__ lut, int64_t n_lut, float shift, float shift_ts, int mode,
               float ts, float* __restrict__ out, int64_t rows, int T, unsigned int* status) {
-  using C = Cfg<DG>;
-  constexpr int kThreads = C::kThreads, kIssueWarp = C::kIssueWarp, kProdWarp = C::kProdWarp, kRing = C::kRing;
-  constexpr int kOffRaw = C::kOffRaw, kOffB = C::kOffB, kOffStage = C::kOffStage, kOffSq = C::kOffSq;
-  constexpr int kOffCarry = C::kOffCarry, kOffBar = C::kOffBar, kNumBars = C::kNumBars;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
@@ -266,7 +241,8 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
   tc_fence_after();
   const uint32_t tmem = *tmem_word;
 
-  const int nt = (T + kN - 1) / kN;
+  // a shifted row's filter output is delayed by up to 3 steps before it is moved by whole words
+  const int nt = (T + (mode != 0 ? 3 : 0) + kN - 1) / kN;
   const int ntile = nt + (wrong ? 2 : 0);
   const int narr = ntile + 2;                 // boxes per block
   const int qoff = corr ? 2 : 0;
@@ -371,11 +347,29 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     __syncwarp();
   } else if (warp < 4) {
     // ---------------- split warps: landing slot -> hi / lo in TMEM ----------------
-    int slot = 0, as = 0;
+    // A row shifted by s = 4 sq + e (e in 0..3) is filtered from its input delayed by e: the
+    // operand row is W[k - e], the e leading values carried over from the previous box of the
+    // row, so what the drain sees is already shifted by e and it only moves whole 128-bit words.
+    int slot = 0, as = 0, a = 0, e_row = 0;
     uint32_t use = 0, ause = 0;
+    uint32_t p0 = 0, p1 = 0, p2 = 0;            // the previous box's values 29..31 of this row
+    int64_t blk = blockIdx.x;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+#ifdef FIRTC_PROF
+    long long s_full = 0, s_afree = 0, s_all = clock64();
+#endif
     for (int64_t f = 0; f < total; ++f) {
-      wait_or_dead(bar_full + 8 * slot, use & 1u, dead);
+      if (a == 0) {
+        e_row = 0;
+        const int64_t row = blk * kM + tid;
+        if (mode != 0 && row < rows) {
+          const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
+          e_row = (max(-T, min(T, __float2int_rz(__fdiv_rn(sv, shift_ts)))) * mode) & 3;
+        }
+        p0 = p1 = p2 = 0;
+      }
+      if (++a == narr) { a = 0; blk += gridDim.x; }
+      PROF_T(s_full, wait_or_dead(bar_full + 8 * slot, use & 1u, dead))
       const uint8_t* rowp = sm + kOffRaw + slot * kBoxBytes + tid * 128;
       uint32_t xr[32];
       uint32_t low = 0;
@@ -385,6 +379,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         xr[4 * c] = q.x; xr[4 * c + 1] = q.y; xr[4 * c + 2] = q.z; xr[4 * c + 3] = q.w;
         low |= q.x | q.y | q.z | q.w;
       }
+      low |= p0 | p1 | p2;   // values carried in from the previous box land in this operand too
       // Does any value of the box need a lo part?  (Spike trains do not.)  The
       // barrier also orders every thread's reads of the slot before its release.
       int any;
@@ -400,16 +395,31 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
 #ifdef FIRTC_NO_SPLIT
       any = 0;
 #endif
+      if (mode != 0) {
+        // delay the row by e steps without diverging: by 2 if (e & 2), then by 1 if (e & 1)
+        const uint32_t n0 = xr[29], n1 = xr[30], n2 = xr[31];
+        const bool by2 = (e_row & 2) != 0, by1 = (e_row & 1) != 0;
+        uint32_t t0 = by2 ? p0 : p2;             // element -1 after the first stage
+#pragma unroll
+        for (int j = 31; j >= 2; --j) xr[j] = by2 ? xr[j - 2] : xr[j];
+        xr[1] = by2 ? p2 : xr[1];
+        xr[0] = by2 ? p1 : xr[0];
+#pragma unroll
+        for (int j = 31; j >= 1; --j) xr[j] = by1 ? xr[j - 1] : xr[j];
+        xr[0] = by1 ? t0 : xr[0];
+        p0 = n0; p1 = n1; p2 = n2;
+      }
       // the MMAs that read this operand slot's previous box have completed?
-      if (ause >= 1) wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
+      if (ause >= 1) PROF_T(s_afree, wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead))
       tc_fence_after();
       if (any) {
         uint32_t lo[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float v = __uint_as_float(xr[j]);
-          const uint32_t h = tf32_rn(v);
-          lo[j] = tf32_rn(__fsub_rn(v, __uint_as_float(h)));
+          // hi = x truncated to TF32 (exact in the operand format), lo = x - hi exactly (13
+          // bits, of which the tensor core keeps 11): two instructions per value
+          const uint32_t h = xr[j] & kTf32Mask;
+          lo[j] = __float_as_uint(__fsub_rn(__uint_as_float(xr[j]), __uint_as_float(h)));
           xr[j] = h;
         }
 #ifndef FIRTC_NO_TST
@@ -428,30 +438,27 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       if (++slot == kRing) { slot = 0; ++use; }
       if (++as == kARing) { as = 0; ++ause; }
     }
+#ifdef FIRTC_PROF
+    if (blockIdx.x == 0 && tid == 0)
+      printf("split: boxes %lld, cycles per box: total %lld wait_full %lld wait_afree %lld\n", (long long)total,
+             (clock64() - s_all) / total, s_full / total, s_afree / total);
+#endif
   } else {
     // ---------------- drain warps: accumulator -> rows of the result ----------------
-    // DG groups of four warps; with two, group g drains the tiles with (tile counter & 1) == g,
-    // i.e. accumulator g, and the three values a shifted row carries from one tile to the next
-    // travel between the groups through shared memory under a pair of named barriers.
-    const int dg = (warp - 4) >> 2;              // drain group
-    const int et = (tid - kM) & (kM - 1);        // row inside the block
+    // Rows differ only in the word offset sq of their shift.
+    const int et = tid - kM;                     // row inside the block
     const int ew = warp & 3;                     // TMEM lane quarter
-    int s_row = 0, e_row = 0;
-    float carry[3] = {0.f, 0.f, 0.f};
+    int s_row = 0;
     int64_t blk = blockIdx.x;
     uint32_t tcount = 0;
-    uint8_t* stage = sm + kOffStage + dg * kBoxBytes;       // rows 32 ew .. 32 ew + 31 are this warp's
-    int* sq_s = reinterpret_cast<int*>(sm + kOffSq) + dg * kM;
-    float4* carry_s = reinterpret_cast<float4*>(sm + kOffCarry);   // [2][128]
-    const uint32_t n_tiles = (uint32_t)(my_nblk * ntile);
+    uint8_t* stage = sm + kOffStage;                        // rows 32 ew .. 32 ew + 31 are this warp's
+    int* sq_s = reinterpret_cast<int*>(sm + kOffSq);
 #ifdef FIRTC_PROF
     long long d_mma = 0, d_all = clock64();
 #endif
     for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
       const int64_t row = blk * kM + et;
-      bool fresh = true;                          // first tile of this block drained by this group
       for (int tile = 0; tile < ntile; ++tile, ++tcount) {
-        if (DG == 2 && (int)(tcount & 1u) != dg) continue;
         const int acc = (int)(tcount & 1u);
         bool ok;
         PROF_T(d_mma, ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead))
@@ -474,23 +481,25 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
 
         const bool live = row < rows && ok;
         float* rowp = out + (live ? row : 0) * (int64_t)T;
-        if (fresh) {
-          fresh = false;
+        if (tile == 0) {
           s_row = 0;
           if (mode != 0 && live) {
             const float sv = lut ? __ldg(lut + (row % n_lut)) : shift;
             s_row = max(-T, min(T, __float2int_rz(__fdiv_rn(sv, shift_ts)))) * mode;
           }
-          e_row = s_row & 3;
           sq_s[et] = s_row >> 2;
-          if (live && tile == 0) {
+          if (live) {
+            // zeros before the row's first word and after its last one
             const int gfirst = min(ngroups, s_row >> 2);
             for (int G = 0; G < gfirst; ++G) reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int G = max(8 * ntile + (s_row >> 2), 0); G < ngroups; ++G)
+              reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
         if (mode > 0 && s_row < 0 && live) {
-          // advance by nd: outputs 0 .. K-2 must not see x[0 .. nd)
-          const int nd = -s_row, tbase = kN * tile;
+          // advance by nd: outputs 0 .. K-2 must not see x[0 .. nd).  Tile value j sits at
+          // output 32 tile + j + s_row - e (the tile is already delayed by e = s_row & 3).
+          const int nd = -s_row, tbase = kN * tile - (s_row & 3);
           if (tbase < nd + K - 1 && tbase + kN > nd) {
             const float* xrow = x + row * (int64_t)T;
 #pragma unroll
@@ -509,41 +518,20 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
           }
         }
-        if (tile == 0) carry[0] = carry[1] = carry[2] = 0.f;
-        if (DG == 2 && mode != 0) {
-          // take the previous tile's tail from the other group, then hand over this tile's (in
-          // this order: the slot written here is the one the other group read two tiles ago)
-          if (tcount > 0u) {
-            asm volatile("bar.sync %0, %1;" ::"r"(4 + (int)((tcount - 1u) & 1u)), "n"(2 * kM) : "memory");
-            if (tile > 0) {
-              const float4 c4 = carry_s[((tcount - 1u) & 1u) * kM + et];
-              carry[0] = c4.x; carry[1] = c4.y; carry[2] = c4.z;
-            }
-          }
-          if (tcount + 1u < n_tiles) {
-            carry_s[(tcount & 1u) * kM + et] = make_float4(v[29], v[30], v[31], 0.f);
-            asm volatile("bar.arrive %0, %1;" ::"r"(4 + (int)(tcount & 1u)), "n"(2 * kM) : "memory");
-          }
+        if (mode < 0 && tile == 0) {
+          // corr reaches forward, so its output is not zero before t = 0; the e values the
+          // delayed operand puts there belong to the zero fill
+          const int e = s_row & 3;
+          if (e > 0) v[0] = 0.f;
+          if (e > 1) v[1] = 0.f;
+          if (e > 2) v[2] = 0.f;
         }
-        uint8_t* stage_row = stage + et * 128;
-        switch (e_row) {
-          case 0: stage_groups<0>(stage_row, et & 7, v, carry); break;
-          case 1: stage_groups<1>(stage_row, et & 7, v, carry); break;
-          case 2: stage_groups<2>(stage_row, et & 7, v, carry); break;
-          default: stage_groups<3>(stage_row, et & 7, v, carry); break;
-        }
-        carry[0] = v[29]; carry[1] = v[30]; carry[2] = v[31];
-        if (tile == ntile - 1 && live) {
-          // the word that holds this tile's last values, then zeros up to T
-          const int gl = 8 * ntile + (s_row >> 2);
-          if (gl >= 0 && gl < ngroups) {
-            const float w0 = e_row == 1 ? v[31] : (e_row == 2 ? v[30] : (e_row == 3 ? v[29] : 0.f));
-            const float w1 = e_row == 2 ? v[31] : (e_row == 3 ? v[30] : 0.f);
-            const float w2 = e_row == 3 ? v[31] : 0.f;
-            reinterpret_cast<float4*>(rowp)[gl] = make_float4(w0, w1, w2, 0.f);
-          }
-          for (int G = max(gl + 1, 0); G < ngroups; ++G)
-            reinterpret_cast<float4*>(rowp)[G] = make_float4(0.f, 0.f, 0.f, 0.f);
+        {
+          uint8_t* stage_row = stage + et * 128;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(stage_row + ((g ^ (et & 7)) << 4)) =
+                make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         }
         __syncwarp();
         // coalesced write-out of the warp's 32 rows: an instruction covers 4 rows x 128 bytes
@@ -569,7 +557,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     }
 #ifdef FIRTC_PROF
     if (blockIdx.x == 0 && et == 0)
-      printf("drain %d: tiles %u, cycles per tile: total %lld wait_mma %lld\n", dg, tcount, (clock64() - d_all) / tcount,
+      printf("drain: tiles %u, cycles per tile: total %lld wait_mma %lld\n", tcount, (clock64() - d_all) / tcount,
              d_mma / tcount);
 #endif
   }
@@ -607,21 +595,13 @@ int fir_tc_try(const float* x, const float* filt, int64_t K, bool corr, const fl
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::kSmemBytes));
-    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
+    SB_CUDA(cudaFuncSetAttribute(fir_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured[dev] = true;
   }
   const int64_t nblk = (rows + kM - 1) / kM;
   const int grid = (int)(nblk < sm_count() ? nblk : sm_count());
-  // A shifted write-out is the longer drain: it gets two drain groups.
-  if (mode == 0)
-    fir_tc_kernel<1><<<grid, Cfg<1>::kThreads, Cfg<1>::kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut,
-                                                                        shift, shift_ts, mode, ts, out, rows, (int)T,
-                                                                        status_ptr());
-  else
-    fir_tc_kernel<2><<<grid, Cfg<2>::kThreads, Cfg<2>::kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut,
-                                                                        shift, shift_ts, mode, ts, out, rows, (int)T,
-                                                                        status_ptr());
+  fir_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(xmap, x, filt, (int)K, corr ? 1 : 0, lut, n_lut, shift, shift_ts, mode,
+                                                    ts, out, rows, (int)T, status_ptr());
   SB_CUDA(cudaGetLastError());
   *taken = true;
   return SB_OK;
