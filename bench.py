@@ -60,7 +60,8 @@ NCU_TRAFFIC_PER_UNIT = {
     'li_fwd': 7.76,
     'li_bwd': 7.74,
     'shift': 7.63,
-    'delay_fir_fwd': 7.62,
+    'fir_conv': 7.77,
+    'delay_fir_fwd': 7.75,
 }
 
 
@@ -596,18 +597,20 @@ def main():
                 'algorithmic_bytes_per_unit': wl.bpu, 'kernel_ms': kern_ms, 'kernel_ms_min': min(per),
                 'frac_of_nominal_8TBps': achieved / 8000.0}
     if 'fir' in wl.name:
-        # 64 FMAs per 8-byte unit: the FP32 pipe (SMs x 128 lanes x clock) caps this kernel below the HBM roof
+        # 64 taps per 8-byte unit run on the tensor cores (banded matrix product, tcgen05 kind::tf32, three
+        # TF32 products per term, two when the input is exact in TF32): the bound is HBM again.  The FP32
+        # sliding-window kernel that small or unaligned problems still take is capped by the FMA pipe at
+        # SMs x 128 lanes x clock / 64 units per second.
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         clk = (clocks.summary()['sm_mhz'] or 1965.0) * 1e6
-        fma_cap_units = sms * 128 * clk / 64.0
-        roofline['fp32_fma_ceiling_GBps'] = fma_cap_units * wl.bpu / 1e9
-        roofline['frac_of_fp32_fma_ceiling'] = (units / (kern_ms * 1e-3)) / fma_cap_units
+        roofline['math'] = 'tcgen05.mma kind::tf32, hi*hi + hi*lo + lo*hi, fp32 accumulate in TMEM'
+        roofline['fp32_fma_ceiling_of_simt_kernel_GBps'] = sms * 128 * clk / 64.0 * wl.bpu / 1e9
 
     line = {
         'metric': f'neuron-steps/sec ({wl.name})' if wl.unit.startswith('neuron') else f'elements/sec ({wl.name})',
         'value': value, 'unit': wl.unit, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-        'dtype': 'int32+f32', 'data': 'synthetic',
+        'dtype': 'f32 (3xTF32 products, fp32 accumulate)' if 'fir' in wl.name else 'int32+f32', 'data': 'synthetic',
         'config': {'workload': f'{wl.name} {list(shape)} per GPU', 'global_batch': shape[0] * world,
                    'l2': 'inputs larger than L2 (no flush)', 'parallelism': f'batch shards x{world}, no forward collective'},
         'gpu_launches': args.steps * launches_per_step,

@@ -50,17 +50,8 @@
 // ends all other waits at once, SB_DEV_TMA_TIMEOUT is recorded, and the CTA
 // waits (bounded) for loads and MMAs in flight, frees its TMEM and returns.
 #include "api_util.cuh"
-#ifdef FIRTC_PROF
-#include <cstdio>
-#endif
 
 using namespace sb;
-
-#ifdef FIRTC_PROF
-#define PROF_T(var, stmt) { long long _t = clock64(); stmt; var += clock64() - _t; }
-#else
-#define PROF_T(var, stmt) stmt;
-#endif
 
 namespace {
 
@@ -279,23 +270,14 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       const uint32_t b0 = desc_lo(base + kOffB);
       int a = 0, as = 0, as1 = 0, as2 = 0;    // operand slots of this arrival and the two before it
       uint32_t ause = 0, tcount = 0;
-#ifdef FIRTC_PROF
-      long long t_ready = 0, t_free = 0, t_issue = 0, t_all = clock64();
-#endif
       for (int64_t f = 0; f < total; ++f) {
         if (a >= 2) {
           if ((tcount & 1u) == me) {
             const uint32_t acc = me;
             bool ok2;
-            PROF_T(t_ready, ok2 = wait_or_dead(bar_aready + 8 * as, ause & 1u, dead))
-            if (tcount >= 2) PROF_T(t_free, ok2 = wait_or_dead(bar_free + 8 * acc, ((tcount >> 1) - 1u) & 1u, dead) && ok2)
+            ok2 = wait_or_dead(bar_aready + 8 * as, ause & 1u, dead);
+            if (tcount >= 2) ok2 = wait_or_dead(bar_free + 8 * acc, ((tcount >> 1) - 1u) & 1u, dead) && ok2;
             tc_fence_after();
-#ifdef FIRTC_PROF
-            long long _ti = clock64();
-#endif
-#ifdef FIRTC_NO_MMA
-            ok2 = false;
-#endif
             if (ok2) {
               const uint32_t d_tmem = tmem + acc * kAccCols;
               const int slots[3] = {as2, as1, as};
@@ -314,9 +296,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
               }
             }
             umma_commit(bar_mma + 8 * acc);
-#ifdef FIRTC_PROF
-            t_issue += clock64() - _ti;
-#endif
           }
           // Operand slots nobody reads after the tile of this arrival: its oldest
           // box, and at the end of a block the two newer ones as well.  Both issue
@@ -332,12 +311,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         as2 = as1; as1 = as;
         if (++as == kARing) { as = 0; ++ause; }
       }
-#ifdef FIRTC_PROF
-      if (blockIdx.x == 0 && me == 0)
-        printf("issuer: tiles %u total %lld  wait_ready %lld  wait_free %lld  issue %lld (cycles per tile: %lld %lld %lld %lld)\n",
-               tcount, clock64() - t_all, t_ready, t_free, t_issue, (clock64() - t_all) / tcount, t_ready / tcount,
-               t_free / tcount, t_issue / tcount);
-#endif
       // nothing may still be writing TMEM when it is freed: wait for this thread's last tile
       if (tcount > me) {
         const uint32_t last = ((tcount - 1u - me) & ~1u) + me;
@@ -355,9 +328,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     uint32_t p0 = 0, p1 = 0, p2 = 0;            // the previous box's values 29..31 of this row
     int64_t blk = blockIdx.x;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-#ifdef FIRTC_PROF
-    long long s_full = 0, s_afree = 0, s_all = clock64();
-#endif
     for (int64_t f = 0; f < total; ++f) {
       if (a == 0) {
         e_row = 0;
@@ -369,7 +339,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         p0 = p1 = p2 = 0;
       }
       if (++a == narr) { a = 0; blk += gridDim.x; }
-      PROF_T(s_full, wait_or_dead(bar_full + 8 * slot, use & 1u, dead))
+      wait_or_dead(bar_full + 8 * slot, use & 1u, dead);
       const uint8_t* rowp = sm + kOffRaw + slot * kBoxBytes + tid * 128;
       uint32_t xr[32];
       uint32_t low = 0;
@@ -392,9 +362,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
           : "r"(low & ~kTf32Mask), "n"(kM)
           : "memory");
       mbar_arrive(bar_rawfree + 8 * slot);
-#ifdef FIRTC_NO_SPLIT
-      any = 0;
-#endif
       if (mode != 0) {
         // delay the row by e steps without diverging: by 2 if (e & 2), then by 1 if (e & 1)
         const uint32_t n0 = xr[29], n1 = xr[30], n2 = xr[31];
@@ -410,7 +377,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         p0 = n0; p1 = n1; p2 = n2;
       }
       // the MMAs that read this operand slot's previous box have completed?
-      if (ause >= 1) PROF_T(s_afree, wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead))
+      if (ause >= 1) wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
       tc_fence_after();
       if (any) {
         uint32_t lo[32];
@@ -422,27 +389,16 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
           lo[j] = __float_as_uint(__fsub_rn(__uint_as_float(xr[j]), __uint_as_float(h)));
           xr[j] = h;
         }
-#ifndef FIRTC_NO_TST
         tmem_st32(tmem + lane_base + kColAlo + as * kN, lo);
-#endif
       }
-#ifndef FIRTC_NO_TST
       tmem_st32(tmem + lane_base + kColAhi + as * kN, xr);
       tmem_st_wait();
-#else
-      if (xr[0] == 0x12345678u && xr[5] == 77u) *dead = 2;
-#endif
       tc_fence_before();
       if (tid == 0) has_lo[as] = any;
       mbar_arrive(bar_aready + 8 * as);
       if (++slot == kRing) { slot = 0; ++use; }
       if (++as == kARing) { as = 0; ++ause; }
     }
-#ifdef FIRTC_PROF
-    if (blockIdx.x == 0 && tid == 0)
-      printf("split: boxes %lld, cycles per box: total %lld wait_full %lld wait_afree %lld\n", (long long)total,
-             (clock64() - s_all) / total, s_full / total, s_afree / total);
-#endif
   } else {
     // ---------------- drain warps: accumulator -> rows of the result ----------------
     // Rows differ only in the word offset sq of their shift.
@@ -453,26 +409,18 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     uint32_t tcount = 0;
     uint8_t* stage = sm + kOffStage;                        // rows 32 ew .. 32 ew + 31 are this warp's
     int* sq_s = reinterpret_cast<int*>(sm + kOffSq);
-#ifdef FIRTC_PROF
-    long long d_mma = 0, d_all = clock64();
-#endif
     for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
       const int64_t row = blk * kM + et;
       for (int tile = 0; tile < ntile; ++tile, ++tcount) {
         const int acc = (int)(tcount & 1u);
         bool ok;
-        PROF_T(d_mma, ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead))
+        ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead);
         tc_fence_after();
         uint32_t r0[32], r1[32];
         const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccCols);
-#ifndef FIRTC_NO_TLD
         tmem_ld32(taddr, r0);
         tmem_ld32(taddr + kN, r1);
         tmem_ld_wait();
-#else
-#pragma unroll
-        for (int j = 0; j < 32; ++j) { r0[j] = taddr + j; r1[j] = tcount; }
-#endif
         tc_fence_before();
         mbar_arrive(bar_free + 8 * acc);
         float v[32];
@@ -535,11 +483,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         }
         __syncwarp();
         // coalesced write-out of the warp's 32 rows: an instruction covers 4 rows x 128 bytes
-#ifdef FIRTC_NO_STORE
-        if (ok && v[0] == 123.456f) {
-#else
         if (ok) {
-#endif
           const int g = lane & 7;
           const int rl0 = ew * 32 + (lane >> 3);
           float* orow = out + (blk * kM + rl0) * (int64_t)T;
@@ -555,11 +499,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         __syncwarp();
       }
     }
-#ifdef FIRTC_PROF
-    if (blockIdx.x == 0 && et == 0)
-      printf("drain: tiles %u, cycles per tile: total %lld wait_mma %lld\n", tcount, (clock64() - d_all) / tcount,
-             d_mma / tcount);
-#endif
   }
   if (*dead && tid == 0) dev_flag(status, SB_DEV_TMA_TIMEOUT);
   tc_fence_before();
