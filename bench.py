@@ -117,6 +117,8 @@ WORKLOADS = {
     # headline: fused CUBA forward, x in, spike + voltage out = 12 B per neuron-step
     'cuba_fwd': Workload('cuba_fwd', (64, 8192, 2000), 12),
     'cuba_fwd_cfg0': Workload('cuba_fwd_cfg0', (16, 512, 1000), 12),
+    # block output path: spikes written one step late plus a per-neuron axonal delay of 0..62 steps, same 12 B
+    'cuba_fwd_delayed': Workload('cuba_fwd_delayed', (64, 8192, 2000), 12),
     # backward of the same: g_spike + voltage in, g_x out
     'cuba_bwd': Workload('cuba_bwd', (64, 8192, 2000), 12),
     'alif_fwd': Workload('alif_fwd', (64, 4096, 2000), 16),
@@ -199,6 +201,15 @@ def build_step(name, shape, device, seed):
         def step():
             N.call('sb_probe_stream', src, N.ptr(src), N.ptr(dst), n, r, w, N.stream_of(src))
         return step, 1, (src, dst)
+    if name == 'cuba_fwd_delayed':
+        cd, vd = one(1024), one(123)
+        gen = torch.Generator(device=device).manual_seed(seed + 1)
+        d['delay'] = torch.randint(0, 63, (C,), device=device, generator=gen).float()
+
+        def step():
+            return _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=False, want_spike=True,
+                                 spike_delay=1, axon_delay=d['delay'])
+        return step, 1, d
     if name.startswith('cuba_fwd'):
         cd, vd = one(1024), one(123)
 

@@ -46,6 +46,7 @@ extern "C" {
 
 /* bits of sb_device_status() */
 #define SB_DEV_TMA_TIMEOUT 1u /* a bulk tensor load did not arrive within the bounded wait */
+#define SB_DEV_BAD_DELAY 2u   /* a fused axonal delay was outside 0..62 steps and was clamped */
 
 /* Row geometry shared by all time-recurrent entry points. */
 typedef struct sb_geom {
@@ -160,12 +161,18 @@ int sb_cspike_bwd(const float* re, const float* im, const float* thr_tensor, flo
  * spike_out[t] = spike[t-1], which is the one-step inter-layer delay of the
  * blocks (block/base.py:15-39) at no extra memory traffic; delay_head
  * (nullable float[rows]) supplies spike_out[0], else 0.  final_s stays the
- * undelayed last spike. */
+ * undelayed last spike.
+ * axon_delay (nullable float[n_axon_delay], n_axon_delay = rows_per_batch;
+ * binary spikes only) folds the block's axonal delay (axon/delay.py:150-175,
+ * applied after the step delay at block/base.py:551-552) into the same store:
+ * row r is written int(axon_delay[r % n] / axon_delay_ts) steps later still,
+ * zero filled.  Delays must lie in 0..62 steps; others are clamped and
+ * SB_DEV_BAD_DELAY is set in the device status word. */
 int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
                 float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
                 int w_scale, int graded, float spike_scale, int spike_delay, const float* delay_head,
-                void* stream);
+                const float* axon_delay, int64_t n_axon_delay, float axon_delay_ts, void* stream);
 /* Backward of CUBA and ALIF forward: surrogate gradient + both integrators.
  * thr_tensor (nullable): per-element threshold (ALIF passes th + ref).
  * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch.

@@ -50,11 +50,13 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
                 const float* cstate, const float* vstate, float* current, float* voltage, float* spike,
                 float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
                 int w_scale, int graded, float spike_scale, int spike_delay, const float* delay_head,
-                void* stream) {
+                const float* axon_delay, int64_t n_axon_delay, float axon_delay_ts, void* stream) {
   RowGeom rg;
   SB_REQUIRE(spike_delay == 0 || (spike_delay == 1 && spike != nullptr && !graded),
              "the fused one-step delay needs binary spike output");
-  const BitDelay bd{spike_delay, delay_head};
+  SB_REQUIRE(axon_delay == nullptr || (spike != nullptr && !graded && n_axon_delay > 0 && axon_delay_ts != 0.f),
+             "the fused axonal delay needs binary spike output, a delay table and a non-zero sampling time");
+  const BitDelay bd{spike_delay, delay_head, axon_delay, n_axon_delay, axon_delay_ts};
   SB_TRY(check_count(n_cdecay, "current decay"));
   SB_TRY(check_count(n_vdecay, "voltage decay"));
   const int64_t nmax = maxn({n_cdecay, n_vdecay});

@@ -108,17 +108,50 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // one-step inter-layer delay of lava-dl's blocks (block/base.py:15-39) folded
 // into the store.  The bit that enters at t = 0 is head[row] != 0 (the spike a
 // persistent-state block carried over from its previous call), 0 without head.
+// lut adds a per-row axonal delay on top (axon/delay.py:150-175 after the step
+// delay, block/base.py:549-552): row r is written int(lut[r % n_lut] / lut_ts)
+// steps later still, 0 .. 62.  A lane keeps the masks of its row's last two
+// boxes and takes each output word out of that 96-bit window with a funnel
+// shift, so the delay costs no memory traffic.
 template <int N>
 struct BitPtrs {
   float* p[N > 0 ? N : 1];
   const float* head;
   int delay;
+  const float* lut;
+  int64_t n_lut;
+  float lut_ts;
 };
 
 struct BitDelay {
   int steps;          // 0 or 1
   const float* head;  // [rows] or null
+  const float* lut;   // per-row delays or null
+  int64_t n_lut;
+  float lut_ts;
 };
+
+constexpr int kMaxBitDelay = 62;  // per-row delay; with the step delay the window shift stays below 64
+
+// Total shift of a row's bit stream (step delay + per-row delay); a delay outside
+// 0 .. kMaxBitDelay is clamped and reported in the device status word.
+__device__ __forceinline__ int bit_shift_of_row(int steps, const float* lut, int64_t n_lut, float lut_ts, int64_t row,
+                                                bool valid, unsigned int* status) {
+  int sh = steps;
+  if (lut != nullptr && valid) {
+    int d = __float2int_rz(__fdiv_rn(__ldg(lut + (row % n_lut)), lut_ts));
+    if (d < 0 || d > kMaxBitDelay) {
+      dev_flag(status, SB_DEV_BAD_DELAY);
+      d = d < 0 ? 0 : kMaxBitDelay;
+    }
+    sh += d;
+  }
+  return sh;
+}
+// Output word of the current box: bits [64 - sh, 96 - sh) of (m : prev1 : prev2).
+__device__ __forceinline__ uint32_t delayed_word(uint32_t m, uint32_t prev1, uint32_t prev2, int sh) {
+  return sh < 32 ? __funnelshift_l(prev1, m, sh) : __funnelshift_l(prev2, prev1, sh - 32);
+}
 
 template <int NB, int TW>
 __device__ __forceinline__ void store_bit_rows(float* __restrict__ base, int64_t T, int nrows, int nvalid,
@@ -218,8 +251,14 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
   const bool valid = row < g.rows;
   op.init(p, g, row, valid);
 
-  uint32_t carry = 0u;  // last bit of the previous box when bit outputs are delayed by one step
-  if (NBIT > 0 && bitout.delay && bitout.head != nullptr && valid) carry = (__ldg(bitout.head + row) != 0.f) ? 1u : 0u;
+  // delayed bit outputs: the masks of the row's last two boxes and the row's shift
+  uint32_t prev1 = 0u, prev2 = 0u;
+  const bool delayed = NBIT > 0 && (bitout.delay != 0 || bitout.lut != nullptr);
+  int sh = 0;
+  if (delayed) {
+    sh = bit_shift_of_row(bitout.delay, bitout.lut, bitout.n_lut, bitout.lut_ts, row, valid, status);
+    if (bitout.delay && bitout.head != nullptr && valid) prev1 = (__ldg(bitout.head + row) != 0.f) ? 0x80000000u : 0u;
+  }
 
   int issued = 0;
   if (lane == 0) {
@@ -247,10 +286,11 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
         else process_tile<Op, false, TW>(op, box, lane, nvalid, boxbits);
         op.tile_end();
       }
-      if (NBIT > 0 && bitout.delay) {  // forward ops only: boxes come in time order
+      if (delayed) {  // forward ops only: boxes come in time order (32-step boxes)
         const uint32_t m = boxbits[0];
-        boxbits[0] = (m << 1) | carry;
-        carry = (m >> (TW - 1)) & 1u;
+        boxbits[0] = delayed_word(m, prev1, prev2, sh);
+        prev2 = prev1;
+        prev1 = m;
       }
 #pragma unroll
       for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) bits[d][b] = boxbits[d];
@@ -309,7 +349,6 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, c
   const int64_t row0 = wid * kTileR;
   if (row0 >= g.rows) return;
   uint8_t* stage = smem + (size_t)warp * NT * kTileBytes;
-  (void)status;
 
   const int T = g.T;
   const int ntiles = (T + kTileT - 1) / kTileT;
@@ -320,8 +359,13 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, c
   const bool valid = row < g.rows;
   op.init(p, g, row, valid);
 
-  uint32_t carry = 0u;
-  if (NBIT > 0 && bd.steps && bd.head != nullptr && valid) carry = (__ldg(bd.head + row) != 0.f) ? 1u : 0u;
+  uint32_t prev1 = 0u, prev2 = 0u;
+  const bool delayed = NBIT > 0 && (bd.steps != 0 || bd.lut != nullptr);
+  int sh = 0;
+  if (delayed) {
+    sh = bit_shift_of_row(bd.steps, bd.lut, bd.n_lut, bd.lut_ts, row, valid, status);
+    if (bd.steps && bd.head != nullptr && valid) prev1 = (__ldg(bd.head + row) != 0.f) ? 0x80000000u : 0u;
+  }
 
   for (int k = 0; k < ntiles; ++k) {
     const int t0 = (Op::REVERSE ? (ntiles - 1 - k) : k) * kTileT;
@@ -344,10 +388,11 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, c
     if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT, bits);
     else process_tile<Op, false, 32>(op, stage, lane, nvalid, bits);
     op.tile_end();
-    if (NBIT > 0 && bd.steps) {
+    if (delayed) {
       const uint32_t m = bits[0];
-      bits[0] = (m << 1) | carry;
-      carry = (m >> 31) & 1u;
+      bits[0] = delayed_word(m, prev1, prev2, sh);
+      prev2 = prev1;
+      prev1 = m;
     }
     __syncwarp();
 #pragma unroll
@@ -401,7 +446,7 @@ template <class Op> constexpr int pipe_tile() { return Op::TILE; }
 
 template <class Op, int STAGES = pipe_stages<Op>(), int NB = pipe_boxes<Op>(), int TW = pipe_tile<Op>()>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
-                   cudaStream_t st, BitDelay bit_delay = BitDelay{0, nullptr}) {
+                   cudaStream_t st, BitDelay bit_delay = BitDelay{0, nullptr, nullptr, 0, 1.f}) {
   // NOUT counts the outputs that travel through shared memory; the NBIT bit
   // outputs follow them in `out`.
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
@@ -414,10 +459,16 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
   for (int i = 0; i < NIN + NOUT; ++i) SB_REQUIRE(all[i] != nullptr, "null tensor pointer (slot %d)", i);
   SB_REQUIRE(bit_delay.steps == 0 || (bit_delay.steps == 1 && NBIT == 1 && !Op::REVERSE),
              "a one-step output delay exists only for ops with one bit output");
+  SB_REQUIRE(bit_delay.lut == nullptr || (NBIT == 1 && !Op::REVERSE && TW == 32 && bit_delay.n_lut > 0 &&
+                                          g.rows % bit_delay.n_lut == 0 && bit_delay.lut_ts != 0.f),
+             "a per-row output delay needs one bit output, 32-step tiles and a table that tiles the rows");
   BitPtrs<NBIT> bitout;
   bitout.p[0] = nullptr;
   bitout.head = bit_delay.head;
   bitout.delay = bit_delay.steps;
+  bitout.lut = bit_delay.lut;
+  bitout.n_lut = bit_delay.n_lut;
+  bitout.lut_ts = bit_delay.lut_ts;
   for (int d = 0; d < NBIT; ++d) {
     SB_REQUIRE(out[NOUT + d] != nullptr, "null tensor pointer (bit output %d)", d);
     bitout.p[d] = out[NOUT + d];

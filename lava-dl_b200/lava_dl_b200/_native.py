@@ -49,7 +49,7 @@ SIGNATURES = {
     'sb_cspike_fwd': (c_int, [_P, _P, _P, c_float, _P, _P, _I64, _I64, c_int, c_float, _P]),
     'sb_cspike_bwd': (c_int, [_P, _P, _P, c_float, _P, _P, _P, _I64, c_float, c_float, c_int, _P]),
     'sb_cuba_fwd': (c_int, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _G,
-                            c_double, c_int, c_int, c_float, c_int, _P, _P]),
+                            c_double, c_int, c_int, c_float, c_int, _P, _P, _I64, c_float, _P]),
     'sb_cuba_bwd': (c_int, [_P, _P, _P, c_float, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _G,
                             c_float, c_float, c_int, c_int, _P]),
     'sb_alif_fwd': (c_int, [_P, _P, _I64, _P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _P,

@@ -318,9 +318,10 @@ def _vec(shape_like):
 
 
 def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current, want_spike, graded=False,
-             spike_scale=1.0, spike_delay=0, delay_head=None):
+             spike_scale=1.0, spike_delay=0, delay_head=None, axon_delay=None, axon_delay_ts=1.0):
     """Returns dict with current/voltage/spike series and final_c/final_v/final_s.
-    ``spike_delay=1`` returns the spike series one step late (``delay_head`` fills t = 0)."""
+    ``spike_delay=1`` returns the spike series one step late (``delay_head`` fills t = 0);
+    ``axon_delay`` (one value per neuron, 0..62 steps) delays each row further."""
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
@@ -332,9 +333,16 @@ def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current
     fs = _vec(x) if want_spike else None
     g = geom(x, cd.numel(), vd.numel())
     head = None if delay_head is None else row_state(delay_head, x)
+    lut, n_lut = None, 0
+    if axon_delay is not None:
+        lut = _c(axon_delay.detach().to(device=x.device, dtype=torch.float32).reshape(-1))
+        n_lut = lut.numel()
+        if n_lut != int(np.prod(x.shape[1:-1])):
+            raise ValueError(f'axon_delay needs one value per neuron ({int(np.prod(x.shape[1:-1]))}), got {n_lut}')
     N.call('sb_cuba_fwd', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(cs), N.ptr(vs),
            N.ptr(cur), N.ptr(vol), N.ptr(spk), N.ptr(fc), N.ptr(fv), N.ptr(fs), g, float(threshold), int(w_scale),
-           int(bool(graded)), float(spike_scale), int(spike_delay), N.ptr(head), N.stream_of(x))
+           int(bool(graded)), float(spike_scale), int(spike_delay), N.ptr(head), N.ptr(lut), n_lut,
+           float(axon_delay_ts), N.stream_of(x))
     return dict(current=cur, voltage=vol, spike=spk, final_c=fc, final_v=fv, final_s=fs)
 
 

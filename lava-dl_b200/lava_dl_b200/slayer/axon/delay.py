@@ -43,6 +43,14 @@ class _DelayLearnable(torch.autograd.Function):
         return _ops.shift(grad_output, -delay_val, ts), grad_delay * ctx.grad_scale, None, None
 
 
+def delay_gradient(output, grad_output, sampling_time):
+    """Finite-difference gradient of a delayed signal with respect to its per-neuron
+    delays (delay.py:205-216), for callers that produced ``output`` themselves."""
+    diff_filter = torch.tensor([-1, 1], dtype=grad_output.dtype, device=grad_output.device) / sampling_time
+    output_diff = _ops.fir(output, diff_filter, 1, corr=False)
+    return torch.sum(grad_output * output_diff, [0, -1], keepdim=True).reshape(grad_output.shape[1:-1]) * sampling_time
+
+
 def delay(input, delay_val=1, sampling_time=1):
     """Delay the signal in time (last dimension).
 
@@ -86,7 +94,9 @@ class Delay(torch.nn.Module):
     def shape(self):
         return self.delay.shape if self.init else None
 
-    def forward(self, input):
+    def delay_per_neuron(self, input):
+        """Initialise on first use, clamp, and return one delay per neuron of
+        ``input`` (the parameter itself, or expanded over the spatial dimensions)."""
         if self.init is False:
             if input.dim() <= 2:
                 raise AssertionError(
@@ -102,9 +112,19 @@ class Delay(torch.nn.Module):
                 f"Expected {self.shape[0]}, found {input.shape[1]}."
             )
         if np.prod(input.shape[1:-1]) == self.shape[0]:
-            delay_val = self.delay
-        else:
-            tile = list(input.shape[1:-1])
-            tile[0] = 1
-            delay_val = self.delay.reshape(-1, *([1] * (len(tile) - 1))).repeat(tile)
+            return self.delay
+        tile = list(input.shape[1:-1])
+        tile[0] = 1
+        return self.delay.reshape(-1, *([1] * (len(tile) - 1))).repeat(tile)
+
+    @property
+    def fusable_steps(self):
+        """Largest delay in time steps when it is bounded (``max_delay`` set), else ``None``:
+        a bounded delay of at most 62 steps can be written by the neuron kernel itself."""
+        if self.max_delay is None:
+            return None
+        return int(self.max_delay / self.sampling_time)
+
+    def forward(self, input):
+        delay_val = self.delay_per_neuron(input)
         return _DelayLearnable.apply(input, delay_val, self.grad_scale, self.sampling_time)

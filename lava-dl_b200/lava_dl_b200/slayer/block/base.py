@@ -45,28 +45,38 @@ class _Block(torch.nn.Module):
             self.synapse.weight.data *= mask
         z = self.synapse(x)
         if self.delay_shift is True and getattr(self.neuron, 'fuses_step_delay', False):
-            x = self._neuron_with_step_delay(z)
+            # a bounded axonal delay (at most 62 steps) is written by the neuron kernel as well
+            steps = None if self.delay is None else self.delay.fusable_steps
+            fuse_axon = steps is not None and 0 <= steps <= 62
+            x = self._neuron_with_step_delay(z, self.delay if fuse_axon else None)
+            if self.delay is not None and not fuse_axon:
+                x = self.delay(x)
         else:
             x = self.neuron(z)
             if self.delay_shift is True:
                 x = step_delay(self, x)
-        if self.delay is not None:
-            x = self.delay(x)
+            if self.delay is not None:
+                x = self.delay(x)
         if self.count_log is True:
             return x, torch.mean((x > 0).to(x.dtype))
         return x
 
-    def _neuron_with_step_delay(self, z):
+    def _neuron_with_step_delay(self, z, axon=None):
         """``step_delay(self, self.neuron(z))`` in one kernel: the neuron writes its
         spikes one step late; the spike carried over between calls of a
-        persistent-state neuron enters at t = 0."""
+        persistent-state neuron enters at t = 0.  With ``axon`` (an ``axon.Delay``)
+        the same kernel also applies the per-channel axonal delay."""
         if not hasattr(self, 'delay_buffer'):
             self.delay_buffer = None
         persistent_state = self.neuron.persistent_state is True
         if self.delay_buffer is not None and self.delay_buffer.shape[0] != z.shape[0]:
             self.delay_buffer = None
         head = self.delay_buffer if persistent_state else None
-        x, last_spike = self.neuron.forward_step_delayed(z, head)
+        if axon is None:
+            x, last_spike = self.neuron.forward_step_delayed(z, head)
+        else:
+            x, last_spike = self.neuron.forward_step_delayed(z, head, axon.delay_per_neuron(z), axon.sampling_time,
+                                                             axon.grad_scale)
         if persistent_state:
             self.delay_buffer = last_spike
         return x

@@ -8,6 +8,7 @@ from .dynamics import leaky_integrator
 from ..spike.spike import Spike
 from ..utils import quantize
 from ... import _ops
+from ..axon.delay import delay_gradient
 
 # heuristic multipliers so that scale_grad = tau_grad = 1 is a good start
 SCALE_RHO_MULT = 0.1
@@ -63,28 +64,42 @@ class _FusedForward(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, cdecay, vdecay, cstate, vstate, threshold, w_scale, tau_rho, scale_rho, graded,
-                spike_delay=0, delay_head=None):
+                spike_delay=0, delay_head=None, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         need_dgrad = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
         r = _ops.cuba_fwd(input, cdecay, vdecay, cstate, vstate, threshold, w_scale,
                           want_current=need_dgrad, want_spike=True, graded=graded, spike_scale=1.0,
-                          spike_delay=spike_delay, delay_head=delay_head)
+                          spike_delay=spike_delay, delay_head=delay_head,
+                          axon_delay=None if axon_delay is None else axon_delay.data, axon_delay_ts=axon_ts)
         saved = [r['voltage'], cdecay, vdecay]
         if need_dgrad:
             saved.append(r['current'])
+        if axon_delay is not None:
+            saved += [axon_delay.data, r['spike']]
         ctx.save_for_backward(*saved)
-        ctx.consts = (threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay)
+        ctx.consts = (threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay, axon_delay is not None, axon_ts,
+                      axon_grad_scale, ctx.needs_input_grad[12] if axon_delay is not None else False)
         ctx.mark_non_differentiable(r['voltage'], r['final_c'], r['final_v'], r['final_s'])
         return r['spike'], r['voltage'], r['final_c'], r['final_v'], r['final_s']
 
     @staticmethod
     def backward(ctx, grad_spike, *_):
-        threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay = ctx.consts
+        (threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay, has_axon, axon_ts, axon_grad_scale,
+         need_axon_grad) = ctx.consts
         voltage, cdecay, vdecay = ctx.saved_tensors[:3]
         current = ctx.saved_tensors[3] if need_dgrad else None
+        g_axon = None
+        if has_axon:
+            # the axonal delay is undone here as a separate shift (the forward folded it into the store);
+            # its own gradient is the finite difference of the delayed output (axon/delay.py:205-216)
+            axon_delay, delayed = ctx.saved_tensors[-2:]
+            grad_spike = _ops._c(grad_spike)
+            if need_axon_grad:
+                g_axon = delay_gradient(delayed, grad_spike, axon_ts) * axon_grad_scale
+            grad_spike = _ops.shift(grad_spike, -axon_delay, axon_ts)
         g_in, g_cdecay, g_vdecay = _ops.cuba_bwd(
             grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_dgrad,
             spike_delay=spike_delay)
-        return (g_in, g_cdecay, g_vdecay) + (None,) * 9
+        return (g_in, g_cdecay, g_vdecay) + (None,) * 9 + (g_axon, None, None)
 
 
 class Neuron(base.Neuron):
@@ -243,20 +258,22 @@ class Neuron(base.Neuron):
         inside the kernel (binary spikes, no normalisation, no dropout)."""
         return self.norm is None and self._fusable and self.graded_spike is not True and self.drop is None
 
-    def forward_step_delayed(self, input, delay_head=None):
+    def forward_step_delayed(self, input, delay_head=None, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         """``forward`` with the blocks' one-step delay folded in: returns
         ``(delayed_spike, last_spike)`` where ``delayed_spike[..., t] = spike[..., t - 1]``,
         ``delayed_spike[..., 0] = delay_head`` (0 when ``None``), and ``last_spike``
-        is the undelayed spike of the last time bin."""
-        return self._fused_forward(input, 1, delay_head)
+        is the undelayed spike of the last time bin.  ``axon_delay`` (one value per
+        neuron, at most 62 steps) delays every neuron's train further, as
+        ``axon.Delay`` does after the step delay; it receives ``axon.Delay``'s gradient."""
+        return self._fused_forward(input, 1, delay_head, axon_delay, axon_ts, axon_grad_scale)
 
-    def _fused_forward(self, input, spike_delay, delay_head):
+    def _fused_forward(self, input, spike_delay, delay_head, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         self._prepare(input)
         spike, _, final_c, final_v, final_s = _FusedForward.apply(
             input, quantize(self.current_decay), quantize(self.voltage_decay),
             self.current_state, self.voltage_state, self.threshold + self.threshold_eps, self.s_scale,
             self.tau_rho * TAU_RHO_MULT, self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True,
-            spike_delay, delay_head)
+            spike_delay, delay_head, axon_delay, axon_ts, axon_grad_scale)
         if self.persistent_state:
             with torch.no_grad():
                 self.current_state = final_c

@@ -72,7 +72,7 @@ def test_argument_errors_are_reported_without_a_gpu(lib):
     assert 'geometry' in _native.last_error()
     g = _native.Geom(4, 8, 1, 1)
     rc = native.sb_cuba_fwd(None, None, 1, None, 1, None, None, None, None, None, None, None, None,
-                            ctypes.byref(g), 1.25, 1000, 0, 1.0, 0, None, None)
+                            ctypes.byref(g), 1.25, 1000, 0, 1.0, 0, None, None, 0, 1.0, None)
     assert rc == -1 and 'power-of-two' in _native.last_error()
     rc = native.sb_fir_conv(None, None, 0, 1.0, None, 4, 8, None)
     assert rc == -1 and 'filter length' in _native.last_error()

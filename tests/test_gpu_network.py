@@ -145,3 +145,40 @@ def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     with torch.backends.cudnn.flags(allow_tf32=False):
         want = F.conv3d(xf, conv.weight, None, conv.stride, conv.padding)
     assert_close(conv(xf), want, 'convolution of floats')
+
+
+def test_block_axon_delay_fused_matches_unfused(cuda):
+    """A CUBA dense block with a bounded axonal delay writes step delay and axonal
+    delay inside the neuron kernel; an unbounded delay takes the separate shift.
+    Same spikes, same gradients (input, weights, delays), also across two calls of
+    a persistent-state block."""
+    import lava_dl_b200.slayer as slayer
+    torch.manual_seed(7)
+    params = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03, requires_grad=True, persistent_state=True)
+    fused = slayer.block.cuba.Dense(params, 24, 40, delay=True, delay_shift=True).to(cuda)
+    plain = slayer.block.cuba.Dense(params, 24, 40, delay=True, delay_shift=True).to(cuda)
+    plain.load_state_dict(fused.state_dict(), strict=False)
+    fused.delay.max_delay = 62      # bounded: fused into the neuron kernel
+    plain.delay.max_delay = None    # unbounded: separate shift kernel
+    x1 = (torch.rand(3, 24, 96, device=cuda) < 0.3).float()
+    x2 = (torch.rand(3, 24, 96, device=cuda) < 0.3).float()
+    delays = torch.rand(40, device=cuda) * 62
+    for blk in (fused, plain):
+        blk.delay.delay.data = delays.clone()
+        blk.delay.init = True
+    outs = []
+    for blk in (fused, plain):
+        xa = x1.clone().requires_grad_()
+        ya = blk(xa)
+        yb = blk(x2)                      # second call: state and delay buffer carried over
+        w = torch.linspace(0.5, 1.5, ya.numel(), device=cuda).reshape(ya.shape)
+        (ya * w).sum().backward()
+        outs.append((ya.detach(), yb.detach(), xa.grad, blk.synapse.weight.grad.clone(), blk.delay.delay.grad.clone(),
+                     blk.neuron.current_decay.grad.clone()))
+    names = ('first call', 'second call', 'grad input', 'grad weight', 'grad delay', 'grad decay')
+    for n, a, b in zip(names, outs[0], outs[1]):
+        if n.endswith('call'):
+            assert torch.equal(a, b), n
+        else:
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(b.abs().max())), n   # same kernels, same order
+    assert outs[0][0].sum() > 0

@@ -388,6 +388,37 @@ def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
     assert_close(gvd, ref['grad_voltage_decay'], 'grad voltage decay', scale=pgrad_scale(1, (g_c, want['voltage'])))
 
 
+@pytest.mark.parametrize('shape', [(2, 5, 50), (1, 257, 64), (4, 64, 128), (2, 8, 200), (3, 11, 33), (2, 3, 2)])
+@pytest.mark.parametrize('misalign', [False, True])
+def test_cuba_fused_axon_delay(shape, misalign, cuda, ops):
+    """Step delay + per-neuron axonal delay written by the neuron kernel ==
+    shift(shift(spike, 1) with head, delay) of the oracle, bit for bit."""
+    from lava_dl_b200 import _native as native
+    rng = rng_for('cuba_axon_delay', shape)
+    T = shape[-1]
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    cd, vd = np.array([1024.0], np.float32), np.array([123.0], np.float32)
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    want = O.cuba(x, 1.25, cd, vd)
+    zeros = dev(np.zeros(shape[:-1]), cuda)
+    for ts, lo, hi in ((1.0, 0, 63), (2.0, 0, 125), (1.0, 31, 34), (1.0, 62, 63)):
+        lut = (rng.integers(lo, hi, size=shape[1:-1]) + rng.uniform(0, 0.9, size=shape[1:-1])).astype(np.float32)
+        for step in (1, 0):
+            for h, h_dev in ((None, None), (head, dev(head, cuda))):
+                if step == 0 and h is not None:
+                    continue
+                late = O.shift(want['spike'], 1) if step else want['spike'].copy()
+                if h is not None:
+                    late[..., 0] = h
+                expect = O.shift(late, lut, ts)
+                r = ops.cuba_fwd(dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), zeros, zeros, 1.25 + 0.01 / W, W,
+                                 want_current=False, want_spike=True, spike_delay=step, delay_head=h_dev,
+                                 axon_delay=dev(lut, cuda), axon_delay_ts=ts)
+                assert_exact(r['spike'], expect, f'delayed spikes ts={ts} step={step} T={T}')
+                assert_exact(r['final_s'], want['spike'][..., -1], 'undelayed last spike')
+    assert native.device_status() == 0
+
+
 @pytest.mark.parametrize('shape', SHAPES)
 @pytest.mark.parametrize('per_channel', [False, True])
 def test_alif_fused(shape, per_channel, cuda, ops):
