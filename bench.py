@@ -97,7 +97,11 @@ def make_inputs(name, shape, device, seed):
         return torch.empty(shape, device=device).normal_(mean, std, generator=g)
 
     d = {}
-    if name.startswith('cuba'):
+    if name.startswith('sigma') or name.startswith('sdnn'):
+        d['x'] = randn(0.01, 0.1)
+    elif name.startswith('delta'):
+        d['x'] = randn(0.0, 0.5)
+    elif name.startswith('cuba'):
         d['x'] = randn(0.3, 1.0)
     elif name.startswith('alif'):
         d['x'] = randn(0.2, 1.0)
@@ -127,6 +131,11 @@ WORKLOADS = {
     'adrf_bwd': Workload('adrf_bwd', (64, 8192, 1000), 24),
     'li_fwd': Workload('li_fwd', (64, 8192, 2000), 8),
     'li_bwd': Workload('li_bwd', (64, 8192, 2000), 8),
+    # sigma-delta family (next to the path): running sum, delta encoder, fused relu neuron, 8 B per step each
+    'sigma_fwd': Workload('sigma_fwd', (64, 8192, 2000), 8),
+    'delta_fwd': Workload('delta_fwd', (64, 8192, 2000), 8),
+    'delta_bwd': Workload('delta_bwd', (64, 8192, 2000), 8),
+    'sdnn_fwd': Workload('sdnn_fwd', (64, 8192, 2000), 8),
     'shift': Workload('shift', (128, 16384, 1000), 8, 'elements/s'),
     'fir_conv': Workload('fir_conv', (128, 16384, 1000), 8, 'elements/s'),
     'delay_fir_fwd': Workload('delay_fir_fwd', (128, 16384, 1000), 8, 'elements/s'),
@@ -201,6 +210,29 @@ def build_step(name, shape, device, seed):
         def step():
             N.call('sb_probe_stream', src, N.ptr(src), N.ptr(dst), n, r, w, N.stream_of(src))
         return step, 1, (src, dst)
+    if name == 'sigma_fwd':
+        def step():
+            return _ops.sigma_fwd(d['x'])
+        return step, 1, d
+    if name == 'delta_fwd':
+        thr = one(0.3)
+
+        def step():
+            return _ops.delta_fwd(d['x'], thr, None, None, 4096, want_delta=False)
+        return step, 1, d
+    if name == 'delta_bwd':
+        thr = one(0.3)
+        del d['x']
+
+        def step():
+            return _ops.delta_bwd(d['g'], None, thr, 1.0, 1.0, False)
+        return step, 1, d
+    if name == 'sdnn_fwd':
+        thr = one(0.1)
+
+        def step():
+            return _ops.sdnn_relu_fwd(d['x'], thr, None, None, None, None, 4096)
+        return step, 1, d
     if name == 'cuba_fwd_delayed':
         cd, vd = one(1024), one(123)
         gen = torch.Generator(device=device).manual_seed(seed + 1)

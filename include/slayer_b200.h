@@ -237,6 +237,45 @@ int sb_shift_fir_bwd(const float* grad_out, const float* lut, int64_t n_lut, flo
                      const float* filter, int64_t K, float sampling_time, float* grad_x, int64_t rows,
                      int64_t T, void* stream);
 
+/* ---- sigma-delta family (next to the path: the same serial-in-time shape) -------
+ * Sigma decoder, replaces dendrite/sigma.py:38-72 (torch.cumsum + persistent
+ * state): out[r,t] = float(sum_{s<=t} x[r,s], accumulated in double as
+ * torch.cumsum does on a CPU float tensor) + state[r] (nullable = 0).
+ * final_state (nullable float[rows]) receives out[r, T-1].
+ * sb_sigma_bwd is its adjoint: the same sum over reversed time. */
+int sb_sigma_fwd(const float* x, const float* state, float* out, float* final_state, int64_t rows, int64_t T,
+                 void* stream);
+int sb_sigma_bwd(const float* grad_out, float* grad_x, int64_t rows, int64_t T, void* stream);
+/* Delta encoder, replaces axon/delta.py:13-76 (cum_error = False, the Python
+ * loop over time) and the floor quantisation of Delta.forward (delta.py:316):
+ *   d[t] = (x[t] - pre) + residual;  y[t] = d[t] if |d[t]| >= threshold else 0;
+ *   residual = d[t] - y[t];  pre = x[t];  out[t] = floor(y[t] * scale) / scale.
+ * threshold: 1 or C values.  pre_state / residual_state (nullable float[rows]).
+ * delta_input (nullable) receives d (saved for the threshold gradient);
+ * final_residual (nullable float[rows]).  scale = 0 leaves out unquantised. */
+int sb_delta_fwd(const float* x, const float* threshold, int64_t n_threshold, const float* pre_state,
+                 const float* residual_state, float* out, float* delta_input, float* final_residual,
+                 const sb_geom* g, double scale, void* stream);
+/* Replaces axon/delta.py:77-122: grad_x[t] = g[t] - g[t+1]; grad_threshold
+ * (nullable; needs delta_input and scratch of sb_param_grad_scratch_bytes) =
+ * sum over batch, space and time of
+ *   (|d| - thr > 0 ? -d * scale_grad * exp(-(|d| - thr) / tau_grad) / thr : -sign(d)) * g.
+ * (The reference's per-channel reduction fails on its own shapes; here it sums
+ * per channel as its comment intends.) */
+int sb_delta_bwd(const float* grad_out, const float* delta_input, const float* threshold, int64_t n_threshold,
+                 float* grad_x, float* grad_threshold, void* scratch, const sb_geom* g, float tau_grad,
+                 float scale_grad, void* stream);
+/* Sigma-delta ReLU neuron, forward only (inference): neuron/sigma_delta.py:171-219
+ * with activation = relu and no normalisation, in one pass of 8 bytes per step:
+ * sigma -> + bias (nullable; 1 value or one per neuron, rows_per_batch values, as
+ * set_bias stores it) -> relu -> delta -> floor.
+ * final_sigma / final_pre / final_residual (nullable float[rows]) are the
+ * persistent states of the sigma and delta units after the call. */
+int sb_sdnn_relu_fwd(const float* x, const float* sigma_state, const float* bias, int64_t n_bias,
+                     const float* threshold, int64_t n_threshold, const float* pre_state,
+                     const float* residual_state, float* out, float* final_sigma, float* final_pre,
+                     float* final_residual, const sb_geom* g, double scale, void* stream);
+
 /* ---- sum-pooling synapse (next to the path: what feeds the neurons in conv networks) ----
  * Replaces the Conv3d call of synapse/layer.py:438-508 for the default pooling
  * geometry (stride = kernel, no padding, no dilation).  x is [NC, H, W, T] with

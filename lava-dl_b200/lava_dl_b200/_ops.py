@@ -311,6 +311,81 @@ def shift_fir(x, shift_val, shift_ts, filt, sampling_time, backward):
 
 
 # --------------------------------------------------------------------------
+# sigma-delta family
+# --------------------------------------------------------------------------
+def _opt_state(state, x):
+    return None if state is None else row_state(state, x)
+
+
+def sigma_fwd(x, state=None, want_final=False):
+    N.require_cuda(x)
+    x = _c(x)
+    rows, T = _rows_T(x)
+    st = _opt_state(state, x)
+    out = torch.empty_like(x)
+    fin = _vec(x) if want_final else None
+    N.call('sb_sigma_fwd', x, N.ptr(x), N.ptr(st), N.ptr(out), N.ptr(fin), rows, T, N.stream_of(x))
+    return (out, fin) if want_final else out
+
+
+def sigma_bwd(grad_out):
+    N.require_cuda(grad_out)
+    grad_out = _c(grad_out)
+    rows, T = _rows_T(grad_out)
+    gx = torch.empty_like(grad_out)
+    N.call('sb_sigma_bwd', grad_out, N.ptr(grad_out), N.ptr(gx), rows, T, N.stream_of(grad_out))
+    return gx
+
+
+def delta_fwd(x, threshold, pre_state, residual_state, scale, want_delta):
+    """Returns (out, delta_input or None, final_residual)."""
+    N.require_cuda(x)
+    x = _c(x)
+    thr = _param(threshold, x)
+    pre, res = _opt_state(pre_state, x), _opt_state(residual_state, x)
+    out = torch.empty_like(x)
+    dlt = torch.empty_like(x) if want_delta else None
+    fres = _vec(x)
+    g = geom(x, thr.numel())
+    N.call('sb_delta_fwd', x, N.ptr(x), N.ptr(thr), thr.numel(), N.ptr(pre), N.ptr(res), N.ptr(out), N.ptr(dlt),
+           N.ptr(fres), g, float(scale), N.stream_of(x))
+    return out, dlt, fres
+
+
+def delta_bwd(grad_out, delta_input, threshold, tau_grad, scale_grad, need_threshold_grad):
+    N.require_cuda(grad_out)
+    grad_out = _c(grad_out)
+    thr = _param(threshold, grad_out)
+    gx = torch.empty_like(grad_out)
+    g = geom(grad_out, thr.numel())
+    if need_threshold_grad:
+        gthr = torch.empty(thr.numel(), device=grad_out.device, dtype=torch.float32)
+        scr = N.scratch(g.rows, thr.numel(), grad_out.device)
+        N.call('sb_delta_bwd', grad_out, N.ptr(grad_out), N.ptr(_c(delta_input)), N.ptr(thr), thr.numel(), N.ptr(gx),
+               N.ptr(gthr), N.ptr(scr), g, float(tau_grad), float(scale_grad), N.stream_of(grad_out))
+        return gx, gthr.reshape(threshold.shape)
+    N.call('sb_delta_bwd', grad_out, N.ptr(grad_out), None, N.ptr(thr), thr.numel(), N.ptr(gx), None, None, g,
+           float(tau_grad), float(scale_grad), N.stream_of(grad_out))
+    return gx, None
+
+
+def sdnn_relu_fwd(x, threshold, bias, sigma_state, pre_state, residual_state, scale):
+    """Sigma -> bias -> relu -> delta -> floor in one pass.  Returns dict(out, final_sigma, final_pre, final_residual)."""
+    N.require_cuda(x)
+    x = _c(x)
+    thr = _param(threshold, x)
+    b = None if bias is None else _param(bias, x)
+    ss, pre, res = _opt_state(sigma_state, x), _opt_state(pre_state, x), _opt_state(residual_state, x)
+    out = torch.empty_like(x)
+    fs, fp, fr = _vec(x), _vec(x), _vec(x)
+    g = geom(x, thr.numel())
+    N.call('sb_sdnn_relu_fwd', x, N.ptr(x), N.ptr(ss), N.ptr(b), 0 if b is None else b.numel(), N.ptr(thr),
+           thr.numel(), N.ptr(pre), N.ptr(res), N.ptr(out), N.ptr(fs), N.ptr(fp), N.ptr(fr), g, float(scale),
+           N.stream_of(x))
+    return dict(out=out, final_sigma=fs, final_pre=fp, final_residual=fr)
+
+
+# --------------------------------------------------------------------------
 # fused neurons
 # --------------------------------------------------------------------------
 def _vec(shape_like):

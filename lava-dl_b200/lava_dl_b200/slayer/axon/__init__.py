@@ -1,5 +1,6 @@
-"""Axonal delay (mirror of ``lava.lib.dl.slayer.axon``)."""
+"""Axon models (mirror of ``lava.lib.dl.slayer.axon``)."""
 
 from .delay import delay, Delay
+from .delta import Delta
 
-__all__ = ['delay', 'Delay']
+__all__ = ['delay', 'Delay', 'Delta']

@@ -251,6 +251,58 @@ def corr(x, filt, sampling_time=1):
     return fir(x, filt, sampling_time, corr=True)
 
 
+def sigma(x, state=None, reverse=False):
+    """dendrite/sigma.py:38-72 (reverse=True: the adjoint, a running sum over reversed time)"""
+    x = _f(x)
+    st = None if state is None else _state(state, x)
+    out = np.empty_like(x)
+    rows, T, _, _ = _geom(x)
+    lib().orc_sigma(_p(x), _p(st), _p(out), I64(rows), I64(T), c_int(int(reverse)))
+    return out
+
+
+def delta_fwd(x, threshold, pre_state=None, residual_state=None, scale=4096):
+    """axon/delta.py:13-76,258-316 with cum_error=False; returns dict(out, delta_input, residual)"""
+    x = _f(x)
+    thr = _vec(threshold)
+    pre = None if pre_state is None else _state(pre_state, x)
+    res = None if residual_state is None else _state(residual_state, x)
+    out, dlt = np.empty_like(x), np.empty_like(x)
+    rows, T, rpb, blk = _geom(x)
+    fres = np.empty(rows, dtype=np.float32)
+    lib().orc_delta_fwd(_p(x), _p(thr), I64(thr.size), _p(pre), _p(res), _p(out), _p(dlt), _p(fres), I64(rows),
+                        I64(T), I64(rpb), I64(blk), c_double(scale))
+    return dict(out=out, delta_input=dlt, residual=fres.reshape(x.shape[:-1]))
+
+
+def delta_bwd(grad_out, delta_input, threshold, tau_grad=1.0, scale_grad=1.0):
+    """axon/delta.py:77-122; returns (grad_x, grad_threshold[float64])"""
+    go, dlt = _f(grad_out), _f(delta_input)
+    thr = _vec(threshold)
+    gx = np.empty_like(go)
+    gthr = np.zeros(thr.size, dtype=np.float64)
+    rows, T, rpb, blk = _geom(go)
+    lib().orc_delta_bwd(_p(go), _p(dlt), _p(thr), I64(thr.size), _p(gx), _p(gthr), I64(rows), I64(T), I64(rpb),
+                        I64(blk), c_float(tau_grad), c_float(scale_grad))
+    return gx, gthr
+
+
+def sdnn_relu(x, threshold, bias=None, sigma_state=None, pre_state=None, residual_state=None, scale=4096):
+    """neuron/sigma_delta.py:171-219 with activation = relu, norm = None:
+    sigma -> + bias (per neuron) -> relu -> delta.  Returns dict(out, sigma, act, delta_input, residual)."""
+    x = _f(x)
+    s = sigma(x, sigma_state)
+    z = s
+    if bias is not None:
+        # one bias per neuron (sigma_delta.py:190-200 adds bias[None, ..., None]) or a single value
+        b = np.asarray(bias, dtype=np.float32).reshape(-1)
+        z = (s + (b.reshape((1,) + x.shape[1:-1] + (1,)) if b.size > 1 else b[0])).astype(np.float32)
+    act = np.maximum(z, np.float32(0)).astype(np.float32)
+    r = delta_fwd(act, threshold, pre_state, residual_state, scale)
+    r.update(sigma=s, act=act, pre=act[..., -1])
+    return r
+
+
 def quantize(p):
     """utils/quantize.py:18-32 with step 1: round half to even, as torch.round"""
     return np.round(np.asarray(p, dtype=np.float32))

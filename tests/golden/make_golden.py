@@ -411,6 +411,53 @@ def main():
     print('network spike counts per layer:', [int(acts[f'act{i}'].sum()) for i in range(len(net))])
     save('network_cuba_conv', **net_arrays)
 
+    # ------------------------------------------------------------------
+    # sigma-delta family (dendrite/sigma.py, axon/delta.py, neuron/sigma_delta.py).
+    # cum_error=True and the gradient of a per-channel threshold raise inside the
+    # reference itself with this torch, so they have no vectors.
+    x = randn(B, C, T, std=0.7)
+    sig = slayer.dendrite.Sigma(persistent_state=True)
+    xs = x.clone().requires_grad_()
+    s1 = sig(xs)
+    g = randn(B, C, T)
+    (s1 * g).sum().backward()
+    s2 = sig(x)
+    save('sigma_persistent', x=x, out1=s1, grad_out=g, grad_x=xs.grad, out2=s2)
+
+    dl = slayer.axon.Delta(threshold=0.5, scale=W, tau_grad=0.7, scale_grad=1.3, shared_param=True,
+                           persistent_state=True, requires_grad=True)
+    xs = x.clone().requires_grad_()
+    y1 = dl(xs)
+    (y1 * g).sum().backward()
+    y2 = dl(x)
+    save('delta_shared', x=x, threshold=dl.threshold.data.clone(), out1=y1, grad_out=g, grad_x=xs.grad,
+         grad_threshold=dl.threshold.grad, out2=y2, residual=dl.residual_state, tau_grad=0.7, scale_grad=1.3)
+
+    dl = slayer.axon.Delta(threshold=0.3, scale=W, shared_param=False)
+    dl.threshold.data = torch.tensor([0.3])
+    x4 = randn(B2, C2, H2, T2, std=0.5)
+    y = dl(x4)
+    dl.threshold.data = torch.linspace(0.1, 0.6, C2).reshape(C2, 1)
+    y = dl(x4)
+    save('delta_chan_rank4', x=x4, threshold=dl.threshold.data.reshape(-1).clone(), out=y)
+
+    relu = torch.nn.functional.relu
+    nrn = slayer.neuron.sigma_delta.Neuron(threshold=0.1, activation=relu, tau_grad=0.5, scale_grad=1.0,
+                                           shared_param=True, persistent_state=True, requires_grad=True)
+    xin = (0.15 * randn(B, C, T)).requires_grad_()
+    y1 = nrn(xin)
+    (y1 * g).sum().backward()
+    y2 = nrn(xin.detach())
+    save('neuron_sdnn_shared', x=xin, threshold=nrn.delta.threshold.data.clone(), out1=y1, grad_out=g,
+         grad_x=xin.grad, grad_threshold=nrn.delta.threshold.grad, out2=y2, tau_grad=0.5 , scale_grad=1.0)
+
+    nrn = slayer.neuron.sigma_delta.Neuron(threshold=0.05, activation=relu, shared_param=False)
+    nrn.set_bias(torch.linspace(-0.2, 0.3, C2 * H2).reshape(C2, H2))   # one bias per neuron
+    x4 = 0.1 * randn(B2, C2, H2, T2)
+    y = nrn(x4)
+    save('neuron_sdnn_bias_rank4', x=x4, threshold=nrn.delta.threshold.data.reshape(-1).clone(),
+         bias=nrn.bias.data.reshape(-1).clone(), out=y)
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

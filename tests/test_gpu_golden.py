@@ -358,3 +358,64 @@ def test_adrf_iz(cuda, slayer):
     n = slayer.neuron.adrf_iz.Neuron(0.5, 0.25, 12, 0.1, 0.1, 0.1).to(cuda)
     out = n((T(g['re_in'], cuda), T(g['im_in'], cuda)))  # forward() works here (TypeError in the reference)
     assert_exact(out, g['spike'], 'forward')
+
+
+# --------------------------------------------------------------------------
+# sigma-delta family through the module API
+# --------------------------------------------------------------------------
+def test_sigma_module(cuda, slayer):
+    g = load_golden('sigma_persistent')
+    sig = slayer.dendrite.Sigma(persistent_state=True)
+    x = T(g['x'], cuda, True)
+    s1 = sig(x)
+    (s1 * T(g['grad_out'], cuda)).sum().backward()
+    assert_exact(s1, g['out1'], 'running sum')
+    assert_exact(x.grad, g['grad_x'], 'adjoint')
+    assert_exact(sig(T(g['x'], cuda)), g['out2'], 'second call continues the sum')
+
+
+def test_delta_module(cuda, slayer):
+    g = load_golden('delta_shared')
+    dl = slayer.axon.Delta(threshold=0.5, scale=S, tau_grad=float(g['tau_grad']), scale_grad=float(g['scale_grad']),
+                           shared_param=True, persistent_state=True, requires_grad=True).to(cuda)
+    x = T(g['x'], cuda, True)
+    y1 = dl(x)
+    (y1 * T(g['grad_out'], cuda)).sum().backward()
+    assert_exact(y1, g['out1'], 'delta output')
+    assert_exact(x.grad, g['grad_x'], 'grad_x')
+    assert_close(dl.threshold.grad, g['grad_threshold'], 'grad_threshold')
+    assert_exact(dl(T(g['x'], cuda)), g['out2'], 'second call with kept states')
+    assert_exact(dl.residual_state, g['residual'], 'residual state')
+    with pytest.raises(NotImplementedError):
+        slayer.axon.Delta(threshold=0.5, cum_error=True)
+    g = load_golden('delta_chan_rank4')
+    dl = slayer.axon.Delta(threshold=0.3, scale=S, shared_param=False).to(cuda)
+    dl(T(g['x'], cuda))   # first call fixes the shape and expands the threshold
+    dl.threshold.data = T(g['threshold'], cuda).reshape(dl.threshold.shape)
+    assert_exact(dl(T(g['x'], cuda)), g['out'], 'one threshold per channel')
+
+
+def test_sigma_delta_neuron(cuda, slayer):
+    relu = torch.nn.functional.relu
+    g = load_golden('neuron_sdnn_shared')
+    nrn = slayer.neuron.sigma_delta.Neuron(threshold=0.1, activation=relu, tau_grad=float(g['tau_grad']),
+                                           scale_grad=float(g['scale_grad']), shared_param=True,
+                                           persistent_state=True, requires_grad=True).to(cuda)
+    x = T(g['x'], cuda, True)
+    y1 = nrn(x)                       # gradients wanted: sigma, relu and delta as separate passes
+    (y1 * T(g['grad_out'], cuda)).sum().backward()
+    assert_exact(y1, g['out1'], 'sigma-delta output')
+    assert_close(x.grad, g['grad_x'], 'grad_x')
+    assert_close(nrn.delta.threshold.grad, g['grad_threshold'], 'grad_threshold')
+    with torch.no_grad():
+        y2 = nrn(T(g['x'], cuda))     # no gradients: the one-pass kernel, continuing the kept states
+    assert_exact(y2, g['out2'], 'second call (one-pass kernel) with kept states')
+    g = load_golden('neuron_sdnn_bias_rank4')
+    nrn = slayer.neuron.sigma_delta.Neuron(threshold=0.05, activation=relu, shared_param=False).to(cuda)
+    C, H = g['x'].shape[1:3]
+    nrn.set_bias(T(g['bias'], cuda).reshape(C, H))
+    x = T(g['x'], cuda)
+    assert_exact(nrn(x), g['out'], 'per-neuron bias, one-pass kernel')
+    nrn2 = slayer.neuron.sigma_delta.Neuron(threshold=0.05, activation=torch.relu, shared_param=False).to(cuda)
+    nrn2.set_bias(T(g['bias'], cuda).reshape(C, H))
+    assert_exact(nrn2(x), g['out'], 'per-neuron bias, separate passes')

@@ -504,6 +504,80 @@ def test_rf_fused(shape, per_channel, adaptive, cuda, ops):
         assert_close(gcs, want['grad_cos_decay'], 'grad_cos', scale=S_p)
 
 
+# --------------------------------------------------------------------------
+# sigma-delta family
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('misalign', [False, True])
+def test_sigma(shape, misalign, cuda, ops):
+    rng = rng_for('sigma', shape)
+    x = rng.normal(0.1, 1.0, size=shape).astype(np.float32)
+    st = rng.normal(size=shape[:-1]).astype(np.float32)
+    out, fin = ops.sigma_fwd(dev(x, cuda, misalign), None, want_final=True)
+    want = O.sigma(x)
+    assert_exact(out, want, 'running sum')
+    assert_exact(fin, want[..., -1], 'final state')
+    assert_exact(ops.sigma_fwd(dev(x, cuda, misalign), dev(st, cuda)), O.sigma(x, st), 'running sum on a kept state')
+    assert_exact(ops.sigma_bwd(dev(x, cuda, misalign)), O.sigma(x, reverse=True), 'adjoint')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('per_channel', [False, True])
+def test_delta(shape, per_channel, cuda, ops):
+    rng = rng_for('delta', shape, per_channel)
+    n = shape[1] if per_channel else 1
+    x = np.cumsum(rng.normal(0, 0.3, size=shape), axis=-1).astype(np.float32)
+    thr = rng.uniform(0.1, 0.6, size=n).astype(np.float32)
+    pre = rng.normal(size=shape[:-1]).astype(np.float32)
+    res = rng.normal(0, 0.1, size=shape[:-1]).astype(np.float32)
+    go = rng.normal(size=shape).astype(np.float32)
+    for states in ((None, None), (pre, res)):
+        want = O.delta_fwd(x, thr, states[0], states[1], 4096)
+        sd = [None if s is None else dev(s, cuda) for s in states]
+        out, dlt, fres = ops.delta_fwd(dev(x, cuda), dev(thr, cuda), sd[0], sd[1], 4096, want_delta=True)
+        assert_exact(out, want['out'], 'delta output')
+        assert_exact(dlt, want['delta_input'], 'difference')
+        assert_exact(fres, want['residual'], 'final residual')
+        out2, none, _ = ops.delta_fwd(dev(x, cuda), dev(thr, cuda), sd[0], sd[1], 4096, want_delta=False)
+        assert none is None
+        assert_exact(out2, want['out'], 'delta output (difference not saved)')
+    assert_exact(ops.delta_fwd(dev(x, cuda), dev(thr, cuda), None, None, 0, False)[0],
+                 O.delta_fwd(x, thr, scale=0)['out'], 'unquantised')
+    gx_want, gthr_want = O.delta_bwd(go, want['delta_input'], thr, 0.7, 1.3)
+    gx, gthr = ops.delta_bwd(dev(go, cuda), dlt, dev(thr, cuda), 0.7, 1.3, True)
+    assert_exact(gx, gx_want, 'grad_x')
+    # scale of the threshold gradient: the sum of the magnitudes of its terms
+    d = want['delta_input'].astype(np.float64)
+    th = thr.astype(np.float64).reshape((1, -1) + (1,) * (len(shape) - 2)) if n > 1 else float(thr[0])
+    sub = np.abs(d) - th
+    mag = np.where(sub > 0, np.abs(d) * 1.3 * np.exp(-np.abs(sub) / 0.7) / th, 1.0) * np.abs(go)
+    scale = mag.sum(axis=tuple(i for i in range(mag.ndim) if i != 1)) if n > 1 else np.array([mag.sum()])
+    assert_close(gthr, gthr_want, 'grad threshold', scale=scale + 1e-30)
+    assert_exact(ops.delta_bwd(dev(go, cuda), None, dev(thr, cuda), 1.0, 1.0, False)[0], gx_want, 'grad_x only')
+
+
+@pytest.mark.parametrize('shape', SHAPES + [(2, 3, 4, 64), (1, 2, 3, 5, 40)])
+@pytest.mark.parametrize('bias_kind', ['none', 'scalar', 'neuron'])
+def test_sigma_delta_relu_fused(shape, bias_kind, cuda, ops):
+    rng = rng_for('sdnn', shape, bias_kind)
+    x = rng.normal(0.02, 0.15, size=shape).astype(np.float32)
+    thr = rng.uniform(0.05, 0.2, size=shape[1]).astype(np.float32)
+    bias = {'none': None, 'scalar': np.array([0.05], np.float32),
+            'neuron': rng.normal(0, 0.2, size=shape[1:-1]).astype(np.float32)}[bias_kind]
+    ss = rng.normal(0, 0.3, size=shape[:-1]).astype(np.float32)
+    pre = np.abs(rng.normal(0, 0.3, size=shape[:-1])).astype(np.float32)
+    res = rng.normal(0, 0.05, size=shape[:-1]).astype(np.float32)
+    for states in ((None, None, None), (ss, pre, res)):
+        want = O.sdnn_relu(x, thr, bias, states[0], states[1], states[2], 4096)
+        sd = [None if s is None else dev(s, cuda) for s in states]
+        r = ops.sdnn_relu_fwd(dev(x, cuda), dev(thr, cuda), None if bias is None else dev(bias, cuda), sd[0], sd[1],
+                              sd[2], 4096)
+        assert_exact(r['out'], want['out'], 'sigma-delta relu output')
+        assert_exact(r['final_sigma'], want['sigma'][..., -1], 'sigma state')
+        assert_exact(r['final_pre'], want['pre'], 'delta pre state')
+        assert_exact(r['final_residual'], want['residual'], 'delta residual state')
+
+
 def test_empty_inputs(cuda, ops):
     for shape in ((0, 4, 16), (2, 4, 0)):
         x = torch.empty(shape, device=cuda)

@@ -212,3 +212,49 @@ def test_adrf_iz_neuron():
     assert_close(r['grad_im'], g['grad_in1'], 'grad_im')
     assert_close(r['grad_sin_decay'], g['grad_sin_decay'], 'grad_sin')
     assert_close(r['grad_cos_decay'], g['grad_cos_decay'], 'grad_cos')
+
+
+# --------------------------------------------------------------------------
+# sigma-delta family
+# --------------------------------------------------------------------------
+def test_sigma():
+    g = load_golden('sigma_persistent')
+    s1 = O.sigma(g['x'])
+    assert_exact(s1, g['out1'], 'cumsum')
+    assert_exact(O.sigma(g['x'], state=s1[..., -1]), g['out2'], 'cumsum on top of the kept state')
+    assert_exact(O.sigma(g['grad_out'], reverse=True), g['grad_x'], 'adjoint')
+
+
+def test_delta_shared():
+    g = load_golden('delta_shared')
+    r = O.delta_fwd(g['x'], g['threshold'])
+    assert_exact(r['out'], g['out1'], 'delta output')
+    gx, gthr = O.delta_bwd(g['grad_out'], r['delta_input'], g['threshold'], float(g['tau_grad']),
+                           float(g['scale_grad']))
+    assert_exact(gx, g['grad_x'], 'grad_x')
+    assert_close(gthr, g['grad_threshold'], 'grad_threshold')
+    r2 = O.delta_fwd(g['x'], g['threshold'], pre_state=g['x'][..., -1], residual_state=r['residual'])
+    assert_exact(r2['out'], g['out2'], 'second call with kept states')
+    assert_exact(r2['residual'], g['residual'], 'residual state')
+
+
+def test_delta_per_channel():
+    g = load_golden('delta_chan_rank4')
+    assert_exact(O.delta_fwd(g['x'], g['threshold'])['out'], g['out'], 'delta output, one threshold per channel')
+
+
+def test_sigma_delta_neuron():
+    g = load_golden('neuron_sdnn_shared')
+    r = O.sdnn_relu(g['x'], g['threshold'])
+    assert_exact(r['out'], g['out1'], 'sigma-delta relu output')
+    # backward: delta -> relu mask -> adjoint of the running sum
+    g_act, gthr = O.delta_bwd(g['grad_out'], r['delta_input'], g['threshold'], float(g['tau_grad']),
+                              float(g['scale_grad']))
+    gx = O.sigma((g_act * (r['act'] > 0)).astype(np.float32), reverse=True)
+    assert_close(gx, g['grad_x'], 'grad_x')
+    assert_close(gthr, g['grad_threshold'], 'grad_threshold')
+    r2 = O.sdnn_relu(g['x'], g['threshold'], sigma_state=r['sigma'][..., -1], pre_state=r['pre'],
+                     residual_state=r['residual'])
+    assert_exact(r2['out'], g['out2'], 'second call with kept states')
+    g = load_golden('neuron_sdnn_bias_rank4')
+    assert_exact(O.sdnn_relu(g['x'], g['threshold'], bias=g['bias'])['out'], g['out'], 'per-neuron bias')
