@@ -294,6 +294,20 @@ int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t
 int sb_conv_fwd(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co, int64_t H,
                 int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, void* stream);
 
+/* Weight gradient of the same convolution (what convolution_backward returns for
+ * the weight of the Conv3d at synapse/layer.py:297-323), fp32:
+ *   grad_weight[co,ci,i,j] = sum_{n,ho,wo,t} grad_y[n,co,ho,wo,t] * x[n,ci,ho+i-ph,wo+j-pw,t].
+ * scratch: sb_conv_wgrad_scratch_bytes(...) bytes (one partial per output row,
+ * summed in a fixed order).  Needs T % 4 == 0, 16-byte aligned tensors and
+ * ceil(Co / 8) * ceil(Ci * kh * kw / 8) <= 384.  The input gradient is
+ * sb_conv_fwd of grad_y with the flipped, transposed weight and padding
+ * (kh - 1 - ph, kw - 1 - pw). */
+int64_t sb_conv_wgrad_scratch_bytes(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t kh, int64_t kw,
+                                    int64_t ph);
+int sb_conv_wgrad(const float* x, const float* grad_y, float* grad_weight, void* scratch, int64_t N, int64_t Ci,
+                  int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T,
+                  void* stream);
+
 /* ---- measurement aid ------------------------------------------------------------
  * No counterpart in the reference and not on the hot path: a plain streaming
  * kernel that reads `reads` streams of n floats (laid out back to back in `in`)

@@ -575,3 +575,34 @@ def conv_fwd(x, weight, padding):
     y = torch.empty((n, co, h + 2 * ph - kh + 1, w + 2 * pw - kw + 1, t), device=x.device, dtype=torch.float32)
     N.call('sb_conv_fwd', x, N.ptr(x), N.ptr(wgt), N.ptr(y), n, ci, co, h, w, kh, kw, ph, pw, t, N.stream_of(x))
     return y
+
+
+def conv_wgrad_supported(x, weight):
+    """The weight-gradient kernel needs T % 4 == 0 and at most 384 accumulator tiles of 8 x 8."""
+    co, ci, kh, kw = weight.shape[:4]
+    tiles = ((co + 7) // 8) * ((ci * kh * kw + 7) // 8)
+    return x.shape[-1] % 4 == 0 and tiles <= 384 and x.data_ptr() % 16 == 0
+
+
+def conv_wgrad(x, grad_y, weight_shape, padding):
+    """Gradient of ``conv_fwd`` with respect to the weight; returns a tensor of ``weight_shape``."""
+    N.require_cuda(x, grad_y)
+    x, grad_y = _c(x), _c(grad_y)
+    n, ci, h, w, t = x.shape
+    co, _, kh, kw = weight_shape[:4]
+    ph, pw = int(padding[0]), int(padding[1])
+    gw = torch.empty(tuple(weight_shape), device=x.device, dtype=torch.float32)
+    nbytes = N.load().sb_conv_wgrad_scratch_bytes(n, ci, co, h, kh, kw, ph)
+    scratch = torch.empty(max(nbytes // 4, 1), device=x.device, dtype=torch.float32)
+    N.call('sb_conv_wgrad', x, N.ptr(x), N.ptr(grad_y), N.ptr(gw), N.ptr(scratch), n, ci, co, h, w, kh, kw, ph, pw,
+           t, N.stream_of(x))
+    return gw
+
+
+def conv_dgrad(grad_y, weight, padding):
+    """Gradient of ``conv_fwd`` with respect to its input: the same kernel on ``grad_y``
+    with the weight flipped in space and its channel axes swapped."""
+    kh, kw = weight.shape[2], weight.shape[3]
+    wt = weight.detach()[:, :, :, :, 0] if weight.dim() == 5 else weight.detach()
+    wt = wt.flip(2, 3).transpose(0, 1).contiguous()
+    return conv_fwd(grad_y, wt, (kh - 1 - int(padding[0]), kw - 1 - int(padding[1])))

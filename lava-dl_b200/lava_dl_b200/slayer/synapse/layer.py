@@ -102,8 +102,9 @@ class Dense(torch.nn.Conv3d, GenericLayer):
 
 
 class _SpikeConv(torch.autograd.Function):
-    """Forward through the direct convolution kernel (time stays the vector axis,
-    no layout change); backward through ATen's convolution backward."""
+    """Forward, input gradient and weight gradient through the direct convolution
+    kernels (time stays the vector axis, no layout change, fp32 throughout).  Shapes
+    the weight-gradient kernel does not take go to ATen's convolution backward."""
 
     @staticmethod
     def forward(ctx, input, weight, padding):
@@ -114,9 +115,21 @@ class _SpikeConv(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         input, weight = ctx.saved_tensors
-        grad_input, grad_weight, _ = torch.ops.aten.convolution_backward(
-            grad_output.contiguous(), input, weight, None, [1, 1, 1], list(ctx.padding), [1, 1, 1], False, [0, 0, 0],
-            1, [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        grad_output = grad_output.contiguous()
+        kh, kw = weight.shape[2], weight.shape[3]
+        own_dgrad = kh - 1 - ctx.padding[0] >= 0 and kw - 1 - ctx.padding[1] >= 0
+        own_wgrad = _ops.conv_wgrad_supported(input, weight) and grad_output.data_ptr() % 16 == 0
+        grad_input = grad_weight = None
+        if ctx.needs_input_grad[0] and own_dgrad:
+            grad_input = _ops.conv_dgrad(grad_output, weight, ctx.padding)
+        if ctx.needs_input_grad[1] and own_wgrad:
+            grad_weight = _ops.conv_wgrad(input, grad_output, weight.shape, ctx.padding)
+        need = [ctx.needs_input_grad[0] and grad_input is None, ctx.needs_input_grad[1] and grad_weight is None, False]
+        if need[0] or need[1]:
+            gi, gw, _ = torch.ops.aten.convolution_backward(
+                grad_output, input, weight, None, [1, 1, 1], list(ctx.padding), [1, 1, 1], False, [0, 0, 0], 1, need)
+            grad_input = gi if need[0] else grad_input
+            grad_weight = gw if need[1] else grad_weight
         return grad_input, grad_weight, None
 
 

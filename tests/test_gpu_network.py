@@ -122,7 +122,7 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
-    backward (ATen) against autograd of conv3d."""
+    backward (own kernels where the shape allows, else ATen) against autograd of conv3d and float64."""
     import torch.nn.functional as F
     import lava_dl_b200.slayer as slayer
     from _util import assert_close
@@ -145,6 +145,19 @@ def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     with torch.backends.cudnn.flags(allow_tf32=False):
         want = F.conv3d(xf, conv.weight, None, conv.stride, conv.padding)
     assert_close(conv(xf), want, 'convolution of floats')
+    # gradients on float data against float64 on the CPU: 1e-5 of the sum of the term magnitudes
+    xd = xf.double().cpu().requires_grad_(True)
+    wd = conv.weight.detach().double().cpu().requires_grad_(True)
+    gd = torch.randn(want.shape, generator=gen, dtype=torch.float64)
+    F.conv3d(xd, wd, None, conv.stride, conv.padding).backward(gd)
+    mx = xf.double().cpu().abs().requires_grad_(True)
+    mw = conv.weight.detach().double().cpu().abs().requires_grad_(True)
+    F.conv3d(mx, mw, None, conv.stride, conv.padding).backward(gd.abs())
+    xg = xf.clone().requires_grad_(True)
+    with torch.backends.cudnn.flags(allow_tf32=False):   # shapes that fall back to ATen: no TF32 there either
+        gx, gw = torch.autograd.grad(conv(xg), [xg, conv.weight], gd.float().to(cuda))
+    assert_close(gx, xd.grad.numpy(), 'input gradient of floats', scale=mx.grad.numpy() + 1e-30)
+    assert_close(gw, wd.grad.numpy(), 'weight gradient of floats', scale=mw.grad.numpy() + 1e-30)
 
 
 def test_block_axon_delay_fused_matches_unfused(cuda):

@@ -127,3 +127,34 @@ def test_persistent_state_helpers():
     assert li.persistent_state(st, sp).tolist() == [1.0, 0.0]
     assert at.persistent_ref_state(st, sp, torch.tensor([0.5, 0.5])).tolist() == [1.0, 3.0]
     assert at.persistent_th_state(st, sp, 0.25).tolist() == [1.0, 2.25]
+
+
+def test_sigma_delta_host_side():
+    """Constructor arithmetic, refusals and shape checks of the sigma-delta family (no kernel runs)."""
+    import lava_dl_b200.slayer as slayer
+    relu = torch.nn.functional.relu
+    n = slayer.neuron.sigma_delta.Neuron(threshold=0.1, activation=relu, scale=1 << 6)
+    assert n.w_scale == 64 and n.s_scale == 4096
+    assert abs(float(n.threshold) - 6 / 64) < 1e-7            # int(0.1 * 64) / 64
+    assert n.delta.scale == 4096 and n.graded_spike is True
+    assert n.device_params == {'type': 'SDNN', 'activation': 'relu', 'vThMant': 6}
+    assert slayer.neuron.sigma_delta.neuron_params({'vThMant': 32}, scale=64) == {'threshold': 0.5}
+    with pytest.raises(NotImplementedError):
+        slayer.axon.Delta(threshold=0.5, cum_error=True)
+    d = slayer.axon.Delta(threshold=1e-6, scale=64)
+    d.clamp()
+    assert float(d.threshold) == 1 / 64
+    with pytest.raises(AssertionError):
+        slayer.dendrite.Sigma()(torch.zeros(4, 8))            # needs [batch, ..., time]
+    with pytest.raises(RuntimeError):
+        slayer.dendrite.Sigma()(torch.zeros(2, 3, 8))         # CPU tensor: no fallback
+    with pytest.raises(RuntimeError):
+        n(torch.zeros(2, 3, 8))
+    assert slayer.dendrite.Sigma().device_params == {'type': 'SDNN', 'sigma_output': True}
+
+
+def test_delay_fusable_bound():
+    import lava_dl_b200.slayer as slayer
+    assert slayer.axon.Delay(max_delay=None).fusable_steps is None
+    assert slayer.axon.Delay(max_delay=62).fusable_steps == 62
+    assert slayer.axon.Delay(sampling_time=2, max_delay=100).fusable_steps == 50
