@@ -265,16 +265,24 @@ int sb_delta_fwd(const float* x, const float* threshold, int64_t n_threshold, co
 int sb_delta_bwd(const float* grad_out, const float* delta_input, const float* threshold, int64_t n_threshold,
                  float* grad_x, float* grad_threshold, void* scratch, const sb_geom* g, float tau_grad,
                  float scale_grad, void* stream);
-/* Sigma-delta ReLU neuron, forward only (inference): neuron/sigma_delta.py:171-219
- * with activation = relu and no normalisation, in one pass of 8 bytes per step:
+/* Sigma-delta ReLU neuron: neuron/sigma_delta.py:171-219 with activation = relu
+ * and no normalisation, one pass each way:
  * sigma -> + bias (nullable; 1 value or one per neuron, rows_per_batch values, as
- * set_bias stores it) -> relu -> delta -> floor.
- * final_sigma / final_pre / final_residual (nullable float[rows]) are the
- * persistent states of the sigma and delta units after the call. */
+ * set_bias stores it) -> relu -> delta -> floor.  8 bytes per step for inference;
+ * activation (nullable) saves the ReLU output for the backward pass, delta_input
+ * (nullable, needs activation) the delta unit's difference for the threshold
+ * gradient.  final_sigma / final_pre / final_residual (nullable float[rows]) are
+ * the persistent states of the sigma and delta units after the call.
+ * Backward: grad_x[t] = float(sum_{s>=t} (g[s] - g[s+1]) * (activation[s] > 0)),
+ * grad_threshold as sb_delta_bwd.  No bias gradient. */
 int sb_sdnn_relu_fwd(const float* x, const float* sigma_state, const float* bias, int64_t n_bias,
                      const float* threshold, int64_t n_threshold, const float* pre_state,
-                     const float* residual_state, float* out, float* final_sigma, float* final_pre,
-                     float* final_residual, const sb_geom* g, double scale, void* stream);
+                     const float* residual_state, float* out, float* activation, float* delta_input,
+                     float* final_sigma, float* final_pre, float* final_residual, const sb_geom* g, double scale,
+                     void* stream);
+int sb_sdnn_relu_bwd(const float* grad_out, const float* activation, const float* delta_input,
+                     const float* threshold, int64_t n_threshold, float* grad_x, float* grad_threshold,
+                     void* scratch, const sb_geom* g, float tau_grad, float scale_grad, void* stream);
 
 /* ---- sum-pooling synapse (next to the path: what feeds the neurons in conv networks) ----
  * Replaces the Conv3d call of synapse/layer.py:438-508 for the default pooling

@@ -168,11 +168,14 @@ struct DeltaBwd {
 //   s[t] = float(cumsum x) + sigma_state;  a[t] = relu(s[t] + bias);  out = delta(a)
 // bias: one value, or one per neuron as set_bias() stores it (sigma_delta.py:152-165)
 // ===========================================================================
+// SAVE = 0: inference (8 B per step).  SAVE = 1 also writes the activation (what the backward's
+// ReLU mask needs), SAVE = 2 the delta unit's difference as well (threshold gradient).
+template <int SAVE>
 struct SdnnFwd {
-  static constexpr int NIN = 1, NOUT = 1;
+  static constexpr int NIN = 1, NOUT = 1 + SAVE;
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = 0;
-  SB_PIPE(3, 3, 32);
+  SB_PIPE(3, (SAVE == 0 ? 3 : 1), 32);
   struct Params {
     DeltaParams delta;
     const float* sigma_state;   // [rows] or null
@@ -191,12 +194,15 @@ struct SdnnFwd {
     has_bias = p.bias.v != nullptr;
     bias = (valid && has_bias) ? __ldg(p.bias.v + (p.bias.n <= 1 ? 0 : row % g.rows_per_batch)) : 0.f;
   }
-  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[1]) {
+  __device__ __forceinline__ void step(const float (&a)[1], float (&b)[NOUT]) {
     acc += (double)a[0];
     last_sigma = __fadd_rn((float)acc, spre);
     const float z = has_bias ? __fadd_rn(last_sigma, bias) : last_sigma;
+    const float act = fmaxf(z, 0.f);
     float d;
-    b[0] = s.step(fmaxf(z, 0.f), d);
+    b[0] = s.step(act, d);
+    if (SAVE >= 1) b[1] = act;
+    if (SAVE >= 2) b[NOUT - 1] = d;
   }
   __device__ __forceinline__ void tile_end() {}
   __device__ __forceinline__ void finish(const Params& p, const RowGeom&, int64_t row, bool valid, int, int64_t) {
@@ -204,6 +210,45 @@ struct SdnnFwd {
     if (p.final_sigma) p.final_sigma[row] = last_sigma;
     if (p.final_pre) p.final_pre[row] = s.pre;
     if (p.delta.final_residual) p.delta.final_residual[row] = s.res;
+  }
+};
+
+// ===========================================================================
+// Backward of the same neuron in one reverse pass:
+//   gd[t] = g[t] - g[t+1]                      (delta, delta.py:103-107)
+//   gz[t] = gd[t] if act[t] > 0 else 0          (ReLU)
+//   gx[t] = float(sum_{s>=t} gz[s])             (adjoint of the running sum, double accumulation)
+// and, with TGRAD, the threshold gradient of the delta unit from its saved difference.
+// ===========================================================================
+template <bool TGRAD>
+struct SdnnBwd {
+  static constexpr int NIN = TGRAD ? 3 : 2, NOUT = 1;
+  static constexpr bool REVERSE = true;
+  static constexpr int NBIT = 0;
+  SB_PIPE(3, 1, 32);
+  typedef typename DeltaBwd<TGRAD>::Params Params;
+  DeltaBwd<TGRAD> dl;
+  double acc;
+  __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
+    dl.init(p, g, row, valid);
+    acc = 0.0;
+  }
+  __device__ __forceinline__ void step(const float (&in)[NIN], float (&b)[1]) {
+    float gd[1];
+    if (TGRAD) {
+      const float din[2] = {in[0], in[2]};
+      dl.step(reinterpret_cast<const float(&)[DeltaBwd<TGRAD>::NIN]>(din), gd);
+    } else {
+      const float din[1] = {in[0]};
+      dl.step(reinterpret_cast<const float(&)[DeltaBwd<TGRAD>::NIN]>(din), gd);
+    }
+    acc += (double)(in[1] > 0.f ? gd[0] : 0.f);
+    b[0] = (float)acc;
+  }
+  __device__ __forceinline__ void tile_end() { dl.tile_end(); }
+  __device__ __forceinline__ void finish(const Params& p, const RowGeom& g, int64_t row, bool valid, int lane,
+                                         int64_t warp_id) {
+    dl.finish(p, g, row, valid, lane, warp_id);
   }
 };
 

@@ -65,7 +65,8 @@ SIGNATURES = {
     'sb_sigma_bwd': (c_int, [_P, _P, _I64, _I64, _P]),
     'sb_delta_fwd': (c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _G, c_double, _P]),
     'sb_delta_bwd': (c_int, [_P, _P, _P, _I64, _P, _P, _P, _G, c_float, c_float, _P]),
-    'sb_sdnn_relu_fwd': (c_int, [_P, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _G, c_double, _P]),
+    'sb_sdnn_relu_fwd': (c_int, [_P, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _G, c_double, _P]),
+    'sb_sdnn_relu_bwd': (c_int, [_P, _P, _P, _P, _I64, _P, _P, _P, _G, c_float, c_float, _P]),
     'sb_fir_conv': (c_int, [_P, _P, _I64, c_float, _P, _I64, _I64, _P]),
     'sb_fir_corr': (c_int, [_P, _P, _I64, c_float, _P, _I64, _I64, _P]),
     'sb_fir_uses_tensor_cores': (c_int, [_I64, _I64, _I64]),

@@ -369,20 +369,42 @@ def delta_bwd(grad_out, delta_input, threshold, tau_grad, scale_grad, need_thres
     return gx, None
 
 
-def sdnn_relu_fwd(x, threshold, bias, sigma_state, pre_state, residual_state, scale):
-    """Sigma -> bias -> relu -> delta -> floor in one pass.  Returns dict(out, final_sigma, final_pre, final_residual)."""
+def sdnn_relu_fwd(x, threshold, bias, sigma_state, pre_state, residual_state, scale, want_act=False,
+                  want_delta=False):
+    """Sigma -> bias -> relu -> delta -> floor in one pass.  Returns dict(out, activation, delta_input,
+    final_sigma, final_pre, final_residual); the two saved tensors only on request."""
     N.require_cuda(x)
     x = _c(x)
     thr = _param(threshold, x)
     b = None if bias is None else _param(bias, x)
     ss, pre, res = _opt_state(sigma_state, x), _opt_state(pre_state, x), _opt_state(residual_state, x)
     out = torch.empty_like(x)
+    act = torch.empty_like(x) if (want_act or want_delta) else None
+    dlt = torch.empty_like(x) if want_delta else None
     fs, fp, fr = _vec(x), _vec(x), _vec(x)
     g = geom(x, thr.numel())
     N.call('sb_sdnn_relu_fwd', x, N.ptr(x), N.ptr(ss), N.ptr(b), 0 if b is None else b.numel(), N.ptr(thr),
-           thr.numel(), N.ptr(pre), N.ptr(res), N.ptr(out), N.ptr(fs), N.ptr(fp), N.ptr(fr), g, float(scale),
-           N.stream_of(x))
-    return dict(out=out, final_sigma=fs, final_pre=fp, final_residual=fr)
+           thr.numel(), N.ptr(pre), N.ptr(res), N.ptr(out), N.ptr(act), N.ptr(dlt), N.ptr(fs), N.ptr(fp), N.ptr(fr), g,
+           float(scale), N.stream_of(x))
+    return dict(out=out, activation=act, delta_input=dlt, final_sigma=fs, final_pre=fp, final_residual=fr)
+
+
+def sdnn_relu_bwd(grad_out, activation, delta_input, threshold, tau_grad, scale_grad, need_threshold_grad):
+    N.require_cuda(grad_out)
+    grad_out = _c(grad_out)
+    thr = _param(threshold, grad_out)
+    gx = torch.empty_like(grad_out)
+    g = geom(grad_out, thr.numel())
+    if need_threshold_grad:
+        gthr = torch.empty(thr.numel(), device=grad_out.device, dtype=torch.float32)
+        scr = N.scratch(g.rows, thr.numel(), grad_out.device)
+        N.call('sb_sdnn_relu_bwd', grad_out, N.ptr(grad_out), N.ptr(activation), N.ptr(delta_input), N.ptr(thr),
+               thr.numel(), N.ptr(gx), N.ptr(gthr), N.ptr(scr), g, float(tau_grad), float(scale_grad),
+               N.stream_of(grad_out))
+        return gx, gthr.reshape(threshold.shape)
+    N.call('sb_sdnn_relu_bwd', grad_out, N.ptr(grad_out), N.ptr(activation), None, N.ptr(thr), thr.numel(), N.ptr(gx),
+           None, None, g, float(tau_grad), float(scale_grad), N.stream_of(grad_out))
+    return gx, None
 
 
 # --------------------------------------------------------------------------

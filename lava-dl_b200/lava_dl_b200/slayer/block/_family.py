@@ -6,7 +6,7 @@ from .. import synapse
 from ..axon import Delay
 
 
-def make_blocks(neuron_class):
+def make_blocks(neuron_class, default_delay_shift=True):
     class _Family:
         """Creates the neuron, the optional learnable delay, and hooks the neuron's
         8-bit quantiser into the synapse unless the caller named a pre-hook."""
@@ -17,6 +17,8 @@ def make_blocks(neuron_class):
             self.synapse = synapse_class(**self.synapse_params)
             if 'pre_hook_fx' not in kwargs:
                 self.synapse.pre_hook_fx = self.neuron.quantize_8bit
+            if 'delay_shift' not in kwargs:
+                self.delay_shift = default_delay_shift
             del self.neuron_params, self.synapse_params
 
     class Dense(_Family, base.AbstractDense):

@@ -458,6 +458,26 @@ def main():
     save('neuron_sdnn_bias_rank4', x=x4, threshold=nrn.delta.threshold.data.reshape(-1).clone(),
          bias=nrn.bias.data.reshape(-1).clone(), out=y)
 
+    # sigma-delta blocks: delta-encoding input block and two dense blocks
+    sdp = dict(threshold=0.1, activation=relu, tau_grad=0.5, scale_grad=1.0, requires_grad=False)
+    sblk = slayer.block.sigma_delta
+    snet = torch.nn.ModuleList([sblk.Input(dict(sdp)), sblk.Dense(dict(sdp), 12, 10, weight_scale=2),
+                                sblk.Dense(dict(sdp), 10, 4, weight_scale=2)])
+    for layer in snet[1:]:
+        layer.synapse.weight.data = 0.4 * randn(*layer.synapse.weight.shape)
+    xs = torch.cumsum(0.08 * randn(B, 12, T), dim=-1)
+    xin = xs.clone().requires_grad_()
+    acts, y = {}, xin
+    for i, layer in enumerate(snet):
+        y = layer(y)
+        acts[f'act{i}'] = y
+    g_s = randn(*y.shape)
+    (y * g_s).sum().backward()
+    save('network_sdnn_dense', x=xs, grad_out=g_s, grad_x=xin.grad, weight1=snet[1].synapse.weight.data,
+         weight2=snet[2].synapse.weight.data, grad_weight1=snet[1].synapse.weight.grad,
+         grad_weight2=snet[2].synapse.weight.grad, **acts)
+    print('sigma-delta network event counts per layer:', [int((acts[f'act{i}'] != 0).sum()) for i in range(3)])
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

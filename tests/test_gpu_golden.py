@@ -419,3 +419,30 @@ def test_sigma_delta_neuron(cuda, slayer):
     nrn2 = slayer.neuron.sigma_delta.Neuron(threshold=0.05, activation=torch.relu, shared_param=False).to(cuda)
     nrn2.set_bias(T(g['bias'], cuda).reshape(C, H))
     assert_exact(nrn2(x), g['out'], 'per-neuron bias, separate passes')
+
+
+def test_sigma_delta_block_network(cuda, slayer):
+    """Delta-encoding input block + two dense sigma-delta blocks against the reference's
+    blocks: events bit-exact layer by layer, gradients to 1e-5."""
+    g = load_golden('network_sdnn_dense')
+    relu = torch.nn.functional.relu
+    p = dict(threshold=0.1, activation=relu, tau_grad=0.5, scale_grad=1.0, requires_grad=False)
+    blk = slayer.block.sigma_delta
+    net = torch.nn.ModuleList([blk.Input(dict(p)), blk.Dense(dict(p), 12, 10, weight_scale=2),
+                               blk.Dense(dict(p), 10, 4, weight_scale=2)]).to(cuda)
+    net[1].synapse.weight.data = T(g['weight1'], cuda)
+    net[2].synapse.weight.data = T(g['weight2'], cuda)
+    x = T(g['x'], cuda, True)
+    y = x
+    for i, layer in enumerate(net):
+        y = layer(y)
+        assert_exact(y, g[f'act{i}'], f'layer {i} events')
+    (y * T(g['grad_out'], cuda)).sum().backward()
+    assert_close(x.grad, g['grad_x'], 'grad_x')
+    assert_close(net[1].synapse.weight.grad, g['grad_weight1'], 'grad weight 1')
+    assert_close(net[2].synapse.weight.grad, g['grad_weight2'], 'grad weight 2')
+    with torch.no_grad():           # inference: every neuron runs as the one-pass kernel
+        y = T(g['x'], cuda)
+        for i, layer in enumerate(net):
+            y = layer(y)
+            assert_exact(y, g[f'act{i}'], f'layer {i} events, one-pass kernels')

@@ -576,6 +576,24 @@ def test_sigma_delta_relu_fused(shape, bias_kind, cuda, ops):
         assert_exact(r['final_sigma'], want['sigma'][..., -1], 'sigma state')
         assert_exact(r['final_pre'], want['pre'], 'delta pre state')
         assert_exact(r['final_residual'], want['residual'], 'delta residual state')
+    # training variant: same output, activation and difference saved, one-pass backward
+    r = ops.sdnn_relu_fwd(dev(x, cuda), dev(thr, cuda), None if bias is None else dev(bias, cuda), sd[0], sd[1], sd[2],
+                          4096, want_act=True, want_delta=True)
+    assert_exact(r['out'], want['out'], 'output with saves')
+    assert_exact(r['activation'], want['act'], 'saved activation')
+    assert_exact(r['delta_input'], want['delta_input'], 'saved difference')
+    go = rng.normal(size=shape).astype(np.float32)
+    g_act, gthr_want = O.delta_bwd(go, want['delta_input'], thr, 0.7, 1.3)
+    gx_want = O.sigma((g_act * (want['act'] > 0)).astype(np.float32), reverse=True)
+    gx, gthr = ops.sdnn_relu_bwd(dev(go, cuda), r['activation'], r['delta_input'], dev(thr, cuda), 0.7, 1.3, True)
+    assert_exact(gx, gx_want, 'grad_x, one-pass backward')
+    d = want['delta_input'].astype(np.float64)
+    th = thr.astype(np.float64).reshape((1, -1) + (1,) * (len(shape) - 2))
+    sub = np.abs(d) - th
+    mag = np.where(sub > 0, np.abs(d) * 1.3 * np.exp(-np.abs(sub) / 0.7) / th, 1.0) * np.abs(go)
+    assert_close(gthr, gthr_want, 'grad threshold', scale=mag.sum(axis=tuple(i for i in range(mag.ndim) if i != 1)) + 1e-30)
+    assert_exact(ops.sdnn_relu_bwd(dev(go, cuda), r['activation'], None, dev(thr, cuda), 1.0, 1.0, False)[0], gx_want,
+                 'grad_x only')
 
 
 def test_empty_inputs(cuda, ops):
