@@ -37,19 +37,21 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
   const int n = blockIdx.x / g.Ho, ho = blockIdx.x % g.Ho;
   const int owner = tid % g.owners, wg = tid / g.owners;
   const int cog = owner % g.ncog, tapg = owner / g.ncog;
-  const int co0 = cog * kTile, tap0 = tapg * kTile;
   const bool active = wg < g.wgroups;
 
-  // offsets of this thread's 8 taps inside x_s (column j added to the output column)
+  // This thread's 8 taps are tapg, tapg + ntapg, ...: for a given k the threads of a warp then read
+  // consecutive taps, and with x_s laid out [row][time word][column] and a row stride that is kw
+  // (mod 8) 128-bit words, consecutive taps sit in consecutive banks.  xoff: offset of tap k in x_s.
   int xoff[kTile];
-  bool xok[kTile];
 #pragma unroll
   for (int k = 0; k < kTile; ++k) {
-    const int tap = tap0 + k;
-    xok[k] = tap < g.taps;
-    const int r = xok[k] ? tap / g.kw : 0, j = xok[k] ? tap - r * g.kw : 0;
-    xoff[k] = r * g.x_row + j * kQ;
+    const int tap = tapg + g.ntapg * k;
+    const bool ok = tap < g.taps;
+    const int r = ok ? tap / g.kw : 0, j = ok ? tap - r * g.kw : 0;
+    xoff[k] = r * g.x_row + j;
   }
+  // dz rows are stored channel-tile interleaved (row = (co % 8) * ncog + co / 8) with an odd stride,
+  // so the ncog different rows a warp reads at once fall into different banks.
   float acc[kTile][kTile];
 #pragma unroll
   for (int c = 0; c < kTile; ++c)
@@ -75,7 +77,8 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
       for (int co = dz_r0; co < rows_dz; co += dz_rstep) {
         const bool ok = tin && co < g.Co;
         const float* p = ok ? src + (int64_t)co * g.Ho * g.Wo * g.T : dz;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + (uint32_t)(co * g.dz_row + dz_lane) * 16u),
+        const int row = (co % kTile) * g.ncog + co / kTile;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + (uint32_t)(row * g.dz_row + dz_lane) * 16u),
                      "l"(p), "r"(ok ? 16 : 0) : "memory");
       }
     }
@@ -88,7 +91,7 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
         const bool ok = cin && hin >= 0 && hin < g.H;
         const float* p = ok ? src + ((int64_t)ci * g.H + hin) * g.W * g.T : x;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     ::"r"(dst0 + (uint32_t)(rows_dz * g.dz_row + r * g.x_row + x_lane) * 16u), "l"(p), "r"(ok ? 16 : 0)
+                     ::"r"(dst0 + (uint32_t)(rows_dz * g.dz_row + r * g.x_row + q * g.Wp + wp) * 16u), "l"(p), "r"(ok ? 16 : 0)
                      : "memory");
       }
     }
@@ -113,10 +116,10 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
         for (int q = 0; q < kQ; ++q) {
           float4 b[kTile];
 #pragma unroll
-          for (int k = 0; k < kTile; ++k) b[k] = x_s[xoff[k] + w * kQ + q];
+          for (int k = 0; k < kTile; ++k) b[k] = x_s[xoff[k] + q * g.Wp + w];
 #pragma unroll
           for (int cc = 0; cc < kTile; ++cc) {
-            const float4 a = dz_s[(co0 + cc) * g.dz_row + w * kQ + q];
+            const float4 a = dz_s[(cc * g.ncog + cog) * g.dz_row + w * kQ + q];
 #pragma unroll
             for (int k = 0; k < kTile; ++k) {
               acc[cc][k] = fmaf(a.x, b[k].x, acc[cc][k]);
@@ -142,7 +145,7 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
   float* out = partial + (size_t)blockIdx.x * g.Co * g.taps;
   for (int i = tid; i < g.owners * 64; i += nthreads) {
     const int o = i / 64, e = i % 64;
-    const int co = (o % g.ncog) * kTile + e / kTile, tap = (o / g.ncog) * kTile + e % kTile;
+    const int co = (o % g.ncog) * kTile + e / kTile, tap = (o / g.ncog) + g.ntapg * (e % kTile);
     if (co < g.Co && tap < g.taps) {
       float s = 0.f;
       for (int wgi = 0; wgi < g.wgroups; ++wgi) s += red[((size_t)wgi * g.owners + o) * 64 + e];
@@ -177,8 +180,9 @@ int wgrad_plan(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t 
   while (wgroups > 1 && g->Wo % wgroups != 0) --wgroups;   // equal work per column group
   g->wgroups = wgroups;
   g->Wp = (int)(Wo + kw - 1);
-  g->dz_row = g->Wo * kQ + 1;      // + one 128-bit word: rows of neighbouring channel groups on different banks
-  g->x_row = g->Wp * kQ + 1;
+  g->dz_row = g->Wo * kQ + 1;                       // odd: interleaved channel tiles on different banks
+  g->x_row = g->Wp * kQ;
+  while ((g->x_row & 7) != (g->kw & 7)) ++g->x_row;  // consecutive taps on consecutive banks
   const size_t stage = 2 * sizeof(float4) * ((size_t)g->ncog * kTile * g->dz_row + (size_t)Ci * kh * g->x_row);
   const size_t red = sizeof(float) * (size_t)wgroups * g->owners * 64;
   *smem = stage > red ? stage : red;
