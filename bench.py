@@ -60,8 +60,12 @@ NCU_TRAFFIC_PER_UNIT = {
     'li_fwd': 7.76,
     'li_bwd': 7.74,
     'shift': 7.63,
-    'fir_conv': 7.77,
+    'fir_conv': 7.76,
     'delay_fir_fwd': 7.75,
+    'sigma_fwd': 7.75,
+    'delta_fwd': 7.74,
+    'sdnn_fwd': 7.75,
+    'cuba_fwd_delayed': 11.70,
 }
 
 
