@@ -699,7 +699,7 @@ struct RfBwd {
   static constexpr int NIN = 3 + (TENSOR_THR ? 1 : 0), NOUT = 2;
   static constexpr bool REVERSE = true;
   static constexpr int NBIT = 0;
-  SB_PIPE(3, 1, 16);
+  SB_PIPE((PGRAD ? 3 : 6), 1, 16);   // six stages measured best without sin/cos gradients (adrf_bwd 0.82 -> 0.87)
   struct Params {
     DecayVec sin_decay, cos_decay;
     CSurrogate sg;
