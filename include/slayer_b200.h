@@ -316,6 +316,13 @@ int sb_conv_wgrad(const float* x, const float* grad_y, float* grad_weight, void*
                   int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T,
                   void* stream);
 
+/* ---- gradient plumbing ------------------------------------------------------------
+ * No counterpart in the reference: out[i] = *value (a device scalar) for i < n.
+ * Autograd hands the backward of sum() / mean() one number broadcast to the
+ * tensor's shape; the backward entry points want a dense tensor, and this fills
+ * it at memory speed without reading the number on the host. */
+int sb_broadcast_fill(const float* value, float* out, int64_t n, void* stream);
+
 /* ---- measurement aid ------------------------------------------------------------
  * No counterpart in the reference and not on the hot path: a plain streaming
  * kernel that reads `reads` streams of n floats (laid out back to back in `in`)

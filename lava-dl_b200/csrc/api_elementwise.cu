@@ -312,3 +312,34 @@ int sb_shift(const float* x, const float* lut, int64_t n_lut, float shift, float
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// out[i] = *value for i < n, value read on the device: materialises a gradient
+// that autograd hands over as one broadcast number (the backward of sum() or
+// mean()) at memory speed and without a host round trip.
+// ---------------------------------------------------------------------------
+namespace {
+__global__ void broadcast_fill_kernel(const float* __restrict__ value, float* __restrict__ out, int64_t n) {
+  const float v = __ldg(value);
+  const int64_t n4 = n >> 2;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = (((uintptr_t)out) & 15u) == 0;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (aligned) {
+    const float4 v4 = make_float4(v, v, v, v);
+    for (int64_t k = i; k < n4; k += stride) reinterpret_cast<float4*>(out)[k] = v4;
+    for (int64_t k = (n4 << 2) + i; k < n; k += stride) out[k] = v;
+  } else {
+    for (int64_t k = i; k < n; k += stride) out[k] = v;
+  }
+}
+}  // namespace
+
+extern "C" int sb_broadcast_fill(const float* value, float* out, int64_t n, void* stream) {
+  SB_REQUIRE(n >= 0, "negative element count");
+  if (n == 0) return SB_OK;
+  SB_REQUIRE(value && out, "null pointer");
+  broadcast_fill_kernel<<<(unsigned)sb::sm_count() * 8, 512, 0, (cudaStream_t)stream>>>(value, out, n);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}

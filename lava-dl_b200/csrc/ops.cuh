@@ -438,7 +438,9 @@ struct CubaFwd {
   static constexpr int NIN = 1, NOUT = 1 + (OUT_CUR ? 1 : 0) + (OUT_SPK ? 1 : 0);
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = (OUT_SPK && !GRADED) ? 1 : 0;  // binary spikes leave as bits
-  SB_PIPE(3, ((NOUT - NBIT) == 1 ? 3 : 1), 32);
+  // boxes per stage by the number of tiles a stage holds: 3 for one (inference), 2 for two (training:
+  // current + voltage; 3.44 -> 3.12 ms at [64,8192,2000]), else 1
+  SB_PIPE(3, ((NOUT - NBIT) == 1 ? 3 : ((NOUT - NBIT) == 2 ? 2 : 1)), 32);
   static constexpr int IV = OUT_CUR ? 1 : 0, IS = IV + 1;
   struct Params {
     DecayVec cdecay, vdecay;
@@ -501,7 +503,8 @@ struct CubaBwd {
   static constexpr int NBIT = 0;
   // Six stages of one 32-step box measured best without decay gradients (cuba_bwd 0.86 -> 0.90,
   // alif_bwd 0.84 -> 0.89 of copy bandwidth): the reverse scan is short of loads in flight, not of warps.
-  SB_PIPE((DGRAD ? 3 : 6), 1, ((DGRAD && NIN >= 3) ? 16 : 32));
+  // With decay gradients (CUBA: three input tiles) two 32-step boxes and three stages (3.03 -> 2.74 ms).
+  SB_PIPE((DGRAD ? 3 : 6), ((DGRAD && NIN == 3) ? 2 : 1), ((DGRAD && NIN > 3) ? 16 : 32));
   static constexpr int ITH = 2, ICUR = 2 + (TENSOR_THR ? 1 : 0);
   struct Params {
     DecayVec cdecay, vdecay;

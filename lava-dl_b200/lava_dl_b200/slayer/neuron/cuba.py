@@ -66,6 +66,7 @@ class _FusedForward(torch.autograd.Function):
     def forward(ctx, input, cdecay, vdecay, cstate, vstate, threshold, w_scale, tau_rho, scale_rho, graded,
                 spike_delay=0, delay_head=None, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         need_dgrad = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+        ctx.set_materialize_grads(False)   # no zero tensors for the outputs nobody differentiates
         r = _ops.cuba_fwd(input, cdecay, vdecay, cstate, vstate, threshold, w_scale,
                           want_current=need_dgrad, want_spike=True, graded=graded, spike_scale=1.0,
                           spike_delay=spike_delay, delay_head=delay_head,
@@ -85,6 +86,8 @@ class _FusedForward(torch.autograd.Function):
     def backward(ctx, grad_spike, *_):
         (threshold, tau_rho, scale_rho, graded, need_dgrad, spike_delay, has_axon, axon_ts, axon_grad_scale,
          need_axon_grad) = ctx.consts
+        if grad_spike is None:
+            return (None,) * 15
         voltage, cdecay, vdecay = ctx.saved_tensors[:3]
         current = ctx.saved_tensors[3] if need_dgrad else None
         g_axon = None
