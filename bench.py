@@ -149,6 +149,10 @@ WORKLOADS = {
 # one-step delay); units = neuron-steps over all seven spiking layers (33291 neurons per sample)
 WORKLOADS['cfg4_fwd'] = Workload('cfg4_fwd', (32, 2, 128, 128, 300), 0)
 WORKLOADS['cfg4_train'] = Workload('cfg4_train', (32, 2, 128, 128, 300), 0)
+# dense recurrent CUBA block (block.cuba.Recurrent, 512 -> 512 neurons): one launch per direction for the walk over time
+WORKLOADS['recurrent_fwd'] = Workload('recurrent_fwd', (128, 512, 300), 0)
+WORKLOADS['recurrent_train'] = Workload('recurrent_train', (128, 512, 300), 0)
+NETWORKS = ('cfg4', 'recurrent')   # chains of kernels: no single roofline, no CPU port
 CFG4_NEURONS = 2048 + 16384 + 4096 + 8192 + 2048 + 512 + 11
 
 # plain streaming kernel at the read:write mixes of the kernels above (sb_probe_stream): the HBM
@@ -204,6 +208,24 @@ def build_step(name, shape, device, seed):
             _dist.allreduce_param_grads(params)
         # forward as above, backward: 7 fused neuron kernels + 3 pooling adjoints
         return step, 20, (net, x)
+    if name.startswith('recurrent'):
+        import lava_dl_b200.slayer as slayer
+        train = name == 'recurrent_train'
+        torch.manual_seed(seed)
+        blk = slayer.block.cuba.Recurrent(dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03),
+                                          shape[1], shape[1], weight_scale=2).to(device)
+        gen = torch.Generator(device=device).manual_seed(seed)
+        x = (torch.rand(shape, device=device, generator=gen) < 0.05).float()
+        params = [q for q in blk.parameters() if q.requires_grad]
+
+        def step():
+            if not train:
+                with torch.no_grad():
+                    return blk(x)
+            for q in params:
+                q.grad = None
+            blk(x).sum().backward()
+        return step, (2 if train else 1), (blk, x)
     if name.startswith('stream_'):
         from lava_dl_b200 import _native as N
         r, w = int(name[7]), int(name[9])
@@ -582,7 +604,7 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        if wl.name.startswith(('stream_', 'cfg4')):
+        if wl.name.startswith(('stream_',) + NETWORKS):
             print(json.dumps({'impl': 'reference', 'unavailable': 'no CPU port of this workload (probe / full network)'}))
             return
         cpu, sec = time_cpu(wl, max(1, args.steps), max(1, args.warmup))
@@ -636,7 +658,7 @@ def main():
     value = units * world / (ms_per_step * 1e-3)
 
     peak, peak_kind = peaks()
-    kern_ms = statistics.mean(per) / (1 if wl.name.startswith('cfg4') else launches_per_step)
+    kern_ms = statistics.mean(per) / (1 if wl.name.startswith(NETWORKS) else launches_per_step)
     achieved = wl.bpu * units / (kern_ms * 1e-3) / 1e9
     tpu = NCU_TRAFFIC_PER_UNIT.get(wl.name)
     roofline = {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
@@ -692,10 +714,13 @@ def main():
                            'allreduce_elements': n_red,
                            'path': 'cuba.Neuron(requires_grad=True)(x).sum().backward() + one all-reduce of decay grads'}
         torch.cuda.empty_cache()
+    if wl.name.startswith('recurrent'):
+        line['roofline'] = None  # latency-bound walk over time plus two GEMMs
+        line['config']['network'] = 'block.cuba.Recurrent(512, 512), spikes in at 5 %'
     if wl.name.startswith('cfg4'):
         line['roofline'] = None  # a network of cuDNN synapses and neuron kernels has no single roof
         line['config']['network'] = 'Pool4-Conv(2,16,5)-Pool2-Conv(16,32,3)-Pool2-Flatten-Dense(2048,512)-Dense(512,11), CUBA'
-    if rank == 0 and not args.no_cpu and not wl.name.startswith(('stream_', 'cfg4')):
+    if rank == 0 and not args.no_cpu and not wl.name.startswith(('stream_',) + NETWORKS):
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         line['cpu_baseline'] = cpu
     if dist is not None:

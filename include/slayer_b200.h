@@ -323,6 +323,27 @@ int sb_conv_wgrad(const float* x, const float* grad_y, float* grad_weight, void*
  * it at memory speed without reading the number on the host. */
 int sb_broadcast_fill(const float* value, float* out, int64_t n, void* stream);
 
+/* ---- dense recurrent CUBA layer ---------------------------------------------------
+ * Replaces the per-step Python loops of slayer/utils/recurrent.py:45-112 (forward
+ * :54-77, backward :79-112), the caller being block/base.py:1460-1488.
+ * z [batch, neurons, T] is the output of the input synapse; rec_t [neurons, neurons]
+ * is the (already quantised) recurrent matrix transposed, rec the same matrix as is.
+ *   spike[t] = CUBA(z[t] + R spike[t-1]), the neuron state carried from step to step
+ *   (cstate/vstate in, final_* out, one value per [batch, neuron]).
+ * Backward: every step was a Neuron call with T = 1 on a detached state, so
+ *   grad_z[t] = surrogate(voltage[t]) * (grad_spike[t] + R^T grad_z[t+1]);
+ * the decay gradients of such calls are zero; grad of R is the plain product
+ * grad_z[..., 1:] x spike[..., :-1] and is left to the caller's GEMM.
+ * One neuron per thread: neurons <= 1024.  Decays: 1 or `neurons` values. */
+int sb_cuba_recurrent_fwd(const float* z, const float* rec_t, const float* cdecay, int64_t n_cdecay,
+                          const float* vdecay, int64_t n_vdecay, const float* cstate, const float* vstate,
+                          float* voltage, float* spike, float* final_c, float* final_v, float* final_s,
+                          int64_t batch, int64_t neurons, int64_t T, double threshold, int w_scale, int graded,
+                          float spike_scale, void* stream);
+int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const float* rec, float* grad_z,
+                          int64_t batch, int64_t neurons, int64_t T, float threshold, float tau_rho,
+                          float scale_rho, int graded, void* stream);
+
 /* ---- measurement aid ------------------------------------------------------------
  * No counterpart in the reference and not on the hot path: a plain streaming
  * kernel that reads `reads` streams of n floats (laid out back to back in `in`)

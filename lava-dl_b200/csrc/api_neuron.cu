@@ -5,6 +5,7 @@
 
 #include "api_util.cuh"
 #include "reduce.cuh"
+#include "recurrent.cuh"
 #include "rowscan.cuh"
 
 using namespace sb;
@@ -276,6 +277,74 @@ int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const f
     SB_TRY(fold_param_grad((double*)scratch_sin, grad_sin, rg, n_decay, st));
     SB_TRY(fold_param_grad((double*)scratch_cos, grad_cos, rg, n_decay, st));
   }
+  return SB_OK;
+}
+
+int sb_cuba_recurrent_fwd(const float* z, const float* rec_t, const float* cdecay, int64_t n_cdecay,
+                          const float* vdecay, int64_t n_vdecay, const float* cstate, const float* vstate,
+                          float* voltage, float* spike, float* final_c, float* final_v, float* final_s,
+                          int64_t batch, int64_t neurons, int64_t T, double threshold, int w_scale, int graded,
+                          float spike_scale, void* stream) {
+  SB_REQUIRE(batch >= 0 && neurons >= 0 && T >= 0 && T <= INT_MAX, "negative or oversized extent");
+  if (batch == 0 || neurons == 0 || T == 0) return SB_OK;
+  SB_REQUIRE(neurons <= 1024, "the recurrent kernel holds one neuron per thread: at most 1024 neurons (got %lld)",
+             (long long)neurons);
+  SB_REQUIRE(batch <= INT_MAX, "batch too large");
+  SB_TRY(check_count(n_cdecay, "current decay"));
+  SB_TRY(check_count(n_vdecay, "voltage decay"));
+  SB_REQUIRE((n_cdecay == 1 || n_cdecay == neurons) && (n_vdecay == 1 || n_vdecay == neurons),
+             "decays are shared or one per neuron");
+  SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
+  SB_REQUIRE(z && rec_t && cdecay && vdecay && cstate && vstate && voltage && spike, "null pointer");
+  const RowGeom rg{batch * neurons, neurons, 1, (int)T};
+  const Scale sc = make_scale(w_scale);
+  // Every step of the reference is a Neuron call with T = 1, so the reset between steps is the state
+  // hand-over voltage * (1 - spike) (leaky_integrator.py persistent_state), i.e. the spike criterion.
+  const int k_spike = int_threshold_ge_scaled((float)threshold, sc.w);
+  const int k_reset = k_spike;
+  const int C = (int)neurons, threads = (C + 31) / 32 * 32;
+  const size_t smem = rec_fwd_smem(C);
+  cudaStream_t st = (cudaStream_t)stream;
+#define SB_GO(G)                                                                                             \
+  {                                                                                                          \
+    typename CubaFwd<false, true, G>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate,        \
+                                               final_c, final_v, final_s, k_reset, k_spike, spike_scale, sc}; \
+    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_fwd_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                 (int)smem));                                                                \
+    cuba_recurrent_fwd_kernel<G><<<(unsigned)batch, threads, smem, st>>>(p, rg, z, rec_t, voltage, spike, C); \
+  }
+  if (graded) SB_GO(true) else SB_GO(false)
+#undef SB_GO
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const float* rec, float* grad_z,
+                          int64_t batch, int64_t neurons, int64_t T, float threshold, float tau_rho,
+                          float scale_rho, int graded, void* stream) {
+  SB_REQUIRE(batch >= 0 && neurons >= 0 && T >= 0 && T <= INT_MAX, "negative or oversized extent");
+  if (batch == 0 || neurons == 0 || T == 0) return SB_OK;
+  SB_REQUIRE(neurons <= 1024, "the recurrent kernel holds one neuron per thread: at most 1024 neurons (got %lld)",
+             (long long)neurons);
+  SB_REQUIRE(batch <= INT_MAX, "batch too large");
+  SB_REQUIRE(grad_spike && voltage && rec && grad_z, "null pointer");
+  const RowGeom rg{batch * neurons, neurons, 1, (int)T};
+  const Surrogate sg = make_surrogate(tau_rho, scale_rho, graded != 0);
+  const int C = (int)neurons, threads = (C + 31) / 32 * 32;
+  const size_t smem = rec_bwd_smem(C);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (graded) {
+    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    cuba_recurrent_bwd_kernel<true><<<(unsigned)batch, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage,
+                                                                             rec, grad_z, C);
+  } else {
+    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    cuba_recurrent_bwd_kernel<false><<<(unsigned)batch, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage,
+                                                                              rec, grad_z, C);
+  }
+  SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
 

@@ -52,6 +52,9 @@ SIGNATURES = {
                             c_double, c_int, c_int, c_float, c_int, _P, _P, _I64, c_float, _P]),
     'sb_cuba_bwd': (c_int, [_P, _P, _P, c_float, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _G,
                             c_float, c_float, c_int, c_int, _P]),
+    'sb_cuba_recurrent_fwd': (c_int, [_P, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P,
+                                      _I64, _I64, _I64, c_double, c_int, c_int, c_float, _P]),
+    'sb_cuba_recurrent_bwd': (c_int, [_P, _P, _P, _P, _I64, _I64, _I64, c_float, c_float, c_float, c_int, _P]),
     'sb_alif_fwd': (c_int, [_P, _P, _I64, _P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _P,
                             _P, _P, _P, _P, _P, _P, _P, _P, _P, _G,
                             c_int, c_int, c_int, c_int, c_int, c_float, _P]),

@@ -477,6 +477,39 @@ def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, s
     return gx, None, None
 
 
+def cuba_recurrent_fwd(z, rec, cdecay, vdecay, cstate, vstate, threshold, w_scale, graded=False, spike_scale=1.0):
+    """Dense recurrent CUBA layer over ``z`` ``[batch, neurons, time]`` with the (quantised) recurrent
+    matrix ``rec`` ``[neurons, neurons]``: one launch for the whole walk over time.  Returns dict with
+    spike/voltage series and final_c/final_v/final_s."""
+    N.require_cuda(z, rec)
+    if z.dim() != 3 or rec.shape != (z.shape[1], z.shape[1]):
+        raise ValueError(f'recurrent layer needs [batch, neurons, time] input and a square matrix, got '
+                         f'{tuple(z.shape)} and {tuple(rec.shape)}')
+    z = _c(z)
+    rec_t = _c(rec.detach().to(torch.float32).t())
+    cd, vd = _param(cdecay, z), _param(vdecay, z)
+    cs, vs = row_state(cstate, z), row_state(vstate, z)
+    vol, spk = torch.empty_like(z), torch.empty_like(z)
+    fc, fv, fs = _vec(z), _vec(z), _vec(z)
+    B, C, T = z.shape
+    N.call('sb_cuba_recurrent_fwd', z, N.ptr(z), N.ptr(rec_t), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(),
+           N.ptr(cs), N.ptr(vs), N.ptr(vol), N.ptr(spk), N.ptr(fc), N.ptr(fv), N.ptr(fs), B, C, T,
+           float(threshold), int(w_scale), int(bool(graded)), float(spike_scale), N.stream_of(z))
+    return dict(voltage=vol, spike=spk, final_c=fc, final_v=fv, final_s=fs)
+
+
+def cuba_recurrent_bwd(grad_spike, voltage, rec, threshold, tau_rho, scale_rho, graded=False):
+    """Gradient of ``cuba_recurrent_fwd`` with respect to ``z``."""
+    N.require_cuda(grad_spike, voltage, rec)
+    grad_spike, voltage = _c(grad_spike), _c(voltage)
+    rec = _c(rec.detach().to(torch.float32))
+    gz = torch.empty_like(voltage)
+    B, C, T = voltage.shape
+    N.call('sb_cuba_recurrent_bwd', voltage, N.ptr(grad_spike), N.ptr(voltage), N.ptr(rec), N.ptr(gz), B, C, T,
+           f32(threshold), f32(tau_rho), f32(scale_rho), int(bool(graded)), N.stream_of(voltage))
+    return gz
+
+
 def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0, w_scale,
              dynamics_mode, graded=False, spike_scale=1.0):
     N.require_cuda(x)

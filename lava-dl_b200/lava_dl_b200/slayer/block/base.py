@@ -155,3 +155,62 @@ class AbstractFlatten(torch.nn.Module):
             self.shape = [int(np.prod(x.shape[1:-1])), 1, 1]
         flat = x.reshape((x.shape[0], -1, x.shape[-1]))
         return (flat, None) if self.count_log is True else flat
+
+
+class AbstractRecurrent(torch.nn.Module):
+    """Dense recurrent block (``block/base.py:1367-1488`` of the reference):
+    ``s[t] = neuron(W x[t] + R s[t-1])``, then the one-step delay and the optional
+    axonal delay.  The neuron always keeps its state between calls.
+
+    Parameters
+    ----------
+    neuron_params : dict
+    in_neurons, out_neurons : int
+    weight_scale, weight_norm, pre_hook_fx : options of both synapses
+    delay : bool
+        add a learnable axonal delay.
+    delay_shift : bool
+        apply the one-step inter-layer delay.
+    requires_grad : bool
+        kept for signature compatibility.
+    count_log : bool
+    """
+
+    def __init__(self, neuron_params, in_neurons, out_neurons, weight_scale=1, weight_norm=False,
+                 pre_hook_fx=None, delay=False, delay_shift=True, requires_grad=True, count_log=False):
+        super().__init__()
+        self.neuron_params = dict(neuron_params, persistent_state=True)
+        self.synapse_params = dict(in_neurons=in_neurons, out_neurons=out_neurons, weight_scale=weight_scale,
+                                   weight_norm=weight_norm, pre_hook_fx=pre_hook_fx)
+        self.recurrent_params = dict(self.synapse_params, in_neurons=out_neurons)
+        self.num_neurons = out_neurons
+        self.requires_grad = requires_grad
+        self.count_log = count_log
+        self.neuron = None
+        self.input_synapse = None
+        self.recurrent_synapse = None
+        self.delay = None
+        self.bias = None
+        self.persistent_state = True
+        self.delay_shift = delay_shift
+
+    def forward(self, x):
+        """``NCT`` input -> spikes (and event rate when ``count_log``)."""
+        from ..utils import recurrent
+        z = self.input_synapse(x)
+        if self.bias is not None:
+            z = z + self.bias
+        # the spike fed back at t = 0 is always zero: the reference stores a zero tensor as its
+        # spike state (block/base.py:1471-1478), only the neuron state survives between calls
+        x = recurrent.custom_recurrent(z, self.neuron, self.recurrent_synapse)
+        if self.delay_shift is True:
+            x = delay(x, 1)
+        if self.delay is not None:
+            x = self.delay(x)
+        if self.count_log is True:
+            return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    @property
+    def shape(self):
+        return self.neuron.shape

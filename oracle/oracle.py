@@ -331,6 +331,46 @@ def cuba(x, threshold, current_decay, voltage_decay, scale=64, cstate=0., vstate
     return out
 
 
+def cuba_recurrent(z, rec, threshold, current_decay, voltage_decay, scale=64, cstate=0., vstate=0., grad_spike=None,
+                   tau_grad=1, scale_grad=1, graded=False):
+    """utils/recurrent.py:45-112: per step, feedback = s[t-1] R^T, one CUBA neuron call
+    with T = 1 whose state persists (neuron/cuba.py:396-440), and for the gradient the
+    reverse walk in which only R couples the steps.  z [B, C, T], rec [C, C]."""
+    z = np.asarray(z, dtype=np.float32)
+    rec = np.asarray(rec, dtype=np.float32)
+    B, C, T = z.shape
+    spike = np.zeros_like(z)
+    voltage = np.zeros_like(z)
+    cs = np.broadcast_to(np.asarray(cstate, dtype=np.float32), (B, C)).copy()
+    vs = np.broadcast_to(np.asarray(vstate, dtype=np.float32), (B, C)).copy()
+    s = np.zeros((B, C), dtype=np.float32)
+    for t in range(T):
+        dend = (z[..., t] + s @ rec.T).astype(np.float32)
+        r = cuba(dend[..., None], threshold, current_decay, voltage_decay, scale, cs, vs, graded=graded)
+        s = r['spike'][..., 0]
+        cs = r['current'][..., 0]
+        vs = r['voltage'][..., 0] * (1 - (s > 0))   # leaky_integrator.py persistent_state
+        spike[..., t], voltage[..., t] = s, r['voltage'][..., 0]
+    out = dict(spike=spike, voltage=voltage, final_c=cs, final_v=vs)
+    if grad_spike is not None:
+        w_scale, s_scale = scale, scale * 64
+        thr = int(threshold * w_scale) / w_scale
+        eps = 0.01 / s_scale
+        tau_rho, scale_rho = tau_grad * thr * 100, scale_grad * 0.1
+        g = np.asarray(grad_spike, dtype=np.float32)
+        grad_z = np.zeros_like(z)
+        carry = np.zeros((B, C), dtype=np.float32)
+        for t in range(T - 1, -1, -1):
+            gs = (g[..., t] + carry).astype(np.float32)
+            gd = spike_bwd(voltage[..., t:t + 1], thr + eps, gs[..., None], tau_rho, scale_rho, graded)[..., 0]
+            grad_z[..., t] = gd
+            carry = (gd @ rec).astype(np.float32)
+        go = grad_z[..., 1:].transpose(1, 0, 2).reshape(C, -1)
+        si = spike[..., :-1].transpose(0, 2, 1).reshape(-1, C)
+        out.update(grad_z=grad_z, grad_rec=(go @ si).astype(np.float32))
+    return out
+
+
 def alif(x, threshold, threshold_step, current_decay, voltage_decay, threshold_decay, refractory_decay, scale=64,
          cstate=0., vstate=0., th_state=None, ref_state=0., grad_spike=None, tau_grad=1, scale_grad=1,
          graded=False):

@@ -478,6 +478,36 @@ def main():
          grad_weight2=snet[2].synapse.weight.grad, **acts)
     print('sigma-delta network event counts per layer:', [int((acts[f'act{i}'] != 0).sum()) for i in range(3)])
 
+    # ------------------------------------------------------------------
+    # dense recurrent CUBA block (block/base.py:1460-1488 over utils/recurrent.py:45-112):
+    # two forward calls (the neuron state persists between them) and one backward
+    # ------------------------------------------------------------------
+    torch.manual_seed(5)
+    rec = slayer.block.cuba.Recurrent(dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03,
+                                           requires_grad=True), 24, 40, weight_scale=3, delay_shift=True)
+    xr = (rand(3, 24, 50) < 0.2).float()
+    xin = xr.clone().requires_grad_(True)
+    y1 = rec(xin)
+    g_r = randn(*y1.shape)
+    (y1 * g_r).sum().backward()
+    with torch.no_grad():
+        y2 = rec(xr)
+    save('block_cuba_recurrent', x=xr, weight_in=rec.input_synapse.weight.data,
+         weight_rec=rec.recurrent_synapse.weight.data, out1=y1, grad_out=g_r, grad_x=xin.grad,
+         grad_weight_in=rec.input_synapse.weight.grad, grad_weight_rec=rec.recurrent_synapse.weight.grad,
+         grad_current_decay=rec.neuron.current_decay.grad, grad_voltage_decay=rec.neuron.voltage_decay.grad, out2=y2)
+    torch.manual_seed(6)
+    rec = slayer.block.cuba.Recurrent(dict(threshold=1.25, current_decay=[0.2, 0.4], voltage_decay=[0.02, 0.1],
+                                           shared_param=False, graded_spike=True), 17, 33, weight_scale=3,
+                                      delay_shift=False)
+    xg = (rand(2, 17, 37) < 0.25).float() * rand(2, 17, 37) * 2
+    with torch.no_grad():
+        yg = rec(xg)
+    save('block_cuba_recurrent_graded', x=xg, weight_in=rec.input_synapse.weight.data,
+         weight_rec=rec.recurrent_synapse.weight.data, current_decay=rec.neuron.current_decay.data,
+         voltage_decay=rec.neuron.voltage_decay.data, out=yg)
+    print('recurrent block spike counts:', int(y1.sum()), int(y2.sum()), int((yg != 0).sum()))
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

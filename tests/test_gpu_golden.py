@@ -446,3 +446,44 @@ def test_sigma_delta_block_network(cuda, slayer):
         for i, layer in enumerate(net):
             y = layer(y)
             assert_exact(y, g[f'act{i}'], f'layer {i} events, one-pass kernels')
+
+
+def test_recurrent_block(cuda, slayer):
+    """Dense recurrent CUBA block against the reference's block (per-step Python loop):
+    spikes bit-exact for two consecutive calls (the neuron state persists), gradients to 1e-5."""
+    g = load_golden('block_cuba_recurrent')
+    p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03, requires_grad=True)
+    blk = slayer.block.cuba.Recurrent(p, 24, 40, weight_scale=3, delay_shift=True).to(cuda)
+    blk.input_synapse.weight.data = T(g['weight_in'], cuda)
+    blk.recurrent_synapse.weight.data = T(g['weight_rec'], cuda)
+    x = T(g['x'], cuda, True)
+    y = blk(x)
+    assert_exact(y, g['out1'], 'recurrent block spikes')
+    (y * T(g['grad_out'], cuda)).sum().backward()
+    assert_close(x.grad, g['grad_x'], 'grad_x')
+    assert_close(blk.input_synapse.weight.grad, g['grad_weight_in'], 'grad input weight')
+    assert_close(blk.recurrent_synapse.weight.grad, g['grad_weight_rec'], 'grad recurrent weight')
+    for k in ('current_decay', 'voltage_decay'):     # zero in the reference, zero or absent here
+        grad = getattr(blk.neuron, k).grad
+        assert grad is None or not grad.any()
+        assert not g[f'grad_{k}'].any()
+    with torch.no_grad():
+        assert_exact(blk(T(g['x'], cuda)), g['out2'], 'second call, persistent neuron state')
+
+
+def test_recurrent_block_graded(cuda, slayer):
+    g = load_golden('block_cuba_recurrent_graded')
+    p = dict(threshold=1.25, current_decay=[0.2, 0.4], voltage_decay=[0.02, 0.1], shared_param=False,
+             graded_spike=True)
+    blk = slayer.block.cuba.Recurrent(p, 17, 33, weight_scale=3, delay_shift=False).to(cuda)
+    blk.input_synapse.weight.data = T(g['weight_in'], cuda)
+    blk.recurrent_synapse.weight.data = T(g['weight_rec'], cuda)
+    with torch.no_grad():
+        blk(T(g['x'], cuda))                       # binds shapes, samples per-neuron decays
+        blk.neuron.current_decay.data = T(g['current_decay'], cuda).reshape(blk.neuron.current_decay.shape)
+        blk.neuron.voltage_decay.data = T(g['voltage_decay'], cuda).reshape(blk.neuron.voltage_decay.shape)
+        blk.neuron.current_state = torch.zeros(1, device=cuda)
+        blk.neuron.voltage_state = torch.zeros(1, device=cuda)
+        y = blk(T(g['x'], cuda))
+    assert_exact(y != 0, g['out'] != 0, 'graded spike pattern')
+    assert_close(y, g['out'], 'graded spike values')

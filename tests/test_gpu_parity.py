@@ -610,3 +610,53 @@ def test_empty_inputs(cuda, ops):
 def test_device_status_clean(cuda):
     from lava_dl_b200 import _native
     assert _native.device_status() == 0
+
+
+def _recurrent_scale(voltage, grad_spike, rec, thr, graded):
+    """Magnitude of the terms that make up grad_z of the recurrent walk: the same
+    reverse recursion on absolute values."""
+    B, C, T = voltage.shape
+    out = np.zeros_like(voltage, dtype=np.float64)
+    carry = np.zeros((B, C))
+    sg = np.abs(O.spike_bwd(voltage, thr, np.ones_like(voltage), 125.0, 0.1, graded)).astype(np.float64)
+    for t in range(T - 1, -1, -1):
+        out[..., t] = sg[..., t] * (np.abs(grad_spike[..., t]) + carry)
+        carry = out[..., t] @ np.abs(rec).astype(np.float64)
+    return out
+
+
+@pytest.mark.parametrize('shape', [(1, 1, 1), (2, 3, 2), (3, 40, 50), (2, 33, 36), (5, 257, 67), (2, 1024, 33),
+                                   (4, 512, 100), (1, 100, 300)])
+@pytest.mark.parametrize('graded', [False, True])
+@pytest.mark.parametrize('per_neuron', [False, True])
+def test_cuba_recurrent(shape, graded, per_neuron, cuda, ops):
+    """One launch for s[t] = CUBA(z[t] + R s[t-1]) and its gradient, against the oracle's
+    step-by-step walk (one neuron call per time step, state handed over)."""
+    B, C, T = shape
+    rng = rng_for('cuba_recurrent', shape, graded, per_neuron)
+    z = rng.normal(0.25, 0.9, size=shape).astype(np.float32)
+    # recurrent weights on the 8-bit grid (multiples of 2/64), mostly inhibitory so activity stays bounded
+    rec = (np.round(rng.normal(-0.02, 0.5 / np.sqrt(C), size=(C, C)) * 32) / 32).astype(np.float32)
+    n = C if per_neuron else 1
+    cd = np.round(rng.uniform(400, 1600, size=n)).astype(np.float32)
+    vd = np.round(rng.uniform(60, 600, size=n)).astype(np.float32)
+    cs = (np.round(rng.normal(0, 0.5, size=(B, C)) * W) / W).astype(np.float32)
+    vs = (np.round(rng.uniform(-0.5, 1.0, size=(B, C)) * W) / W).astype(np.float32)
+    gs = rng.normal(size=shape).astype(np.float32)
+    thr = 1.25 + 0.01 / W
+    want = O.cuba_recurrent(z, rec, 1.25, cd, vd, cstate=cs, vstate=vs, grad_spike=gs, graded=graded)
+    r = ops.cuba_recurrent_fwd(dev(z, cuda), dev(rec, cuda), dev(cd, cuda), dev(vd, cuda), dev(cs, cuda),
+                               dev(vs, cuda), thr, W, graded=graded)
+    if graded:
+        # graded spike values times weights are inexact in fp32: the order of the feedback sum shows
+        assert_exact(r['spike'] != 0, want['spike'] != 0, 'spike pattern')
+        assert_close(r['spike'], want['spike'], 'graded spike values')
+        assert_close(r['voltage'], want['voltage'], 'voltage', scale=1.0)
+    else:
+        assert_exact(r['spike'], want['spike'], 'spikes')
+        assert_quantised_equal(r['voltage'], want['voltage'], W, 'voltage')
+        assert_quantised_equal(r['final_c'], want['final_c'], W, 'final current')
+        fv = r['final_v'] * (1 - (r['final_s'] > 0).float())
+        assert_quantised_equal(fv, want['final_v'], W, 'final voltage after hand-over')
+    gz = ops.cuba_recurrent_bwd(dev(gs, cuda), dev(want['voltage'], cuda), dev(rec, cuda), thr, 125.0, 0.1, graded)
+    assert_close(gz, want['grad_z'], 'grad_z', scale=_recurrent_scale(want['voltage'], gs, rec, thr, graded))

@@ -158,3 +158,22 @@ def test_delay_fusable_bound():
     assert slayer.axon.Delay(max_delay=None).fusable_steps is None
     assert slayer.axon.Delay(max_delay=62).fusable_steps == 62
     assert slayer.axon.Delay(sampling_time=2, max_delay=100).fusable_steps == 50
+
+
+def test_recurrent_block_host_side():
+    """Construction mirrors block.cuba.Recurrent of the reference; there is no CPU path, other neuron
+    families are refused, and the input must be [batch, neurons, time]."""
+    import lava_dl_b200.slayer as slayer
+    p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03)
+    blk = slayer.block.cuba.Recurrent(p, 6, 8, weight_scale=2, delay=True)
+    assert blk.neuron.persistent_state is True and 'persistent_state' not in p
+    assert blk.recurrent_synapse.weight.shape[:2] == (8, 8) and blk.input_synapse.weight.shape[:2] == (8, 6)
+    assert blk.input_synapse.pre_hook_fx == blk.neuron.quantize_8bit
+    assert blk.delay is not None
+    with pytest.raises(RuntimeError, match='no CPU fallback'):
+        blk(torch.zeros(2, 6, 5))
+    alif = slayer.neuron.alif.Neuron(1.0, 0.1, 0.3, 0.1, 0.9, 0.9, persistent_state=True)
+    with pytest.raises(NotImplementedError):
+        slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 5), alif, blk.recurrent_synapse)
+    with pytest.raises(ValueError):
+        slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 1, 1, 5), blk.neuron, blk.recurrent_synapse)
