@@ -152,6 +152,9 @@ WORKLOADS['cfg4_train'] = Workload('cfg4_train', (32, 2, 128, 128, 300), 0)
 # dense recurrent CUBA block (block.cuba.Recurrent, 512 -> 512 neurons): one launch per direction for the walk over time
 WORKLOADS['recurrent_fwd'] = Workload('recurrent_fwd', (128, 512, 300), 0)
 WORKLOADS['recurrent_train'] = Workload('recurrent_train', (128, 512, 300), 0)
+# the same block walked the way the reference does it (utils/recurrent.py:17-32): one matmul and one
+# neuron call with a single time step per step, here on this library's own neuron kernel
+WORKLOADS['recurrent_fwd_stepwise'] = Workload('recurrent_fwd_stepwise', (128, 512, 300), 0)
 NETWORKS = ('cfg4', 'recurrent')   # chains of kernels: no single roofline, no CPU port
 CFG4_NEURONS = 2048 + 16384 + 4096 + 8192 + 2048 + 512 + 11
 
@@ -217,6 +220,20 @@ def build_step(name, shape, device, seed):
         gen = torch.Generator(device=device).manual_seed(seed)
         x = (torch.rand(shape, device=device, generator=gen) < 0.05).float()
         params = [q for q in blk.parameters() if q.requires_grad]
+
+        def stepwise():
+            with torch.no_grad():
+                z = blk.input_synapse(x)
+                rec_t = blk.neuron.quantize_8bit(blk.recurrent_synapse.weight.reshape(shape[1], shape[1])).t()
+                out = torch.zeros_like(z)
+                spike = torch.zeros(z.shape[:-1] + (1,), device=device)
+                for t in range(z.shape[-1]):
+                    feedback = torch.matmul(spike[..., 0], rec_t)
+                    spike = blk.neuron((z[..., t] + feedback).unsqueeze(-1))
+                    out[..., t:t + 1] = spike
+                return out
+        if name == 'recurrent_fwd_stepwise':
+            return stepwise, shape[-1], (blk, x)
 
         def step():
             if not train:

@@ -331,19 +331,26 @@ int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const f
   const RowGeom rg{batch * neurons, neurons, 1, (int)T};
   const Surrogate sg = make_surrogate(tau_rho, scale_rho, graded != 0);
   const int C = (int)neurons, threads = (C + 31) / 32 * 32;
-  const size_t smem = rec_bwd_smem(C);
+  // Two samples per CTA halve the L2 traffic of R; worth it once the batch fills the GPU twice over or
+  // anyway leaves SMs idle in a second wave, and only while both samples' tiles fit in shared memory.
+#ifdef SB_REC_BWD_S
+  const int S = SB_REC_BWD_S;
+#else
+  const int S = (batch >= 64 && rec_bwd_smem(C, 2) <= 200 * 1024) ? 2 : 1;
+#endif
+  const size_t smem = rec_bwd_smem(C, S);
+  const unsigned grid = (unsigned)((batch + S - 1) / S);
   cudaStream_t st = (cudaStream_t)stream;
-  if (graded) {
-    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    cuba_recurrent_bwd_kernel<true><<<(unsigned)batch, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage,
-                                                                             rec, grad_z, C);
-  } else {
-    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    cuba_recurrent_bwd_kernel<false><<<(unsigned)batch, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage,
-                                                                              rec, grad_z, C);
+#define SB_GO(G, SS)                                                                                        \
+  {                                                                                                         \
+    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<G, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem));                                                               \
+    cuba_recurrent_bwd_kernel<G, SS><<<grid, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage, rec, \
+                                                                  grad_z, C, (int)batch);                   \
   }
+  if (S == 2) { if (graded) SB_GO(true, 2) else SB_GO(false, 2) }
+  else        { if (graded) SB_GO(true, 1) else SB_GO(false, 1) }
+#undef SB_GO
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -71,7 +71,16 @@ cuba_recurrent_fwd_kernel(typename CubaFwd<false, true, GRADED>::Params p, RowGe
       if (valid) {
         const unsigned short* li = sidx + cur * C;
         const float* lv = sval + cur * C;
-        for (int k = 0; k < ns; ++k)
+        // eight columns in flight per round (the loads are L2 latency bound), summed in list order
+        int k = 0;
+        for (; k + 8 <= ns; k += 8) {
+          float r[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) r[u] = __ldg(rec_t + (size_t)li[k + u] * C + i);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) fb = __fmaf_rn(GRADED ? lv[k + u] : 1.f, r[u], fb);
+        }
+        for (; k < ns; ++k)
           fb = __fmaf_rn(GRADED ? lv[k] : 1.f, __ldg(rec_t + (size_t)li[k] * C + i), fb);
       }
       float a[1], b[2];
@@ -112,54 +121,80 @@ cuba_recurrent_fwd_kernel(typename CubaFwd<false, true, GRADED>::Params p, RowGe
 // with T = 1 whose incoming state carries no gradient, so the time recursion
 // runs through R only:
 //   g_d[t] = surrogate(v[t]) * (grad_spike[t] + R^T g_d[t + 1]),  grad_z[t] = g_d[t].
-// rec [C, C] = R (row i holds the weights into neuron i).  Shared memory:
-// 2 tiles [C][kRecPitch], then C floats for g_d of the current step.
-template <bool GRADED>
+// rec [C, C] = R (row i holds the weights into neuron i).  Shared memory per
+// sample of the CTA: 2 tiles [C][kRecPitch] and C floats for g_d of the current step.
+template <bool GRADED, int S>
 __global__ void __launch_bounds__(1024, 1)
 cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __restrict__ grad_spike,
                           const float* __restrict__ voltage, const float* __restrict__ rec,
-                          float* __restrict__ grad_z, int C) {
+                          float* __restrict__ grad_z, int C, int batch) {
+  // S samples per CTA share every load of R (the walk is bound by the L2 traffic of R).
   extern __shared__ __align__(16) unsigned char rec_smem[];
-  float* gt = reinterpret_cast<float*>(rec_smem);   // grad_spike tile, overwritten by grad_z
-  float* vt = gt + (size_t)C * kRecPitch;
-  float* gd = vt + (size_t)C * kRecPitch;           // [C]
+  const size_t tile_floats = (size_t)C * kRecPitch;
+  float* gt = reinterpret_cast<float*>(rec_smem);   // [S] grad_spike tiles, overwritten by grad_z
+  float* vt = gt + S * tile_floats;                 // [S] voltage tiles
+  float* gd = vt + S * tile_floats;                 // [S][C]
 
   const int j = threadIdx.x;
   const bool valid = j < C;
-  const int64_t row0 = (int64_t)blockIdx.x * C;
+  const int b0 = blockIdx.x * S;
+  const int ns = min(S, batch - b0);
+  const int64_t row0 = (int64_t)b0 * C;
   const int T = g.T;
-  float carry = 0.f;
+  float carry[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) carry[s] = 0.f;
   const int ntile = (T + kRecTile - 1) / kRecTile;
   for (int tile = ntile - 1; tile >= 0; --tile) {
     const int t0 = tile * kRecTile;
-    rec_tile_io<true>(gt, nullptr, grad_spike, row0, C, T, t0);
-    rec_tile_io<true>(vt, nullptr, voltage, row0, C, T, t0);
+    for (int s = 0; s < ns; ++s) {
+      rec_tile_io<true>(gt + s * tile_floats, nullptr, grad_spike, row0 + (int64_t)s * C, C, T, t0);
+      rec_tile_io<true>(vt + s * tile_floats, nullptr, voltage, row0 + (int64_t)s * C, C, T, t0);
+    }
     __syncthreads();
     const int nstep = min(kRecTile, T - t0);
     for (int tt = nstep - 1; tt >= 0; --tt) {
-      float d = 0.f;
       if (valid) {
-        const float gs = __fadd_rn(gt[j * kRecPitch + tt], carry);
-        d = __fmul_rn(surrogate<GRADED>(sg, vt[j * kRecPitch + tt], thr), gs);
-        gt[j * kRecPitch + tt] = d;
-        gd[j] = d;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          float d = 0.f;
+          if (s < ns) {
+            float* gts = gt + s * tile_floats;
+            const float gs = __fadd_rn(gts[j * kRecPitch + tt], carry[s]);
+            d = __fmul_rn(surrogate<GRADED>(sg, vt[s * tile_floats + j * kRecPitch + tt], thr), gs);
+            gts[j * kRecPitch + tt] = d;
+          }
+          gd[s * C + j] = d;
+        }
       }
       __syncthreads();
       if (valid && (t0 + tt) > 0) {
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        float acc[S][4];
+#pragma unroll
+        for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
         int i = 0;
         for (; i + 4 <= C; i += 4) {
-          s0 = __fmaf_rn(gd[i], __ldg(rec + (size_t)i * C + j), s0);
-          s1 = __fmaf_rn(gd[i + 1], __ldg(rec + (size_t)(i + 1) * C + j), s1);
-          s2 = __fmaf_rn(gd[i + 2], __ldg(rec + (size_t)(i + 2) * C + j), s2);
-          s3 = __fmaf_rn(gd[i + 3], __ldg(rec + (size_t)(i + 3) * C + j), s3);
+          float r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) r[u] = __ldg(rec + (size_t)(i + u) * C + j);
+#pragma unroll
+          for (int s = 0; s < S; ++s)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[s][u] = __fmaf_rn(gd[s * C + i + u], r[u], acc[s][u]);
         }
-        for (; i < C; ++i) s0 = __fmaf_rn(gd[i], __ldg(rec + (size_t)i * C + j), s0);
-        carry = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+        for (; i < C; ++i) {
+          const float r = __ldg(rec + (size_t)i * C + j);
+#pragma unroll
+          for (int s = 0; s < S; ++s) acc[s][0] = __fmaf_rn(gd[s * C + i], r, acc[s][0]);
+        }
+#pragma unroll
+        for (int s = 0; s < S; ++s)
+          carry[s] = __fadd_rn(__fadd_rn(acc[s][0], acc[s][1]), __fadd_rn(acc[s][2], acc[s][3]));
       }
       __syncthreads();
     }
-    rec_tile_io<false>(gt, grad_z, nullptr, row0, C, T, t0);
+    for (int s = 0; s < ns; ++s)
+      rec_tile_io<false>(gt + s * tile_floats, grad_z, nullptr, row0 + (int64_t)s * C, C, T, t0);
     __syncthreads();
   }
 }
@@ -167,6 +202,6 @@ cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __res
 inline size_t rec_fwd_smem(int C) {
   return 2 * (size_t)C * kRecPitch * 4 + 2 * (size_t)C * 4 + 66 * 4 + 2 * (size_t)C * 2;
 }
-inline size_t rec_bwd_smem(int C) { return 2 * (size_t)C * kRecPitch * 4 + (size_t)C * 4; }
+inline size_t rec_bwd_smem(int C, int S) { return (size_t)S * (2 * (size_t)C * kRecPitch * 4 + (size_t)C * 4); }
 
 }  // namespace sb

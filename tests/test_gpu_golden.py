@@ -457,9 +457,11 @@ def test_recurrent_block(cuda, slayer):
     blk.input_synapse.weight.data = T(g['weight_in'], cuda)
     blk.recurrent_synapse.weight.data = T(g['weight_rec'], cuda)
     x = T(g['x'], cuda, True)
-    y = blk(x)
-    assert_exact(y, g['out1'], 'recurrent block spikes')
-    (y * T(g['grad_out'], cuda)).sum().backward()
+    # the dense synapses are library convolutions: keep them in fp32 so that 1e-5 applies to the whole block
+    with torch.backends.cudnn.flags(allow_tf32=False):
+        y = blk(x)
+        assert_exact(y, g['out1'], 'recurrent block spikes')
+        (y * T(g['grad_out'], cuda)).sum().backward()
     assert_close(x.grad, g['grad_x'], 'grad_x')
     assert_close(blk.input_synapse.weight.grad, g['grad_weight_in'], 'grad input weight')
     assert_close(blk.recurrent_synapse.weight.grad, g['grad_weight_rec'], 'grad recurrent weight')
@@ -475,15 +477,15 @@ def test_recurrent_block_graded(cuda, slayer):
     g = load_golden('block_cuba_recurrent_graded')
     p = dict(threshold=1.25, current_decay=[0.2, 0.4], voltage_decay=[0.02, 0.1], shared_param=False,
              graded_spike=True)
-    blk = slayer.block.cuba.Recurrent(p, 17, 33, weight_scale=3, delay_shift=False).to(cuda)
+    blk = slayer.block.cuba.Recurrent(p, 17, 33, weight_scale=2, delay_shift=False).to(cuda)
     blk.input_synapse.weight.data = T(g['weight_in'], cuda)
     blk.recurrent_synapse.weight.data = T(g['weight_rec'], cuda)
-    with torch.no_grad():
+    # graded (float) inputs through the library convolution of the dense synapse: fp32, not TF32
+    with torch.no_grad(), torch.backends.cudnn.flags(allow_tf32=False):
         blk(T(g['x'], cuda))                       # binds shapes, samples per-neuron decays
         blk.neuron.current_decay.data = T(g['current_decay'], cuda).reshape(blk.neuron.current_decay.shape)
         blk.neuron.voltage_decay.data = T(g['voltage_decay'], cuda).reshape(blk.neuron.voltage_decay.shape)
         blk.neuron.current_state = torch.zeros(1, device=cuda)
         blk.neuron.voltage_state = torch.zeros(1, device=cuda)
         y = blk(T(g['x'], cuda))
-    assert_exact(y != 0, g['out'] != 0, 'graded spike pattern')
-    assert_close(y, g['out'], 'graded spike values')
+    assert_exact(y, g['out'], 'graded spikes (every product and sum of this case is exact in fp32)')
