@@ -331,12 +331,12 @@ int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const f
   const RowGeom rg{batch * neurons, neurons, 1, (int)T};
   const Surrogate sg = make_surrogate(tau_rho, scale_rho, graded != 0);
   const int C = (int)neurons, threads = (C + 31) / 32 * 32;
-  // Two samples per CTA halve the L2 traffic of R; worth it once the batch fills the GPU twice over or
-  // anyway leaves SMs idle in a second wave, and only while both samples' tiles fit in shared memory.
+  // Two samples per CTA share every load of R.  One CTA's walk gets about 1.2x slower that way (measured at
+  // batch 128, 512 neurons: 5.5 -> 6.6 ms), so it pays only when it saves a wave of CTAs: batch > SM count.
 #ifdef SB_REC_BWD_S
   const int S = SB_REC_BWD_S;
 #else
-  const int S = (batch >= 64 && rec_bwd_smem(C, 2) <= 200 * 1024) ? 2 : 1;
+  const int S = (batch > sm_count() && rec_bwd_smem(C, 2) <= 200 * 1024) ? 2 : 1;
 #endif
   const size_t smem = rec_bwd_smem(C, S);
   const unsigned grid = (unsigned)((batch + S - 1) / S);

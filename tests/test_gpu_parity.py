@@ -627,7 +627,7 @@ def _recurrent_scale(voltage, grad_spike, rec, thr, graded):
 
 @pytest.mark.parametrize('shape', [(1, 1, 1), (2, 3, 2), (3, 40, 50), (2, 33, 36), (5, 257, 67), (2, 1024, 33),
                                    (4, 512, 100), (1, 100, 300),
-                                   (65, 48, 20), (64, 130, 17)])   # batch >= 64: two samples per CTA in the backward
+                                   (151, 48, 20), (150, 130, 9)])   # more samples than SMs: two per CTA in the backward
 @pytest.mark.parametrize('graded', [False, True])
 @pytest.mark.parametrize('per_neuron', [False, True])
 def test_cuba_recurrent(shape, graded, per_neuron, cuda, ops):
