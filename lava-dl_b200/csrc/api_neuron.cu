@@ -341,15 +341,19 @@ int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const f
   const size_t smem = rec_bwd_smem(C, S);
   const unsigned grid = (unsigned)((batch + S - 1) / S);
   cudaStream_t st = (cudaStream_t)stream;
-#define SB_GO(G, SS)                                                                                        \
+  // 16-byte loads of R need whole column quads and an aligned matrix; partial sums are 16-byte stores too
+  const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(rec) & 15u) == 0);
+#define SB_GO(G, SS, V)                                                                                     \
   {                                                                                                         \
-    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<G, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)smem));                                                               \
-    cuba_recurrent_bwd_kernel<G, SS><<<grid, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage, rec, \
-                                                                  grad_z, C, (int)batch);                   \
+    SB_CUDA(cudaFuncSetAttribute(cuba_recurrent_bwd_kernel<G, SS, V>,                                       \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                  \
+    cuba_recurrent_bwd_kernel<G, SS, V><<<grid, threads, smem, st>>>(sg, threshold, rg, grad_spike, voltage, \
+                                                                     rec, grad_z, C, (int)batch);           \
   }
-  if (S == 2) { if (graded) SB_GO(true, 2) else SB_GO(false, 2) }
-  else        { if (graded) SB_GO(true, 1) else SB_GO(false, 1) }
+#define SB_GO2(G, SS) { if (vec) SB_GO(G, SS, true) else SB_GO(G, SS, false) }
+  if (S == 2) { if (graded) SB_GO2(true, 2) else SB_GO2(false, 2) }
+  else        { if (graded) SB_GO2(true, 1) else SB_GO2(false, 1) }
+#undef SB_GO2
 #undef SB_GO
   SB_CUDA(cudaGetLastError());
   return SB_OK;

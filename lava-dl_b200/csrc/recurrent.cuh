@@ -122,8 +122,9 @@ cuba_recurrent_fwd_kernel(typename CubaFwd<false, true, GRADED>::Params p, RowGe
 // runs through R only:
 //   g_d[t] = surrogate(v[t]) * (grad_spike[t] + R^T g_d[t + 1]),  grad_z[t] = g_d[t].
 // rec [C, C] = R (row i holds the weights into neuron i).  Shared memory per
-// sample of the CTA: 2 tiles [C][kRecPitch] and C floats for g_d of the current step.
-template <bool GRADED, int S>
+// sample of the CTA: 2 tiles [C][kRecPitch], C floats for g_d of the current step and
+// 4 x C partial sums.
+template <bool GRADED, int S, bool VEC>
 __global__ void __launch_bounds__(1024, 1)
 cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __restrict__ grad_spike,
                           const float* __restrict__ voltage, const float* __restrict__ rec,
@@ -134,6 +135,7 @@ cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __res
   float* gt = reinterpret_cast<float*>(rec_smem);   // [S] grad_spike tiles, overwritten by grad_z
   float* vt = gt + S * tile_floats;                 // [S] voltage tiles
   float* gd = vt + S * tile_floats;                 // [S][C]
+  float* part = gd + (size_t)S * C;                 // [S][4][C] partial sums of the vector path
 
   const int j = threadIdx.x;
   const bool valid = j < C;
@@ -168,7 +170,56 @@ cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __res
         }
       }
       __syncthreads();
-      if (valid && (t0 + tt) > 0) {
+      const bool more = (t0 + tt) > 0;
+      if (VEC) {
+        // C % 4 == 0: a thread owns four adjacent columns of R and every fourth row, so each load is
+        // 16 bytes (four times the bytes in flight of the scalar path); the four row groups meet in shared memory
+        if (valid && more) {
+          const int q = C >> 2, jq = j % q, ig = j / q;
+          float4 acc[S];
+#pragma unroll
+          for (int s = 0; s < S; ++s) acc[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4* base = reinterpret_cast<const float4*>(rec) + jq;
+          int i = ig;
+          for (; i + 12 < C; i += 16) {
+            float4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) r[u] = __ldg(base + (size_t)(i + 4 * u) * q);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int s = 0; s < S; ++s) {
+                const float gv = gd[s * C + i + 4 * u];
+                acc[s].x = __fmaf_rn(gv, r[u].x, acc[s].x);
+                acc[s].y = __fmaf_rn(gv, r[u].y, acc[s].y);
+                acc[s].z = __fmaf_rn(gv, r[u].z, acc[s].z);
+                acc[s].w = __fmaf_rn(gv, r[u].w, acc[s].w);
+              }
+          }
+          for (; i < C; i += 4) {
+            const float4 r = __ldg(base + (size_t)i * q);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+              const float gv = gd[s * C + i];
+              acc[s].x = __fmaf_rn(gv, r.x, acc[s].x);
+              acc[s].y = __fmaf_rn(gv, r.y, acc[s].y);
+              acc[s].z = __fmaf_rn(gv, r.z, acc[s].z);
+              acc[s].w = __fmaf_rn(gv, r.w, acc[s].w);
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < S; ++s)
+            *reinterpret_cast<float4*>(part + ((size_t)(s * 4 + ig) * C) + 4 * jq) = acc[s];
+        }
+        __syncthreads();
+        if (valid && more) {
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            const float* ps = part + (size_t)s * 4 * C + j;
+            carry[s] = __fadd_rn(__fadd_rn(ps[0], ps[C]), __fadd_rn(ps[2 * C], ps[3 * C]));
+          }
+        }
+      } else if (valid && more) {
         float acc[S][4];
 #pragma unroll
         for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
@@ -202,6 +253,8 @@ cuba_recurrent_bwd_kernel(Surrogate sg, float thr, RowGeom g, const float* __res
 inline size_t rec_fwd_smem(int C) {
   return 2 * (size_t)C * kRecPitch * 4 + 2 * (size_t)C * 4 + 66 * 4 + 2 * (size_t)C * 2;
 }
-inline size_t rec_bwd_smem(int C, int S) { return (size_t)S * (2 * (size_t)C * kRecPitch * 4 + (size_t)C * 4); }
+inline size_t rec_bwd_smem(int C, int S) {
+  return (size_t)S * (2 * (size_t)C * kRecPitch * 4 + (size_t)C * 4 + 4 * (size_t)C * 4);
+}
 
 }  // namespace sb
