@@ -36,7 +36,9 @@ def import_reference(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    if len(sys.argv) < 2:
+        sys.exit('usage: python tests/golden/make_golden.py /path/to/lava-dl')
+    root = sys.argv[1]
     out_dir = os.path.dirname(os.path.abspath(__file__))
     slayer = import_reference(root)
     import torch
