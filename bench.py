@@ -213,6 +213,7 @@ def build_step(name, shape, device, seed):
         return step, 20, (net, x)
     if name.startswith('recurrent'):
         import lava_dl_b200.slayer as slayer
+        from lava_dl_b200 import _dist
         train = name == 'recurrent_train'
         torch.manual_seed(seed)
         blk = slayer.block.cuba.Recurrent(dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03),
@@ -242,6 +243,7 @@ def build_step(name, shape, device, seed):
             for q in params:
                 q.grad = None
             blk(x).sum().backward()
+            _dist.allreduce_param_grads(params)
         return step, (2 if train else 1), (blk, x)
     if name.startswith('stream_'):
         from lava_dl_b200 import _native as N
