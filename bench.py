@@ -145,7 +145,7 @@ WORKLOADS = {
     'delay_fir_fwd': Workload('delay_fir_fwd', (128, 16384, 1000), 8, 'elements/s'),
     'delay_fir_bwd': Workload('delay_fir_bwd', (128, 16384, 1000), 8, 'elements/s'),
 }
-# full CUBA conv network of the last benchmark config (blocks = cuDNN synapse + fused neuron kernel +
+# full CUBA conv network of the last benchmark config (blocks = this library's synapse kernels + fused neuron kernel +
 # one-step delay); units = neuron-steps over all seven spiking layers (33291 neurons per sample)
 WORKLOADS['cfg4_fwd'] = Workload('cfg4_fwd', (32, 2, 128, 128, 300), 0)
 WORKLOADS['cfg4_train'] = Workload('cfg4_train', (32, 2, 128, 128, 300), 0)
@@ -157,11 +157,6 @@ WORKLOADS['recurrent_train'] = Workload('recurrent_train', (128, 512, 300), 0)
 WORKLOADS['recurrent_fwd_stepwise'] = Workload('recurrent_fwd_stepwise', (128, 512, 300), 0)
 NETWORKS = ('cfg4', 'recurrent')   # chains of kernels: no single roofline, no CPU port
 CFG4_NEURONS = 2048 + 16384 + 4096 + 8192 + 2048 + 512 + 11
-
-# plain streaming kernel at the read:write mixes of the kernels above (sb_probe_stream): the HBM
-# ceiling a kernel with that mix can be held against.  One unit = one element of one stream.
-for _r, _w in ((1, 1), (1, 2), (1, 3), (2, 1), (3, 1), (2, 4), (4, 2)):
-    WORKLOADS[f'stream_{_r}r{_w}w'] = Workload(f'stream_{_r}r{_w}w', (64, 8192, 2000), 4 * (_r + _w), 'elements/s')
 
 
 def build_step(name, shape, device, seed):
@@ -245,16 +240,6 @@ def build_step(name, shape, device, seed):
             blk(x).sum().backward()
             _dist.allreduce_param_grads(params)
         return step, (2 if train else 1), (blk, x)
-    if name.startswith('stream_'):
-        from lava_dl_b200 import _native as N
-        r, w = int(name[7]), int(name[9])
-        n = int(np.prod(shape))
-        src = torch.zeros(r * n, device=device)
-        dst = torch.empty(w * n, device=device)
-
-        def step():
-            N.call('sb_probe_stream', src, N.ptr(src), N.ptr(dst), n, r, w, N.stream_of(src))
-        return step, 1, (src, dst)
     if name == 'sigma_fwd':
         def step():
             return _ops.sigma_fwd(d['x'])
@@ -623,8 +608,8 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        if wl.name.startswith(('stream_',) + NETWORKS):
-            print(json.dumps({'impl': 'reference', 'unavailable': 'no CPU port of this workload (probe / full network)'}))
+        if wl.name.startswith(NETWORKS):
+            print(json.dumps({'impl': 'reference', 'unavailable': 'no CPU port of this workload (a network of kernels)'}))
             return
         cpu, sec = time_cpu(wl, max(1, args.steps), max(1, args.warmup))
         line = {
@@ -737,9 +722,9 @@ def main():
         line['roofline'] = None  # latency-bound walk over time plus two GEMMs
         line['config']['network'] = 'block.cuba.Recurrent(512, 512), spikes in at 5 %'
     if wl.name.startswith('cfg4'):
-        line['roofline'] = None  # a network of cuDNN synapses and neuron kernels has no single roof
+        line['roofline'] = None  # a chain of synapse and neuron kernels has no single roof
         line['config']['network'] = 'Pool4-Conv(2,16,5)-Pool2-Conv(16,32,3)-Pool2-Flatten-Dense(2048,512)-Dense(512,11), CUBA'
-    if rank == 0 and not args.no_cpu and not wl.name.startswith(('stream_',) + NETWORKS):
+    if rank == 0 and not args.no_cpu and not wl.name.startswith(NETWORKS):
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         line['cpu_baseline'] = cpu
     if dist is not None:

@@ -173,6 +173,19 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
                 float* final_c, float* final_v, float* final_s, const sb_geom* g, double threshold,
                 int w_scale, int graded, float spike_scale, int spike_delay, const float* delay_head,
                 const float* axon_delay, int64_t n_axon_delay, float axon_delay_ts, void* stream);
+/* Inference form of sb_cuba_fwd with the spikes as bits (no counterpart in the
+ * reference, whose Neuron.forward returns fp32 0/1 values, neuron/cuba.py:423-440):
+ * spike_bits is uint32[rows][ceil(T / 32)], word w of row r holding steps
+ * 32 w .. 32 w + 31 of that row (bit i = step 32 w + i; bits past T are 0).
+ * The fp32 spike tensor is not written, and neither is the voltage series when
+ * voltage is null: 4 B read and 1/8 B written per neuron-step instead of 12 B,
+ * and a device-to-host copy of the result that is 32 times smaller.
+ * Binary spikes only; spike_delay / delay_head as in sb_cuba_fwd. */
+int sb_cuba_fwd_packed(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay,
+                       int64_t n_vdecay, const float* cstate, const float* vstate, float* voltage,
+                       uint32_t* spike_bits, float* final_c, float* final_v, float* final_s, const sb_geom* g,
+                       double threshold, int w_scale, int spike_delay, const float* delay_head, void* stream);
+
 /* Backward of CUBA and ALIF forward: surrogate gradient + both integrators.
  * thr_tensor (nullable): per-element threshold (ALIF passes th + ref).
  * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch.
@@ -343,13 +356,6 @@ int sb_cuba_recurrent_fwd(const float* z, const float* rec_t, const float* cdeca
 int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const float* rec, float* grad_z,
                           int64_t batch, int64_t neurons, int64_t T, float threshold, float tau_rho,
                           float scale_rho, int graded, void* stream);
-
-/* ---- measurement aid ------------------------------------------------------------
- * No counterpart in the reference and not on the hot path: a plain streaming
- * kernel that reads `reads` streams of n floats (laid out back to back in `in`)
- * and writes `writes` streams of n floats (back to back in `out`).  bench.py
- * uses it to show what HBM delivers for the read:write mix of each kernel. */
-int sb_probe_stream(const float* in, float* out, int64_t n, int reads, int writes, void* stream);
 
 #ifdef __cplusplus
 }

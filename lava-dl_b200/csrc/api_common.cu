@@ -124,9 +124,7 @@ static void bind_primary_context() {
 // L2 fetches 256 bytes per missed 128-byte tile row: the next tile of the same
 // row (needed 32 steps later) is then an L2 hit and DRAM sees 256-byte reads.
 // Measured: CUBA forward 0.76 -> 0.80 of copy bandwidth, LI forward 0.79 -> 0.84.
-#ifndef SB_L2_PROMOTION
-#define SB_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-#endif
+static constexpr CUtensorMapL2promotion kL2Promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
 
 int make_row_map(CUtensorMap* out, const void* base, int64_t rows, int64_t T, int tile_steps) {
   return make_row_map_box(out, base, rows, T, tile_steps, kTileR);
@@ -145,7 +143,7 @@ int make_row_map_box(CUtensorMap* out, const void* base, int64_t rows, int64_t T
   const CUtensorMapSwizzle swizzle = tile_steps == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, SB_L2_PROMOTION,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, kL2Promotion,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld T=%lld base=%p)", (int)r, (long long)rows,

@@ -96,6 +96,42 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
 #undef SB_GO
 }
 
+int sb_cuba_fwd_packed(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay,
+                       int64_t n_vdecay, const float* cstate, const float* vstate, float* voltage,
+                       uint32_t* spike_bits, float* final_c, float* final_v, float* final_s, const sb_geom* g,
+                       double threshold, int w_scale, int spike_delay, const float* delay_head, void* stream) {
+  RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || spike_delay == 1, "spike_delay is 0 or 1");
+  SB_TRY(check_count(n_cdecay, "current decay"));
+  SB_TRY(check_count(n_vdecay, "voltage decay"));
+  const int64_t nmax = maxn({n_cdecay, n_vdecay});
+  SB_TRY(check_geom(g, &rg, nmax));
+  if (rg.rows == 0 || rg.T == 0) return SB_OK;
+  SB_REQUIRE(counts_ok({n_cdecay, n_vdecay}, nmax), "decay counts disagree");
+  SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
+  SB_REQUIRE(cdecay && vdecay && cstate && vstate, "null parameter pointer");
+  SB_REQUIRE(spike_bits != nullptr, "the packed spike output is required");
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(spike_bits) & 3u) == 0, "spike_bits must be 4-byte aligned");
+  const Scale sc = make_scale(w_scale);
+  const float thr_scaled = (float)(threshold * (double)w_scale);
+  const int k_reset = thr_scaled > 0.f ? int_threshold_ge(thr_scaled) : INT_MAX;
+  const int k_spike = int_threshold_ge_scaled((float)threshold, sc.w);
+  BitDelay bd{spike_delay, delay_head, nullptr, 0, 1.f};
+  bd.packed = spike_bits;
+  cudaStream_t st = (cudaStream_t)stream;
+  const float* in[1] = {x};
+  if (voltage != nullptr) {
+    typename CubaFwd<false, true, false, true>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate,
+                                                          final_c, final_v, final_s, k_reset, k_spike, 1.f, sc};
+    float* out[2] = {voltage, nullptr};
+    return launch_rowscan<CubaFwd<false, true, false, true>>(p, rg, in, out, st, bd);
+  }
+  typename CubaFwd<false, true, false, false>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate,
+                                                         final_c, final_v, final_s, k_reset, k_spike, 1.f, sc};
+  float* out[1] = {nullptr};
+  return launch_rowscan<CubaFwd<false, true, false, false>>(p, rg, in, out, st, bd);
+}
+
 int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
                 const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
                 int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,
@@ -333,11 +369,7 @@ int sb_cuba_recurrent_bwd(const float* grad_spike, const float* voltage, const f
   const int C = (int)neurons, threads = (C + 31) / 32 * 32;
   // Two samples per CTA share every load of R.  One CTA's walk gets about 1.2x slower that way (measured at
   // batch 128, 512 neurons: 5.5 -> 6.6 ms), so it pays only when it saves a wave of CTAs: batch > SM count.
-#ifdef SB_REC_BWD_S
-  const int S = SB_REC_BWD_S;
-#else
   const int S = (batch > sm_count() && rec_bwd_smem(C, 2) <= 200 * 1024) ? 2 : 1;
-#endif
   const size_t smem = rec_bwd_smem(C, S);
   const unsigned grid = (unsigned)((batch + S - 1) / S);
   cudaStream_t st = (cudaStream_t)stream;

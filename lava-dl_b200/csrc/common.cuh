@@ -75,6 +75,32 @@ __device__ __forceinline__ int mul_shift12(int a, int m) {
   return (int)(p >> 12);
 }
 
+// Shorter forms of the same value for multipliers of limited size, used on the
+// serial chain of the recurrences (every instruction there is latency).
+//   trunc(a * m / 4096) = floor((16 * a * m + 65535 * [a * m < 0]) / 65536):
+// 16 * a * m is a multiple of 16, so any bias in [65520, 65535] lands on the
+// same quotient as 4095 does before the scaling, and 0xFFFF is what one byte
+// permute with sign replication makes out of a sign bit.  The multiplier rides
+// in pre-shifted (m16 = m << 4), so the chain is PRMT, IMAD.WIDE, SHF.
+// sign16(x) = 0x0000FFFF for x < 0, else 0.
+__device__ __forceinline__ uint32_t sign16(int x) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, 0, 0x44BB;" : "=r"(d) : "r"(x));
+  return d;
+}
+// m16 = m << 4 with 0 <= m: the sign of the product is the sign of a.
+__device__ __forceinline__ int mul_shift12_pos(int a, int m16) {
+  const long long p = (long long)a * (long long)m16 + (long long)sign16(a);
+  return (int)(p >> 16);
+}
+// m16 = m << 4 with |m| < 2^27, either sign.
+__device__ __forceinline__ int mul_shift12_sym(int a, int m16) {
+  const long long p = (long long)a * (long long)m16 + (long long)sign16(a ^ m16);
+  return (int)(p >> 16);
+}
+// A multiplier the short forms may take (warp-uniform test at kernel start).
+__device__ __forceinline__ bool mul_is_decay(int m) { return m >= 0 && m <= 4096; }
+
 // (w_scale * x).to(int): one fp32 multiply (round to nearest), then truncation.
 __device__ __forceinline__ int to_fixed(float w, float x) { return __float2int_rz(__fmul_rn(w, x)); }
 

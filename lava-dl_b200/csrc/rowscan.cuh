@@ -50,10 +50,29 @@ struct RowPtrs {
 
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
+// An op may offer a second, shorter form of its step for parameters every lane
+// of the warp can take (HAS_FAST, fast(), step_t<FAST>): the skeleton asks once
+// per warp and runs whole tiles in that form.
+template <class Op, class = void>
+struct OpHasFast { static constexpr bool value = false; };
+template <class Op>
+struct OpHasFast<Op, decltype((void)Op::HAS_FAST)> { static constexpr bool value = Op::HAS_FAST; };
+
+template <class Op>
+__device__ __forceinline__ bool op_fast(const Op& op) {
+  if constexpr (OpHasFast<Op>::value) return op.fast();
+  else return false;
+}
+template <bool FAST, class Op, class A, class B>
+__device__ __forceinline__ void op_step(Op& op, const A& a, B& b) {
+  if constexpr (OpHasFast<Op>::value) op.template step_t<FAST>(a, b);
+  else op.step(a, b);
+}
+
 // ---------------------------------------------------------------------------
 // One tile: TW / 4 chunks of 4 steps.  nvalid < TW only for the ragged last tile.
 // ---------------------------------------------------------------------------
-template <class Op, bool FULL, int TW>
+template <class Op, bool FULL, int TW, bool FAST = false>
 __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, int nvalid,
                                              uint32_t (&bits)[Op::NBIT > 0 ? Op::NBIT : 1]) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT, NS = Op::NOUT - Op::NBIT;
@@ -80,7 +99,7 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 #pragma unroll
       for (int i = 0; i < NIN; ++i) a[i] = vin[i][j];
       if (FULL || c * 4 + j < nvalid) {
-        op.step(a, b);
+        op_step<FAST>(op, a, b);
       } else {
 #pragma unroll
         for (int o = 0; o < NOUT; ++o) b[o] = 0.f;
@@ -113,9 +132,13 @@ __device__ __forceinline__ void process_tile(Op& op, uint8_t* stage, int lane, i
 // steps later still, 0 .. 62.  A lane keeps the masks of its row's last two
 // boxes and takes each output word out of that 96-bit window with a funnel
 // shift, so the delay costs no memory traffic.
+// packed (bit output 0 only): the same bits as 32-bit words instead of, or next to, the 0.f / 1.f
+// values: word w of row r holds steps 32 w .. 32 w + 31 (bit i = step 32 w + i), packed_words words per row.
 template <int N>
 struct BitPtrs {
   float* p[N > 0 ? N : 1];
+  uint32_t* packed;
+  int64_t packed_words;
   const float* head;
   int delay;
   const float* lut;
@@ -129,6 +152,7 @@ struct BitDelay {
   const float* lut;   // per-row delays or null
   int64_t n_lut;
   float lut_ts;
+  uint32_t* packed = nullptr;  // [rows, ceil(T / 32)] or null: bit output 0 as 32-step words
 };
 
 constexpr int kMaxBitDelay = 62;  // per-row delay; with the step delay the window shift stays below 64
@@ -197,38 +221,21 @@ __device__ __forceinline__ void store_bit_rows(float* __restrict__ base, int64_t
 // ---------------------------------------------------------------------------
 // TMA-pipelined kernel
 // ---------------------------------------------------------------------------
-template <class Op, int STAGES, int NB, int TW>
-__global__ void __launch_bounds__(128)
-rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT> maps,
-                   const BitPtrs<Op::NBIT> bitout, const typename Op::Params p, const RowGeom g,
-                   unsigned int* status) {
+template <class Op, int STAGES, int NB, int TW, bool FAST>
+__device__ __forceinline__ void rowscan_tma_body(const MapPack<Op::NIN + Op::NOUT - Op::NBIT>& maps,
+                                                 const BitPtrs<Op::NBIT>& bitout, const typename Op::Params& p,
+                                                 const RowGeom& g, unsigned int* status, Op& op, uint8_t* wsm,
+                                                 uint32_t bar0, int64_t row0, int lane, int64_t warp_id) {
   constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
   constexpr int kTileT = TW;                         // shadows the 32-step default
   constexpr int kTileBytes = TW * kTileR * 4;
   constexpr int kStageBytes = NT * NB * kTileBytes;  // NB boxes of TW steps, side by side in time
   constexpr int kSpan = NB * kTileT;                 // time steps per stage
-  constexpr int kWarpBytes = STAGES * kStageBytes;
-  extern __shared__ uint8_t smem_raw[];
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * nwarps + warp) * kTileR;
-  if (row0 >= g.rows) return;
-  // swizzle-128B tiles need 1024-byte alignment; the launch reserves the slack
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* wsm = smem + (size_t)warp * kWarpBytes;
-  const uint32_t bar0 = smem_u32(smem + (size_t)nwarps * kWarpBytes) + warp * STAGES * 8;
-
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + s * 8, 1);
-    fence_mbar_init();
-    fence_proxy_async();
-  }
-  __syncwarp();
-
   const int T = g.T;
   const int ntiles = (T + kSpan - 1) / kSpan;
   const int y = (int)row0;
+  const int64_t row = row0 + lane;
+  const bool valid = row < g.rows;
 
   auto tile_t0 = [&](int k) { return (Op::REVERSE ? (ntiles - 1 - k) : k) * kSpan; };
   auto issue_load = [&](int k) {  // lane 0 only
@@ -245,11 +252,6 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
                     bar);
     }
   };
-
-  Op op;
-  const int64_t row = row0 + lane;
-  const bool valid = row < g.rows;
-  op.init(p, g, row, valid);
 
   // delayed bit outputs: the masks of the row's last two boxes and the row's shift
   uint32_t prev1 = 0u, prev2 = 0u;
@@ -282,8 +284,8 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
       const int nvalid = T - (t0 + b * kTileT);
       if (nvalid > 0) {
         uint8_t* box = stage + b * NT * kTileBytes;
-        if (nvalid >= kTileT) process_tile<Op, true, TW>(op, box, lane, kTileT, boxbits);
-        else process_tile<Op, false, TW>(op, box, lane, nvalid, boxbits);
+        if (nvalid >= kTileT) process_tile<Op, true, TW, FAST>(op, box, lane, kTileT, boxbits);
+        else process_tile<Op, false, TW, FAST>(op, box, lane, nvalid, boxbits);
         op.tile_end();
       }
       if (delayed) {  // forward ops only: boxes come in time order (32-step boxes)
@@ -314,10 +316,19 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
     __syncwarp();
     if (NBIT > 0) {
       const int64_t left = g.rows - row0;
+      if (TW == 32 && bitout.packed != nullptr && valid) {
+        uint32_t* dst = bitout.packed + row * bitout.packed_words + t0 / 32;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const int left_t = T - (t0 + b * kTileT);  // a delayed word carries the row's last bits past T
+          if (left_t > 0) dst[b] = left_t >= 32 ? bits[0][b] : (bits[0][b] & ((1u << left_t) - 1u));
+        }
+      }
 #pragma unroll
       for (int d = 0; d < NBIT; ++d)
-        store_bit_rows<NB, TW>(bitout.p[d] + row0 * (int64_t)T + t0, T, left < kTileR ? (int)left : kTileR, T - t0,
-                               bits[d], lane, (reinterpret_cast<uintptr_t>(bitout.p[d]) & 15u) == 0);
+        if (bitout.p[d] != nullptr)
+          store_bit_rows<NB, TW>(bitout.p[d] + row0 * (int64_t)T + t0, T, left < kTileR ? (int)left : kTileR, T - t0,
+                                 bits[d], lane, (reinterpret_cast<uintptr_t>(bitout.p[d]) & 15u) == 0);
     }
   }
 
@@ -332,32 +343,59 @@ rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT
     }
     return;
   }
-  op.finish(p, g, row, valid, lane, (int64_t)blockIdx.x * nwarps + warp);
+  op.finish(p, g, row, valid, lane, warp_id);
+}
+
+template <class Op, int STAGES, int NB, int TW>
+__global__ void __launch_bounds__(128)
+rowscan_tma_kernel(const __grid_constant__ MapPack<Op::NIN + Op::NOUT - Op::NBIT> maps,
+                   const BitPtrs<Op::NBIT> bitout, const typename Op::Params p, const RowGeom g,
+                   unsigned int* status) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NT = cmax(NIN, NOUT);
+  constexpr int kWarpBytes = STAGES * NT * NB * (TW * kTileR * 4);
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int64_t warp_id = (int64_t)blockIdx.x * nwarps + warp;
+  const int64_t row0 = warp_id * kTileR;
+  if (row0 >= g.rows) return;
+  // swizzle-128B tiles need 1024-byte alignment; the launch reserves the slack
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* wsm = smem + (size_t)warp * kWarpBytes;
+  const uint32_t bar0 = smem_u32(smem + (size_t)nwarps * kWarpBytes) + warp * STAGES * 8;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + s * 8, 1);
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  Op op;
+  op.init(p, g, row0 + lane, row0 + lane < g.rows);
+  // one warp-uniform choice between the two forms of the op's step for the whole walk
+  if (OpHasFast<Op>::value && op_fast(op))
+    rowscan_tma_body<Op, STAGES, NB, TW, true>(maps, bitout, p, g, status, op, wsm, bar0, row0, lane, warp_id);
+  else
+    rowscan_tma_body<Op, STAGES, NB, TW, false>(maps, bitout, p, g, status, op, wsm, bar0, row0, lane, warp_id);
 }
 
 // ---------------------------------------------------------------------------
 // Plain-load kernel: any T, any alignment.  Same tiles, same ops.
 // ---------------------------------------------------------------------------
-template <class Op>
-__global__ void __launch_bounds__(128)
-rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, const typename Op::Params p,
-                     const RowGeom g, unsigned int* status) {
-  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT, NT = cmax(NIN, NOUT);
-  extern __shared__ uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int64_t wid = (int64_t)blockIdx.x * nwarps + warp;
+template <class Op, bool FAST>
+__device__ __forceinline__ void rowscan_plain_body(const RowPtrs<Op::NIN, Op::NOUT>& ptrs, const BitDelay& bd,
+                                                   const typename Op::Params& p, const RowGeom& g,
+                                                   unsigned int* status, Op& op, uint8_t* stage, int64_t wid,
+                                                   int lane) {
+  constexpr int NIN = Op::NIN, NOUT = Op::NOUT - Op::NBIT, NBIT = Op::NBIT;
   const int64_t row0 = wid * kTileR;
-  if (row0 >= g.rows) return;
-  uint8_t* stage = smem + (size_t)warp * NT * kTileBytes;
-
   const int T = g.T;
   const int ntiles = (T + kTileT - 1) / kTileT;
   const int nrows = (int)((g.rows - row0) < kTileR ? (g.rows - row0) : kTileR);
-
-  Op op;
   const int64_t row = row0 + lane;
   const bool valid = row < g.rows;
-  op.init(p, g, row, valid);
 
   uint32_t prev1 = 0u, prev2 = 0u;
   const bool delayed = NBIT > 0 && (bd.steps != 0 || bd.lut != nullptr);
@@ -385,8 +423,8 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, c
     uint32_t bits[NBIT > 0 ? NBIT : 1];
 #pragma unroll
     for (int d = 0; d < (NBIT > 0 ? NBIT : 1); ++d) bits[d] = 0u;
-    if (nvalid >= kTileT) process_tile<Op, true, 32>(op, stage, lane, kTileT, bits);
-    else process_tile<Op, false, 32>(op, stage, lane, nvalid, bits);
+    if (nvalid >= kTileT) process_tile<Op, true, 32, FAST>(op, stage, lane, kTileT, bits);
+    else process_tile<Op, false, 32, FAST>(op, stage, lane, nvalid, bits);
     op.tile_end();
     if (delayed) {
       const uint32_t m = bits[0];
@@ -404,14 +442,33 @@ rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, c
           dst[(int64_t)r * T] = *reinterpret_cast<const float*>(stage + o * kTileBytes + swz_elem(r, lane));
       }
     }
+    if (NBIT > 0 && bd.packed != nullptr && valid)
+      bd.packed[row * (int64_t)((T + 31) / 32) + t0 / 32] = nvalid >= 32 ? bits[0] : (bits[0] & ((1u << nvalid) - 1u));
 #pragma unroll
     for (int d = 0; d < NBIT; ++d) {
+      if (ptrs.out[NOUT + d] == nullptr) continue;
       const uint32_t one[1] = {bits[d]};
       store_bit_rows<1, 32>(ptrs.out[NOUT + d] + row0 * (int64_t)T + t0, T, nrows, nvalid, one, lane, false);
     }
     __syncwarp();
   }
   op.finish(p, g, row, valid, lane, wid);
+}
+
+template <class Op>
+__global__ void __launch_bounds__(128)
+rowscan_plain_kernel(const RowPtrs<Op::NIN, Op::NOUT> ptrs, const BitDelay bd, const typename Op::Params p,
+                     const RowGeom g, unsigned int* status) {
+  constexpr int NT = cmax(Op::NIN, Op::NOUT - Op::NBIT);
+  extern __shared__ uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int64_t wid = (int64_t)blockIdx.x * nwarps + warp;
+  if (wid * kTileR >= g.rows) return;
+  uint8_t* stage = smem + (size_t)warp * NT * kTileBytes;
+  Op op;
+  op.init(p, g, wid * kTileR + lane, wid * kTileR + lane < g.rows);
+  if (OpHasFast<Op>::value && op_fast(op)) rowscan_plain_body<Op, true>(ptrs, bd, p, g, status, op, stage, wid, lane);
+  else rowscan_plain_body<Op, false>(ptrs, bd, p, g, status, op, stage, wid, lane);
 }
 
 // ---------------------------------------------------------------------------
@@ -426,23 +483,10 @@ struct LaunchPlan {
 LaunchPlan plan_rowscan(int64_t rows, size_t bytes_per_warp, size_t fixed_bytes);
 int prepare_kernel(const void* fn, size_t smem);
 
-// Pipeline shape of the TMA kernels.  Each op names its own (ops.cuh); the
-// macros override all of them at once for sweeps.
-#ifdef SB_STAGES
-template <class Op> constexpr int pipe_stages() { return SB_STAGES; }
-#else
+// Pipeline shape of the TMA kernels: each op names its own (ops.cuh).
 template <class Op> constexpr int pipe_stages() { return Op::STAGES; }
-#endif
-#ifdef SB_BOXES
-template <class Op> constexpr int pipe_boxes() { return SB_BOXES; }
-#else
 template <class Op> constexpr int pipe_boxes() { return Op::BOXES; }
-#endif
-#ifdef SB_TILE_STEPS
-template <class Op> constexpr int pipe_tile() { return SB_TILE_STEPS; }
-#else
 template <class Op> constexpr int pipe_tile() { return Op::TILE; }
-#endif
 
 template <class Op, int STAGES = pipe_stages<Op>(), int NB = pipe_boxes<Op>(), int TW = pipe_tile<Op>()>
 int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* const* in, float* const* out,
@@ -464,13 +508,18 @@ int launch_rowscan(const typename Op::Params& p, const RowGeom& g, const float* 
              "a per-row output delay needs one bit output, 32-step tiles and a table that tiles the rows");
   BitPtrs<NBIT> bitout;
   bitout.p[0] = nullptr;
+  bitout.packed = bit_delay.packed;
+  bitout.packed_words = (g.T + 31) / 32;
   bitout.head = bit_delay.head;
   bitout.delay = bit_delay.steps;
   bitout.lut = bit_delay.lut;
   bitout.n_lut = bit_delay.n_lut;
   bitout.lut_ts = bit_delay.lut_ts;
+  SB_REQUIRE(bit_delay.packed == nullptr || (NBIT == 1 && TW == 32 && !Op::REVERSE),
+             "packed output exists only for forward ops with one bit output and 32-step tiles");
   for (int d = 0; d < NBIT; ++d) {
-    SB_REQUIRE(out[NOUT + d] != nullptr, "null tensor pointer (bit output %d)", d);
+    SB_REQUIRE(out[NOUT + d] != nullptr || (d == 0 && bit_delay.packed != nullptr),
+               "null tensor pointer (bit output %d)", d);
     bitout.p[d] = out[NOUT + d];
   }
   unsigned int* status = status_ptr();

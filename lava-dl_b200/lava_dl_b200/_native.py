@@ -50,6 +50,8 @@ SIGNATURES = {
     'sb_cspike_bwd': (c_int, [_P, _P, _P, c_float, _P, _P, _P, _I64, c_float, c_float, c_int, _P]),
     'sb_cuba_fwd': (c_int, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _G,
                             c_double, c_int, c_int, c_float, c_int, _P, _P, _I64, c_float, _P]),
+    'sb_cuba_fwd_packed': (c_int, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _G,
+                                   c_double, c_int, c_int, _P, _P]),
     'sb_cuba_bwd': (c_int, [_P, _P, _P, c_float, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _G,
                             c_float, c_float, c_int, c_int, _P]),
     'sb_cuba_recurrent_fwd': (c_int, [_P, _P, _P, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P,
@@ -80,7 +82,6 @@ SIGNATURES = {
     'sb_conv_wgrad_scratch_bytes': (_I64, [_I64] * 7),
     'sb_conv_wgrad': (c_int, [_P, _P, _P, _P] + [_I64] * 10 + [_P]),
     'sb_broadcast_fill': (c_int, [_P, _P, _I64, _P]),
-    'sb_probe_stream': (c_int, [_P, _P, _I64, c_int, c_int, _P]),
     'sb_shift_fir_bwd': (c_int, [_P, _P, _I64, c_float, c_float, _P, _I64, c_float, _P, _I64, _I64, _P]),
 }
 

@@ -453,6 +453,35 @@ def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current
     return dict(current=cur, voltage=vol, spike=spk, final_c=fc, final_v=fv, final_s=fs)
 
 
+def cuba_fwd_packed(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_voltage=False, spike_delay=0,
+                    delay_head=None):
+    """Inference pass with the spikes as bits: ``spike_bits`` is int32 ``x.shape[:-1] + (ceil(T / 32),)``,
+    bit ``i`` of word ``w`` = spike at step ``32 w + i`` (``unpack_spikes`` restores the fp32 tensor).
+    Returns dict(spike_bits, voltage or None, final_c, final_v, final_s)."""
+    N.require_cuda(x)
+    x = _c(x)
+    cd, vd = _param(cdecay, x), _param(vdecay, x)
+    cs, vs = row_state(cstate, x), row_state(vstate, x)
+    T = x.shape[-1]
+    bits = torch.empty(x.shape[:-1] + ((T + 31) // 32,), device=x.device, dtype=torch.int32)
+    vol = torch.empty_like(x) if want_voltage else None
+    fc, fv, fs = _vec(x), _vec(x), _vec(x)
+    g = geom(x, cd.numel(), vd.numel())
+    head = None if delay_head is None else row_state(delay_head, x)
+    N.call('sb_cuba_fwd_packed', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(cs), N.ptr(vs),
+           N.ptr(vol), N.ptr(bits), N.ptr(fc), N.ptr(fv), N.ptr(fs), g, float(threshold), int(w_scale),
+           int(spike_delay), N.ptr(head), N.stream_of(x))
+    return dict(spike_bits=bits, voltage=vol, final_c=fc, final_v=fv, final_s=fs)
+
+
+def unpack_spikes(bits, T):
+    """fp32 0/1 tensor ``bits.shape[:-1] + (T,)`` from the packed words of ``cuba_fwd_packed``
+    (plain torch ops, on whatever device ``bits`` lives)."""
+    shifts = torch.arange(32, device=bits.device, dtype=torch.int32)
+    b = (bits.unsqueeze(-1) >> shifts) & 1
+    return b.reshape(bits.shape[:-1] + (-1,))[..., :T].to(torch.float32)
+
+
 def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_decay_grad,
              spike_delay=0):
     N.require_cuda(grad_spike, voltage)

@@ -255,6 +255,27 @@ class Neuron(base.Neuron):
             spike = self.drop(spike)
         return spike
 
+    def forward_packed(self, input, want_voltage=False):
+        """Inference-only ``forward`` with the spikes as bits (no counterpart in lava-dl).
+
+        Returns an int32 tensor ``input.shape[:-1] + (ceil(T / 32),)``: bit ``i`` of word ``w``
+        is the spike at step ``32 w + i``; ``slayer.utils.unpack_spikes(bits, T)`` restores what
+        ``forward`` returns.  The fp32 spike tensor is never written, so the pass moves a third of
+        the bytes and its result is 32 times smaller to copy to the host.  No gradient, binary
+        spikes, no normalisation or dropout; persistent state is kept as ``forward`` keeps it.
+        With ``want_voltage`` the voltage series is returned as well: ``(bits, voltage)``."""
+        if self.norm is not None or not self._fusable or self.graded_spike is True or self.drop is not None:
+            raise NotImplementedError('forward_packed needs binary spikes and no normalisation or dropout')
+        self._prepare(input)
+        with torch.no_grad():
+            r = _ops.cuba_fwd_packed(input, quantize(self.current_decay), quantize(self.voltage_decay),
+                                     self.current_state, self.voltage_state,
+                                     self.threshold + self.threshold_eps, self.s_scale, want_voltage=want_voltage)
+            if self.persistent_state:
+                self.current_state = r['final_c']
+                self.voltage_state = leaky_integrator.persistent_state(r['final_v'], r['final_s'])
+        return (r['spike_bits'], r['voltage']) if want_voltage else r['spike_bits']
+
     @property
     def fuses_step_delay(self):
         """True when ``forward_step_delayed`` can write the spikes one step late

@@ -1,5 +1,6 @@
 """Time-axis manipulation (mirror of ``lava.lib.dl.slayer.utils.time``)."""
 
 from .shift import shift
+from .replicate import replicate
 
-__all__ = ['shift']
+__all__ = ['shift', 'replicate']

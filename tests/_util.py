@@ -64,12 +64,29 @@ def assert_quantised_equal(a, b, w_scale, what=''):
     assert_exact(a.astype(np.int64), b.astype(np.int64), what)
 
 
+# Reported, not asserted: how many elements of each sum-type comparison would also pass the plain
+# element-wise criterion |a - b| <= 1e-5 * |b|.  what -> [elements, elements inside, smallest
+# per-call fraction]; conftest prints the table at the end of a run.
+LITERAL = {}
+
+
+def record_literal(a, b, what, rtol=RTOL):
+    inside = int(np.count_nonzero(np.abs(a - b) <= rtol * np.abs(b)))
+    rec = LITERAL.setdefault(what, [0, 0, 1.0])
+    rec[0] += a.size
+    rec[1] += inside
+    rec[2] = min(rec[2], inside / a.size)
+    return inside / a.size
+
+
 def assert_close(a, b, what='', rtol=RTOL, floor=FLOOR, scale=None):
     a, b = to_np(a).astype(np.float64), to_np(b).astype(np.float64)
     assert a.shape == b.shape, f'{what}: shape {a.shape} vs {b.shape}'
     if b.size == 0:
         return
     assert np.all(np.isfinite(a)), f'{what}: non-finite values'
+    if scale is not None:
+        record_literal(a, b, what, rtol)
     if scale is None:
         scale = np.maximum(np.abs(b), floor * np.max(np.abs(b)))
     else:

@@ -513,6 +513,27 @@ def main():
          voltage_decay=rec.neuron.voltage_decay.data, out=yg)
     print('recurrent block spike counts:', int(y1.sum()), int(y2.sum()), int((yg != 0).sum()))
 
+    # ------------------------------------------------------------------
+    # learnable filter bank (utils/filter/fir.py:57-100) and replication in time (utils/time/replicate.py)
+    # ------------------------------------------------------------------
+    from lava.lib.dl.slayer.utils.filter import FIRBank
+    from lava.lib.dl.slayer.utils.time import replicate
+    torch.manual_seed(7)
+    bank = FIRBank(3, 9, scale=2)
+    xb = randn(2, 5, 41)
+    xin = xb.clone().requires_grad_(True)
+    yb = bank(xin)
+    g_b = randn(*yb.shape)
+    (yb * g_b).sum().backward()
+    xb4 = randn(2, 3, 2, 37)
+    with torch.no_grad():
+        yb4 = bank(xb4)
+    save('firbank', x=xb, weight=bank.weight.data, out=yb, grad_out=g_b, grad_x=xin.grad,
+         grad_weight=bank.weight.grad, x4=xb4, out4=yb4)
+    xr2 = randn(3, 4)
+    xr4 = randn(2, 3, 2, 2)
+    save('replicate', x2=xr2, out2=replicate(xr2, 5), x4=xr4, out4=replicate(xr4, 3))
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

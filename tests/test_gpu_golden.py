@@ -489,3 +489,24 @@ def test_recurrent_block_graded(cuda, slayer):
         blk.neuron.voltage_state = torch.zeros(1, device=cuda)
         y = blk(T(g['x'], cuda))
     assert_exact(y, g['out'], 'graded spikes (every product and sum of this case is exact in fp32)')
+
+
+def test_firbank(cuda, slayer):
+    """Learnable filter bank: outputs, input gradient and weight gradient of the reference's
+    conv3d-based module, on rank-3 and rank-4 inputs; same state_dict key."""
+    g = load_golden('firbank')
+    bank = slayer.utils.filter.FIRBank(3, 9, scale=2).to(cuda)
+    assert list(bank.state_dict().keys()) == ['weight']
+    bank.load_state_dict({'weight': torch.tensor(g['weight'])})
+    x = torch.tensor(g['x'], device=cuda, requires_grad=True)
+    out = bank(x)
+    mag = np.abs(g['weight']).sum() * np.abs(g['x']).max()
+    assert_close(out, g['out'], 'filter bank output', scale=mag)
+    (out * torch.tensor(g['grad_out'], device=cuda)).sum().backward()
+    gmag = np.abs(g['weight']).sum() * np.abs(g['grad_out']).max() * 3
+    assert_close(x.grad, g['grad_x'], 'filter bank input gradient', scale=gmag)
+    wmag = np.abs(g['grad_out']).max() * np.abs(g['x']).sum()
+    assert_close(bank.weight.grad, g['grad_weight'], 'filter bank weight gradient', scale=wmag)
+    with torch.no_grad():
+        out4 = bank(torch.tensor(g['x4'], device=cuda))
+    assert_close(out4, g['out4'], 'filter bank output, rank 4', scale=np.abs(g['weight']).sum() * np.abs(g['x4']).max())

@@ -353,6 +353,111 @@ def test_cuba_fused(shape, per_channel, misalign, cuda, ops):
         assert_exact(gx2, gx, 'grad_x with and without decay gradients')
 
 
+@pytest.mark.parametrize('shape', [(2, 3, 2), (3, 11, 33), (1, 257, 64), (4, 64, 128), (2, 33, 36)])
+@pytest.mark.parametrize('per_channel', [False, True])
+def test_decays_outside_the_clamp(shape, per_channel, cuda, ops):
+    """The raw dynamics() calls accept any decay: 4096 - decay below 0 or above 4096 (the Neuron
+    classes clamp to 0 .. 4096 first).  The kernels pick their short truncating multiply per warp only
+    when every lane's multiplier is a plain decay; these inputs make warps take the general one,
+    alone and mixed with in-range channels, plus a spike threshold that differs from the reset one."""
+    rng = rng_for('wide', shape, per_channel)
+    B, C, T = shape
+    n = C if per_channel else 1
+
+    def wide(k):
+        d = decays(rng, n, -60, 4400)   # 4096 - d <= 4156: states grow at most 6.5-fold over 128 steps (int32 states)
+        if per_channel and n > 2:
+            d[:: 3] = decays(rng, len(d[:: 3]), 0, 4096)   # in-range channels next to out-of-range ones
+        else:
+            d[0] = (-50.0, 4200.0, 4096.0, 0.0)[k % 4]
+        return d
+
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    st = [quant(rng.normal(0, 0.5, size=shape[:-1])) for _ in range(4)]
+    for k in range(2):
+        dec = wide(k)
+        for thr in (None, 0.9):
+            want = O.li_fwd(x, dec, st[0], W, thr)
+            got = ops.li_fwd(dev(x, cuda), dev(dec, cuda), dev(st[0], cuda), W, thr)
+            assert_quantised_equal(got, want, W, f'li_fwd decay={dec[:3]} thr={thr}')
+        cd, vd = wide(k), wide(k + 1)
+        want = O.cuba(x, 1.25, cd, vd, cstate=st[0], vstate=st[1])
+        r = ops.cuba_fwd(dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(st[0], cuda), dev(st[1], cuda),
+                         1.25 + 0.01 / W, W, want_current=True, want_spike=True)
+        assert_quantised_equal(r['current'], want['current'], W, 'current')
+        assert_quantised_equal(r['voltage'], want['voltage'], W, 'voltage')
+        assert_exact(r['spike'], want['spike'], 'spike')
+        td, rd = wide(k + 2), wide(k + 3)
+        ths, refs = quant(rng.uniform(0.8, 1.5, size=shape[:-1])), quant(rng.uniform(0.0, 0.5, size=shape[:-1]))
+        th_w, ref_w = O.ath_fwd(x, refs, rd, ths, td, 0.5, 1.0, W)
+        th, ref = ops.ath_fwd(dev(x, cuda), dev(refs, cuda), dev(rd, cuda), dev(ths, cuda), dev(td, cuda), 0.5, 1.0, W)
+        assert_quantised_equal(th, th_w, W, 'ath threshold')
+        assert_quantised_equal(ref, ref_w, W, 'ath refractory')
+        want = O.alif(x, 1.0, 0.5, cd, vd, td, rd, cstate=st[0], vstate=st[1], th_state=ths, ref_state=refs)
+        args = (dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(rd, cuda), dev(td, cuda), dev(st[0], cuda),
+                dev(st[1], cuda), dev(refs, cuda), dev(ths, cuda), 0.5, 1.0, W)
+        outs, _ = ops.alif_fwd(*args, dynamics_mode=True)
+        for o, key in zip(outs, ('current', 'voltage', 'threshold', 'refractory')):
+            assert_quantised_equal(o, want[key], W, key)
+        (spike, _, _), _ = ops.alif_fwd(*args, dynamics_mode=False)
+        assert_exact(spike, want['spike'], 'alif spike')
+    # spike threshold and reset threshold that differ: no reset at all (threshold <= 0 disables it)
+    cd, vd = decays(rng, n, 800, 1300), decays(rng, n, 50, 300)
+    r = ops.cuba_fwd(dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(st[0], cuda), dev(st[1], cuda),
+                     -0.5, W, want_current=True, want_spike=True)
+    cur = O.li_fwd(x, cd, st[0], W)
+    vol = O.li_fwd(cur, vd, st[1], W)
+    assert_quantised_equal(r['current'], cur, W, 'current without reset')
+    assert_quantised_equal(r['voltage'], vol, W, 'voltage without reset')
+    assert_exact(r['spike'], O.spike_fwd(vol, -0.5), 'spike without reset')
+    # sin / cos beyond the pre-shifted multiplier's range take the general product
+    sd = np.full(n, float(1 << 27), np.float32)
+    cdk = np.full(n, -float((1 << 27) + 4096), np.float32)
+    small = (x * 1e-3).astype(np.float32)
+    zero = np.zeros(shape[:-1], np.float32)
+    re_w, im_w = O.res_fwd(small, small, sd, cdk, zero, zero, W, None)
+    re, im = ops.res_fwd(dev(small, cuda), dev(small, cuda), dev(sd, cuda), dev(cdk, cuda), dev(zero, cuda),
+                         dev(zero, cuda), W, None)
+    # such multipliers grow the state 32768-fold per step: the first two steps stay inside int32
+    keep = min(T, 2)
+    assert np.abs(re_w[..., :keep]).max() * W < 2 ** 31 and np.abs(im_w[..., :keep]).max() * W < 2 ** 31
+    assert_quantised_equal(re[..., :keep], re_w[..., :keep], W, 'resonator with huge sin/cos (real)')
+    assert_quantised_equal(im[..., :keep], im_w[..., :keep], W, 'resonator with huge sin/cos (imag)')
+
+
+@pytest.mark.parametrize('shape', SHAPES + [(3, 40, 96), (2, 70, 416)])
+@pytest.mark.parametrize('misalign', [False, True])
+@pytest.mark.parametrize('want_voltage', [False, True])
+def test_cuba_packed_spikes(shape, misalign, want_voltage, cuda, ops):
+    """Spikes as 32-step bit words, with and without the voltage series, with and without the
+    one-step delay: unpacked they are the fp32 spike tensor of the oracle."""
+    rng = rng_for('packed', shape)
+    B, C, T = shape
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, C, 800, 1300), decays(rng, C, 50, 300)
+    cs, vs = quant(rng.normal(0, 0.5, size=shape[:-1])), quant(rng.normal(0, 0.5, size=shape[:-1]))
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    want = O.cuba(x, 1.25, cd, vd, cstate=cs, vstate=vs)
+    for delay in (0, 1):
+        r = ops.cuba_fwd_packed(dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), dev(cs, cuda), dev(vs, cuda),
+                                1.25 + 0.01 / W, W, want_voltage=want_voltage, spike_delay=delay,
+                                delay_head=dev(head, cuda) if delay else None)
+        bits = r['spike_bits']
+        assert bits.dtype == torch.int32 and tuple(bits.shape) == (B, C, (T + 31) // 32)
+        spike = want['spike']
+        if delay:
+            spike = np.concatenate([head[..., None], spike[..., :-1]], axis=-1)
+        assert_exact(ops.unpack_spikes(bits, T), spike, f'unpacked spikes (delay {delay})')
+        tail = ops.unpack_spikes(bits, 32 * bits.shape[-1])[..., T:]
+        assert not bool(tail.any()), 'bits past the end of the row must be zero'
+        if want_voltage:
+            assert_quantised_equal(r['voltage'], want['voltage'], W, 'voltage')
+        else:
+            assert r['voltage'] is None
+        assert_exact(r['final_v'], want['voltage'][..., -1], 'final voltage')
+        assert_exact(r['final_s'], want['spike'][..., -1], 'final spike')
+
+
 @pytest.mark.parametrize('shape', SHAPES)
 @pytest.mark.parametrize('misalign', [False, True])
 def test_cuba_fused_step_delay(shape, misalign, cuda, ops):

@@ -177,3 +177,20 @@ def test_recurrent_block_host_side():
         slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 5), alif, blk.recurrent_synapse)
     with pytest.raises(ValueError):
         slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 1, 1, 5), blk.neuron, blk.recurrent_synapse)
+
+
+def test_replicate_matches_reference():
+    """utils.time.replicate against the reference's interpolate-based version (values and gradient)."""
+    import torch
+    from _util import load_golden
+    from lava_dl_b200.slayer.utils.time import replicate
+    g = load_golden('replicate')
+    for k, steps in (('2', 5), ('4', 3)):
+        x = torch.tensor(g['x' + k], requires_grad=True)
+        out = replicate(x, steps)
+        assert out.shape == g['out' + k].shape
+        assert (out.detach().numpy() == g['out' + k]).all()
+        out.sum().backward()
+        assert (x.grad == steps).all()
+    with pytest.raises(NotImplementedError):
+        replicate(torch.zeros(3), 4)
