@@ -117,7 +117,11 @@ class _SpikeConv(torch.autograd.Function):
         input, weight = ctx.saved_tensors
         grad_output = grad_output.contiguous()
         kh, kw = weight.shape[2], weight.shape[3]
-        own_dgrad = kh - 1 - ctx.padding[0] >= 0 and kw - 1 - ctx.padding[1] >= 0
+        # the input gradient is the forward kernel on the swapped problem (channels Co -> Ci, flipped
+        # padding): it must pass that kernel's own limits, which a wide layer can meet forward only
+        flipped = (kh - 1 - ctx.padding[0], kw - 1 - ctx.padding[1], 0)
+        own_dgrad = flipped[0] >= 0 and flipped[1] >= 0 and _ops.conv_fwd_supported(
+            grad_output, weight.transpose(0, 1), (1, 1, 1), flipped, (1, 1, 1), 1)
         own_wgrad = _ops.conv_wgrad_supported(input, weight) and grad_output.data_ptr() % 16 == 0
         grad_input = grad_weight = None
         if ctx.needs_input_grad[0] and own_dgrad:

@@ -331,6 +331,29 @@ def cuba(x, threshold, current_decay, voltage_decay, scale=64, cstate=0., vstate
     return out
 
 
+def cuba_grad_x_scale(voltage, threshold, grad_spike, current_decay, voltage_decay, scale=64, tau_grad=1,
+                      scale_grad=1, graded=False):
+    """Comparison scale for the input gradient of ``cuba``: the two reverse scans run on the
+    magnitudes of their terms (float64).  An element of grad_x is a sum of signed terms whose
+    exponentials differ by an ulp between math libraries; 1e-5 of this sum of magnitudes is the
+    forward-error bound such a sum can be held to, and equals 1e-5 relative where nothing cancels."""
+    w_scale, s_scale = scale, scale * 64
+    thr = int(threshold * w_scale) / w_scale + 0.01 / s_scale
+    g = np.abs(spike_bwd(voltage, thr, grad_spike, tau_grad * (int(threshold * w_scale) / w_scale) * 100,
+                         scale_grad * 0.1, graded)).astype(np.float64)
+    for decay in (voltage_decay, current_decay):
+        d = quantize(decay).astype(np.float64).reshape(-1)
+        a = np.abs(1.0 - d / 4096.0)
+        a = a[0] if a.size == 1 else a.reshape((1, -1) + (1,) * (g.ndim - 3))
+        acc = np.zeros(g.shape[:-1])
+        out = np.empty_like(g)
+        for t in range(g.shape[-1] - 1, -1, -1):
+            acc = a * acc + g[..., t]
+            out[..., t] = acc
+        g = out
+    return g
+
+
 def cuba_recurrent(z, rec, threshold, current_decay, voltage_decay, scale=64, cstate=0., vstate=0., grad_spike=None,
                    tau_grad=1, scale_grad=1, graded=False):
     """utils/recurrent.py:45-112: per step, feedback = s[t-1] R^T, one CUBA neuron call

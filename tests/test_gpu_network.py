@@ -118,7 +118,10 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
 
 @pytest.mark.parametrize('shape,co,k,pad', [((2, 2, 8, 8, 40), 16, 5, 2), ((1, 3, 7, 9, 12), 5, 3, 1),
                                             ((2, 16, 6, 6, 33), 32, 3, 1), ((1, 4, 5, 6, 8), 20, (3, 1), (0, 0)),
-                                            ((3, 1, 4, 4, 1), 2, 1, 0)])
+                                            ((3, 1, 4, 4, 1), 2, 1, 0),
+                                            # forward fits the kernel, the swapped (input-gradient) problem does not:
+                                            # 200 output channels x 9 taps of weights, and N * H = 66000 rows
+                                            ((1, 4, 6, 6, 8), 200, 3, 1), ((2200, 1, 30, 3, 4), 2, (3, 1), (0, 0))])
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
