@@ -311,9 +311,24 @@ int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t
 
 /* Convolution synapse, forward (replaces the Conv3d call of synapse/layer.py:297-323
  * for stride 1, dilation 1, one group).  x [N, Ci, H, W, T], weight [Co, Ci, kh, kw]
- * (after the pre-hook), y [N, Co, H+2ph-kh+1, W+2pw-kw+1, T].  Needs N * Ho <= 65535. */
+ * (after the pre-hook), y [N, Co, H+2ph-kh+1, W+2pw-kw+1, T].
+ * Two kernels: an implicit GEMM on the tensor cores (tcgen05, operands split into TF32 pairs so
+ * that the result keeps fp32 accuracy; bit-exact for spikes and weights on a 1/32 grid) for 1x1,
+ * 3x3 and 5x5 kernels with T a multiple of 4 and >= 32 and 16-byte aligned tensors, and an fp32
+ * kernel for every shape with N * Ho <= 65535 and the weights of 16 output channels in 96 KB.
+ * sb_conv_fwd picks the tensor cores when the shape allows and the contraction is long enough to
+ * pay for them (Ci * kh * kw >= 64); sb_conv_fwd_path takes the choice from the caller:
+ * path 0 = fp32 kernel, 1 = tensor cores (SB_ERR_UNSUPPORTED if the shape does not fit), -1 = as
+ * sb_conv_fwd.  sb_conv_uses_tensor_cores says what sb_conv_fwd would do. */
 int sb_conv_fwd(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co, int64_t H,
                 int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, void* stream);
+int sb_conv_fwd_path(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co, int64_t H,
+                     int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, int path, void* stream);
+int sb_conv_uses_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw,
+                              int64_t ph, int64_t pw, int64_t T);
+/* 1 when the tensor-core kernel can take the geometry at all (what path = 1 needs). */
+int sb_conv_fits_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw,
+                              int64_t ph, int64_t pw, int64_t T);
 
 /* Weight gradient of the same convolution (what convolution_backward returns for
  * the weight of the Conv3d at synapse/layer.py:297-323), fp32:

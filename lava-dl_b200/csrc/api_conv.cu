@@ -144,15 +144,32 @@ conv_fwd_kernel(const float* __restrict__ x, const float* __restrict__ wgt, floa
 
 }  // namespace
 
-extern "C" int sb_conv_fwd(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co,
-                           int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T,
-                           void* stream) {
+namespace sb {
+int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W,
+                int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, cudaStream_t st, bool* taken);
+}
+
+extern "C" int sb_conv_fwd_path(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co,
+                                int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T,
+                                int path, void* stream) {
+  SB_REQUIRE(path >= -1 && path <= 1, "path is -1 (automatic), 0 (fp32 kernel) or 1 (tensor cores)");
   SB_REQUIRE(N >= 0 && Ci >= 1 && Co >= 1 && H >= 0 && W >= 0 && T >= 0, "bad geometry");
   SB_REQUIRE(kh >= 1 && kw >= 1 && ph >= 0 && pw >= 0, "bad kernel geometry");
   const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
   SB_REQUIRE(Ho >= 0 && Wo >= 0, "kernel larger than the padded input");
   if (N * Co * Ho * Wo * T == 0) return SB_OK;
   SB_REQUIRE(x && weight && y, "null tensor pointer");
+  const bool aligned = ((((uintptr_t)x) | ((uintptr_t)y)) & 15u) == 0;
+  if (path == 1 || (path == -1 && aligned && sb_conv_uses_tensor_cores(N, Ci, Co, H, W, kh, kw, ph, pw, T))) {
+    // implicit GEMM on the tensor cores (api_conv_tc.cu)
+    bool taken = false;
+    SB_TRY(conv_tc_try(x, weight, y, N, Ci, Co, H, W, kh, kw, ph, pw, T, (cudaStream_t)stream, &taken));
+    if (taken) return SB_OK;
+    if (path == 1) {
+      set_error("the tensor-core convolution does not take this geometry or alignment");
+      return SB_ERR_UNSUPPORTED;
+    }
+  }
   SB_REQUIRE(N * Ho <= 65535 * 32767LL && H < (1 << 20) && W < (1 << 20) && T < (1 << 24) && Ci * kh * kw < (1 << 20),
              "geometry too large");
   const size_t smem = sizeof(float) * (size_t)(Ci * kh * kw) * kCoTile;
@@ -179,4 +196,10 @@ extern "C" int sb_conv_fwd(const float* x, const float* weight, float* y, int64_
 #undef SB_GO
   SB_CUDA(cudaGetLastError());
   return SB_OK;
+}
+
+extern "C" int sb_conv_fwd(const float* x, const float* weight, float* y, int64_t N, int64_t Ci, int64_t Co,
+                           int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T,
+                           void* stream) {
+  return sb_conv_fwd_path(x, weight, y, N, Ci, Co, H, W, kh, kw, ph, pw, T, -1, stream);
 }

@@ -50,6 +50,7 @@
 // ends all other waits at once, SB_DEV_TMA_TIMEOUT is recorded, and the CTA
 // waits (bounded) for loads and MMAs in flight, frees its TMEM and returns.
 #include "api_util.cuh"
+#include "tc.cuh"
 
 using namespace sb;
 
@@ -64,7 +65,6 @@ constexpr int kAccCols = 2 * kN;         // hi*hi + lo*hi | hi*lo
 constexpr int kColAhi = 2 * kAccCols;            // 128
 constexpr int kColAlo = kColAhi + kARing * kN;   // 320
 constexpr int kTmemCols = 512;
-constexpr uint32_t kTf32Mask = 0xffffe000u;
 
 // warps: split 0-3, drain 4-7, two issue warps, producer warp
 constexpr int kIssueWarp = 8, kProdWarp = 10;
@@ -82,86 +82,7 @@ constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(kColAlo + kARing * kN == kTmemCols, "TMEM column budget");
 
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address and
-// offsets in 16-byte units, 8-row groups 1024 bytes apart, descriptor version 1.
-// Only the low word depends on the address.
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3ffffu) >> 4) | (1u << 16); }
-// Instruction descriptor: D = f32, A = B = tf32, both K-major, M = 128.
-__host__ __device__ constexpr uint32_t idesc_n(int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
-}
-
-// D[tmem] (+)= A[tmem] * B[smem]^T: A is 128 lanes x 8 columns of TF32.
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "mov.b64 db, {%2, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// Bounded wait that also gives up as soon as any thread of the CTA has given up
-// (the dead flag), so that one lost transfer costs one time-out, not one per wait.
-__device__ __forceinline__ bool wait_or_dead(uint32_t bar, uint32_t parity, volatile int* dead) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) {
-      if (*dead) return false;
-      __nanosleep(it > 4096 ? 256 : 32);
-    }
-  }
-  *dead = 1;
-  return false;
-}
-
-#define SB_R32(r)                                                                                                  \
-  r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15], r[16],     \
-      r[17], r[18], r[19], r[20], r[21], r[22], r[23], r[24], r[25], r[26], r[27], r[28], r[29], r[30], r[31]
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Nearest TF32 value, low 13 bits zero (so the tensor core reads it exactly).
-__device__ __forceinline__ uint32_t tf32_rn(float v) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-  return r & kTf32Mask;
-}
+__host__ __device__ constexpr uint32_t idesc_n(int n) { return idesc_tf32(kM, n); }
 
 __global__ void __launch_bounds__(kThreads, 1)
 fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ x, const float* __restrict__ filt,

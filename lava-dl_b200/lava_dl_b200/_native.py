@@ -79,6 +79,9 @@ SIGNATURES = {
     'sb_pool_fwd': (c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P]),
     'sb_pool_bwd': (c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P]),
     'sb_conv_fwd': (c_int, [_P, _P, _P] + [_I64] * 10 + [_P]),
+    'sb_conv_fwd_path': (c_int, [_P, _P, _P] + [_I64] * 10 + [c_int, _P]),
+    'sb_conv_uses_tensor_cores': (c_int, [_I64] * 10),
+    'sb_conv_fits_tensor_cores': (c_int, [_I64] * 10),
     'sb_conv_wgrad_scratch_bytes': (_I64, [_I64] * 7),
     'sb_conv_wgrad': (c_int, [_P, _P, _P, _P] + [_I64] * 10 + [_P]),
     'sb_broadcast_fill': (c_int, [_P, _P, _I64, _P]),

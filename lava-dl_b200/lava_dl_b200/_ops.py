@@ -648,18 +648,27 @@ def pool_bwd(grad_y, weight, in_shape):
 
 
 def conv_fwd_supported(x, weight, stride, padding, dilation, groups):
-    """The direct convolution kernel covers stride 1, dilation 1, one group."""
+    """``sb_conv_fwd`` covers stride 1, dilation 1, one group: on the tensor cores for 1x1, 3x3 and
+    5x5 kernels with T % 4 == 0, through the fp32 kernel for the other shapes it can launch."""
     if not (x.is_cuda and x.dim() == 5 and x.dtype == torch.float32):
         return False
     if tuple(stride) != (1, 1, 1) or tuple(dilation) != (1, 1, 1) or groups != 1 or padding[2] != 0:
         return False
     n, ci, h, w, t = x.shape
-    ho = h + 2 * padding[0] - weight.shape[2] + 1
-    return 0 < n * ho <= 65535 and ci * weight.shape[2] * weight.shape[3] * 16 * 4 <= 96 * 1024
+    kh, kw = int(weight.shape[2]), int(weight.shape[3])
+    ho = h + 2 * padding[0] - kh + 1
+    if ho <= 0 or w + 2 * padding[1] - kw + 1 <= 0:
+        return False
+    if x.data_ptr() % 16 == 0 and N.load().sb_conv_fits_tensor_cores(
+            n, ci, int(weight.shape[0]), h, w, kh, kw, int(padding[0]), int(padding[1]), t):
+        return True   # tcgen05 implicit GEMM
+    # limits of the fp32 kernel: its launch grid and the weights of 16 output channels in shared memory
+    return 0 < n * ho <= 65535 and ci * kh * kw * 16 * 4 <= 96 * 1024
 
 
-def conv_fwd(x, weight, padding):
-    """x: [N, Ci, H, W, T]; weight: [Co, Ci, kh, kw, 1] (already hooked); padding (ph, pw)."""
+def conv_fwd(x, weight, padding, path=-1):
+    """x: [N, Ci, H, W, T]; weight: [Co, Ci, kh, kw, 1] (already hooked); padding (ph, pw).
+    ``path``: -1 lets the library choose, 0 forces the fp32 kernel, 1 the tensor cores."""
     N.require_cuda(x)
     x = _c(x)
     n, ci, h, w, t = x.shape
@@ -667,7 +676,13 @@ def conv_fwd(x, weight, padding):
     wgt = _c(weight.detach().to(device=x.device, dtype=torch.float32).reshape(co, -1))
     ph, pw = int(padding[0]), int(padding[1])
     y = torch.empty((n, co, h + 2 * ph - kh + 1, w + 2 * pw - kw + 1, t), device=x.device, dtype=torch.float32)
-    N.call('sb_conv_fwd', x, N.ptr(x), N.ptr(wgt), N.ptr(y), n, ci, co, h, w, kh, kw, ph, pw, t, N.stream_of(x))
+    if path == -1:
+        # shapes only the tensor-core kernel can launch (more than 65535 output rows, wide layers)
+        fp32_ok = 0 < n * y.shape[2] <= 65535 and ci * kh * kw * 16 * 4 <= 96 * 1024
+        if not fp32_ok:
+            path = 1
+    N.call('sb_conv_fwd_path', x, N.ptr(x), N.ptr(wgt), N.ptr(y), n, ci, co, h, w, kh, kw, ph, pw, t, int(path),
+           N.stream_of(x))
     return y
 
 
@@ -699,4 +714,10 @@ def conv_dgrad(grad_y, weight, padding):
     kh, kw = weight.shape[2], weight.shape[3]
     wt = weight.detach()[:, :, :, :, 0] if weight.dim() == 5 else weight.detach()
     wt = wt.flip(2, 3).transpose(0, 1).contiguous()
-    return conv_fwd(grad_y, wt, (kh - 1 - int(padding[0]), kw - 1 - int(padding[1])))
+    # gradients are not exact in TF32, so the tensor-core kernel would run its three-product form:
+    # measured slower than the fp32 kernel on the benchmark network, which therefore takes the
+    # latter whenever it can launch the shape
+    pad = (kh - 1 - int(padding[0]), kw - 1 - int(padding[1]))
+    n, co, ho = grad_y.shape[0], grad_y.shape[1], grad_y.shape[2]
+    fp32_ok = 0 < n * (ho + 2 * pad[0] - kh + 1) <= 65535 and co * kh * kw * 16 * 4 <= 96 * 1024
+    return conv_fwd(grad_y, wt, pad, path=0 if fp32_ok else -1)

@@ -121,7 +121,13 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
                                             ((3, 1, 4, 4, 1), 2, 1, 0),
                                             # forward fits the kernel, the swapped (input-gradient) problem does not:
                                             # 200 output channels x 9 taps of weights, and N * H = 66000 rows
-                                            ((1, 4, 6, 6, 8), 200, 3, 1), ((2200, 1, 30, 3, 4), 2, (3, 1), (0, 0))])
+                                            ((1, 4, 6, 6, 8), 200, 3, 1), ((2200, 1, 30, 3, 4), 2, (3, 1), (0, 0)),
+                                            # tensor-core shapes: two chunks of input channels; 5 x 5 with a ragged
+                                            # last time chunk; two groups of output channels with a partial one and
+                                            # a width that is no multiple of four; 1 x 1; a partial channel chunk
+                                            ((2, 16, 6, 6, 64), 32, 3, 1), ((1, 2, 9, 10, 44), 16, 5, 2),
+                                            ((2, 16, 5, 7, 32), 70, 3, 1), ((2, 24, 3, 5, 96), 24, 1, 0),
+                                            ((1, 11, 4, 9, 36), 5, 3, 0), ((3, 3, 12, 12, 300), 8, 5, 1)])
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
@@ -138,6 +144,15 @@ def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     xb = x.clone().requires_grad_(True)
     fast = conv(xa)
     assert 'SpikeConv' in type(fast.grad_fn).__name__
+    from lava_dl_b200 import _native, _ops
+    geo = (shape[0], shape[1], co, shape[2], shape[3], *conv.kernel_size[:2], *conv.padding[:2], shape[-1])
+    fits = _native.load().sb_conv_fits_tensor_cores(*geo) == 1
+    assert fits == (shape[-1] % 4 == 0 and shape[-1] >= 32)
+    if fits:
+        # both kernels on the same spikes: identical sums
+        w = conv._hooked_weight()
+        assert_exact(_ops.conv_fwd(x, w, conv.padding, path=1), _ops.conv_fwd(x, w, conv.padding, path=-1),
+                     'tensor-core kernel against the automatic choice')
     slow = F.conv3d(xb, conv.weight, None, conv.stride, conv.padding, conv.dilation, conv.groups)
     assert_exact(fast, slow, 'convolution of spikes')
     g = torch.randint(-8, 8, fast.shape, generator=gen).float().to(cuda) / 4
@@ -147,7 +162,20 @@ def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     xf = torch.randn(shape, generator=gen).to(cuda)
     with torch.backends.cudnn.flags(allow_tf32=False):
         want = F.conv3d(xf, conv.weight, None, conv.stride, conv.padding)
-    assert_close(conv(xf), want, 'convolution of floats')
+    # float operands: 1e-5 of the sum of the term magnitudes (the tensor-core path adds three TF32
+    # products per term, each within 2^-21 of the term; plain relative error where nothing cancels)
+    with torch.backends.cudnn.flags(allow_tf32=False):
+        mag = F.conv3d(xf.abs(), conv.weight.detach().abs(), None, conv.stride, conv.padding)
+    assert_close(conv(xf), want, 'convolution of floats', scale=mag.cpu().numpy())
+    if fits:
+        assert_close(_ops.conv_fwd(xf, conv._hooked_weight(), conv.padding, path=1), want,
+                     'convolution of floats, tensor cores', scale=mag.cpu().numpy())
+        wf = torch.randn(conv.weight.shape, generator=gen).to(cuda)   # weights off the TF32 grid as well
+        with torch.backends.cudnn.flags(allow_tf32=False):
+            want2 = F.conv3d(xf, wf, None, conv.stride, conv.padding)
+            mag2 = F.conv3d(xf.abs(), wf.abs(), None, conv.stride, conv.padding)
+        assert_close(_ops.conv_fwd(xf, wf, conv.padding, path=1), want2,
+                     'convolution of floats with float weights, tensor cores', scale=mag2.cpu().numpy())
     # gradients on float data against float64 on the CPU: 1e-5 of the sum of the term magnitudes
     xd = xf.double().cpu().requires_grad_(True)
     wd = conv.weight.detach().double().cpu().requires_grad_(True)
