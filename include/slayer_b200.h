@@ -90,8 +90,10 @@ int sb_li_bwd(const float* grad_y, const float* y, const float* decay, int64_t n
  * on every GPU that loads it.  Limits: shared decay up to 32 * (capacity/8 - 64)
  * rows; per-channel decay rows + 64 * n_decay <= capacity/8.  Larger problems
  * return SB_ERR_INVALID_ARG.  The first call on a device looks the array up
- * (do it outside stream capture).  Calls share the array: calls overlapping on
- * the GPU race.  Allocates nothing. */
+ * (do it outside stream capture; the per-device lookup is safe to race from several
+ * threads).  Calls share the array: calls overlapping on the GPU race.  If
+ * sb_device_status reports SB_DEV_TMA_TIMEOUT after a call, that call's grad_x and
+ * grad_decay are incomplete.  Allocates nothing. */
 #define SB_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
 int sb_li_bwd_noalloc(const float* grad_y, const float* y, const float* decay, int64_t n_decay, float* grad_x,
                       float* grad_decay, const sb_geom* g, void* stream);

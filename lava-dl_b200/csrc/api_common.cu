@@ -6,6 +6,8 @@
 #include <string.h>
 #include <limits.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "rowscan.cuh"
 #include "reduce.cuh"
@@ -34,8 +36,11 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ---------------------------------------------------------------------------
 __device__ unsigned int g_dev_status = 0;
 
+// Host-side caches are filled lazily and may be reached from several threads at once (autograd
+// runs backward passes on worker threads): every cached value is the same whoever computes it, so
+// the slots are atomics with release / acquire ordering and a lost race only repeats the lookup.
 static constexpr int kMaxDev = 64;
-static unsigned int* g_status_ptr[kMaxDev] = {nullptr};
+static std::atomic<unsigned int*> g_status_ptr[kMaxDev];
 
 unsigned int* status_ptr() {
   int dev = 0;
@@ -43,16 +48,18 @@ unsigned int* status_ptr() {
     set_error("no usable CUDA device (cudaGetDevice failed)");
     return nullptr;
   }
-  if (!g_status_ptr[dev]) {
+  unsigned int* cached = g_status_ptr[dev].load(std::memory_order_acquire);
+  if (!cached) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_dev_status);
     if (e != cudaSuccess) {
       cuda_fail(e, "cudaGetSymbolAddress(g_dev_status)");
       return nullptr;
     }
-    g_status_ptr[dev] = (unsigned int*)p;
+    cached = (unsigned int*)p;
+    g_status_ptr[dev].store(cached, std::memory_order_release);
   }
-  return g_status_ptr[dev];
+  return cached;
 }
 
 // ---------------------------------------------------------------------------
@@ -62,17 +69,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static EncodeTiledFn resolve_encode_fn() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    return (EncodeTiledFn)p;
+  return nullptr;
+}
+
 static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
+  static const EncodeTiledFn fn = resolve_encode_fn();   // initialised once, thread-safe since C++11
   return fn;
 }
 
@@ -106,19 +113,19 @@ static void bind_primary_context() {
   static CtxSetCurrentFn set_cur = (CtxSetCurrentFn)driver_fn("cuCtxSetCurrent");
   static PrimaryRetainFn retain = (PrimaryRetainFn)driver_fn("cuDevicePrimaryCtxRetain");
   static DeviceGetFn dev_get = (DeviceGetFn)driver_fn("cuDeviceGet");
-  static CUcontext primary[kMaxDev] = {nullptr};
+  static std::atomic<CUcontext> primary[kMaxDev];
   if (!get_cur || !set_cur || !retain || !dev_get) return;
   CUcontext cur = nullptr;
   if (get_cur(&cur) == CUDA_SUCCESS && cur != nullptr) return;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return;
-  if (!primary[dev]) {
+  CUcontext ctx = primary[dev].load(std::memory_order_acquire);
+  if (!ctx) {
     CUdevice cd;
-    CUcontext ctx = nullptr;
     if (dev_get(&cd, dev) != CUDA_SUCCESS || retain(&ctx, cd) != CUDA_SUCCESS) return;
-    primary[dev] = ctx;
+    primary[dev].store(ctx, std::memory_order_release);
   }
-  set_cur(primary[dev]);
+  set_cur(ctx);
 }
 
 // L2 fetches 256 bytes per missed 128-byte tile row: the next tile of the same
@@ -220,21 +227,25 @@ struct DevInfo {
   bool ok;
 };
 static DevInfo g_dev[kMaxDev];
+static std::atomic<bool> g_dev_ready[kMaxDev];
 
 static const DevInfo& dev_info() {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= kMaxDev) dev = 0;
   DevInfo& d = g_dev[dev];
-  if (!d.ok) {
+  if (!g_dev_ready[dev].load(std::memory_order_acquire)) {
+    DevInfo n;
     int v = 0;
-    d.sms = 148; d.smem_per_sm = 228 * 1024; d.smem_per_block_optin = 227 * 1024;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) d.sms = v;
+    n.sms = 148; n.smem_per_sm = 228 * 1024; n.smem_per_block_optin = 227 * 1024;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n.sms = v;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess && v > 0)
-      d.smem_per_sm = (size_t)v;
+      n.smem_per_sm = (size_t)v;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0)
-      d.smem_per_block_optin = (size_t)v;
-    d.ok = true;
+      n.smem_per_block_optin = (size_t)v;
+    n.ok = true;
+    d = n;   // racing threads write the same values
+    g_dev_ready[dev].store(true, std::memory_order_release);
   }
   return d;
 }
@@ -290,24 +301,27 @@ int64_t scratch_slots(int64_t rows, int64_t n) {
 
 __global__ void fold_stage1(const double* __restrict__ partial, double* __restrict__ stage, RowGeom g, int64_t n,
                             int64_t nparts) {
-  // grid: (slices, n).  Block (s, c) sums the partials of channel c that fall in slice s.
-  const int64_t c = blockIdx.y;
+  // grid: (slices, min(n, 65535)).  Block (s, c) sums the partials of channel c that fall in slice s;
+  // with more channels than the grid's second dimension allows a block takes every gridDim.y-th one.
   const int s = blockIdx.x;
-  double acc = 0.0;
-  if (n <= 1) {
-    for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < nparts; i += (int64_t)gridDim.x * blockDim.x)
-      acc += partial[i];
-  } else {
-    // rows of channel c: for each batch b, [b*rpb + c*blk, b*rpb + (c+1)*blk)
-    const int64_t batches = g.rows / g.rows_per_batch;
-    const int64_t per = batches * g.decay_block;
-    for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < per; i += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t b = i / g.decay_block, j = i - b * g.decay_block;
-      acc += partial[b * g.rows_per_batch + c * g.decay_block + j];
+  for (int64_t c = blockIdx.y; c < (n < 1 ? 1 : n); c += gridDim.y) {
+    double acc = 0.0;
+    if (n <= 1) {
+      for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < nparts; i += (int64_t)gridDim.x * blockDim.x)
+        acc += partial[i];
+    } else {
+      // rows of channel c: for each batch b, [b*rpb + c*blk, b*rpb + (c+1)*blk)
+      const int64_t batches = g.rows / g.rows_per_batch;
+      const int64_t per = batches * g.decay_block;
+      for (int64_t i = (int64_t)s * blockDim.x + threadIdx.x; i < per; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / g.decay_block, j = i - b * g.decay_block;
+        acc += partial[b * g.rows_per_batch + c * g.decay_block + j];
+      }
     }
+    acc = block_sum(acc);
+    if (threadIdx.x == 0) stage[c * gridDim.x + s] = acc;
+    __syncthreads();   // block_sum's shared slots are reused by the next channel
   }
-  acc = block_sum(acc);
-  if (threadIdx.x == 0) stage[c * gridDim.x + s] = acc;
 }
 
 __global__ void fold_stage2(const double* __restrict__ stage, float* __restrict__ out, int slices, int64_t n) {
@@ -325,7 +339,7 @@ int fold_param_grad(double* scratch, float* out, const RowGeom& g, int64_t n, cu
   if (n < 1) n = 1;
   const int64_t nparts = (n <= 1) ? (g.rows + kTileR - 1) / kTileR : g.rows;
   double* stage = scratch + nparts;
-  dim3 grid1(kFoldSlices, (unsigned)n);
+  dim3 grid1(kFoldSlices, (unsigned)(n > 65535 ? 65535 : n));
   fold_stage1<<<grid1, 256, 0, st>>>(scratch, stage, g, n, nparts);
   SB_CUDA(cudaGetLastError());
   const int wpb = 4;

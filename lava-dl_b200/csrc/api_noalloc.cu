@@ -26,12 +26,18 @@
 //  * All calls on one device share the one array, and it keeps whatever the
 //    previous call left in it.  Nothing in it has to start at zero: every slot
 //    that is read has been written earlier in the same call (each warp or row
-//    writes its partial before the fold reads it, the fold writes its stage
-//    slots before summing them), so no clearing pass is issued.
+//    writes its partial before the fold reads it -- also a warp that gave up
+//    waiting for a tile and set SB_DEV_TMA_TIMEOUT, whose partial then covers
+//    only the steps it walked -- and the fold writes its stage slots before
+//    summing them), so no clearing pass is issued.  After any call check
+//    sb_device_status: with SB_DEV_TMA_TIMEOUT set, grad_x and grad_decay of
+//    that call are incomplete.
 //  * Two calls that overlap on the GPU (different streams, or different host
 //    threads on different streams) race on the array and produce garbage in
 //    grad_decay.  Serialise them on one stream or with events.
 //  * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+#include <atomic>
+
 #include "api_util.cuh"
 #include "reduce.cuh"
 #include "rowscan.cuh"
@@ -43,7 +49,9 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[SB_NOALLOC_SCRA
 namespace {
 
 constexpr int kMaxDevices = 64;
-double* g_scratch_dev_ptr[kMaxDevices] = {nullptr};
+// One slot per device ordinal.  Threads may race to fill a slot; they all store the same address
+// (release / acquire), so the race only repeats the lookup.
+std::atomic<double*> g_scratch_dev_ptr[kMaxDevices];
 
 // In host code `g_noalloc_scratch` is only a handle for the symbol, not an
 // address a kernel could use; the address on the current device comes from the
@@ -52,13 +60,15 @@ int noalloc_scratch(double** out) {
   int dev = -1;
   SB_CUDA(cudaGetDevice(&dev));
   SB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside [0, %d)", dev, kMaxDevices);
-  if (g_scratch_dev_ptr[dev] == nullptr) {
+  double* cached = g_scratch_dev_ptr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     SB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
     SB_REQUIRE(p != nullptr && (((uintptr_t)p) & 255u) == 0, "built-in scratch has an unusable address %p", p);
-    g_scratch_dev_ptr[dev] = (double*)p;
+    cached = (double*)p;
+    g_scratch_dev_ptr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_scratch_dev_ptr[dev];
+  *out = cached;
   return SB_OK;
 }
 

@@ -334,14 +334,15 @@ __device__ __forceinline__ void rowscan_tma_body(const MapPack<Op::NIN + Op::NOU
 
   if (lane == 0) tma_wait_all<0>();
   if (!ok) {
-    // A load never arrived.  Record it, drain what this warp still has in
-    // flight (bounded), and leave without touching per-row outputs.
+    // A load never arrived.  Record it and drain what this warp still has in flight (bounded).
+    // The per-row results below are then those of a walk that stopped early: the status bit says
+    // so, and every slot a later pass reads (parameter-gradient partials) is still written.
     if (lane == 0) {
       dev_flag(status, SB_DEV_TMA_TIMEOUT);
       const int last = (k + STAGES - 1 < ntiles) ? k + STAGES - 1 : ntiles;
       for (int kk = k + 1; kk < last; ++kk) (void)mbar_wait(bar0 + (kk % STAGES) * 8, (kk / STAGES) & 1);
     }
-    return;
+    __syncwarp();
   }
   op.finish(p, g, row, valid, lane, warp_id);
 }

@@ -1,6 +1,5 @@
-"""Blocks: synapse + neuron + delay (mirror of ``lava.lib.dl.slayer.block`` for
-the real-valued neuron families)."""
+"""Blocks: synapse + neuron + delay (mirror of ``lava.lib.dl.slayer.block``)."""
 
-from . import base, cuba, alif, sigma_delta
+from . import base, cuba, alif, rf, adrf, rf_iz, adrf_iz, sigma_delta
 
-__all__ = ['base', 'cuba', 'alif', 'sigma_delta']
+__all__ = ['base', 'cuba', 'alif', 'rf', 'adrf', 'rf_iz', 'adrf_iz', 'sigma_delta']

@@ -42,7 +42,11 @@ class _Block(torch.nn.Module):
         """``NCT`` or ``NCHWT`` input -> spikes (and event rate when ``count_log``)."""
         mask = getattr(self, 'mask', None)
         if mask is not None:
-            self.synapse.weight.data *= mask
+            if self.synapse.complex is True:
+                self.synapse.real.weight.data *= mask
+                self.synapse.imag.weight.data *= mask
+            else:
+                self.synapse.weight.data *= mask
         z = self.synapse(x)
         if self.delay_shift is True and getattr(self.neuron, 'fuses_step_delay', False):
             # a bounded axonal delay (at most 62 steps) is written by the neuron kernel as well
@@ -84,6 +88,74 @@ class _Block(torch.nn.Module):
     @property
     def shape(self):
         return self.neuron.shape
+
+
+class AbstractInput(torch.nn.Module):
+    """Input block (``block/base.py:42-137``): an optional learnable affine transform of the input,
+    both factors passed through the neuron's weight quantiser, then the neuron and the one-step delay.
+
+    Parameters
+    ----------
+    neuron_params : dict or None
+        ``None`` passes the input through (only the delay applies).
+    weight, bias : float or None
+    delay_shift, count_log : bool
+    """
+
+    def __init__(self, neuron_params=None, weight=None, bias=None, delay_shift=True, count_log=False):
+        super().__init__()
+        self.neuron_params = neuron_params
+        self.synapse_params = None
+        self.count_log = count_log
+        self.neuron = None
+        self.delay = None
+        for name, value in (('weight', weight), ('bias', bias)):
+            if value is not None:
+                self.register_parameter(name, torch.nn.Parameter(torch.FloatTensor([value]), requires_grad=True))
+            else:
+                setattr(self, name, None)
+        self.input_shape = None
+        self.pre_hook_fx = lambda x: x
+        self.delay_shift = delay_shift
+
+    def forward(self, x):
+        if self.neuron is not None:
+            z = self.pre_hook_fx(x)
+            if self.weight is not None:
+                z = z * self.pre_hook_fx(self.weight)
+            if self.bias is not None:
+                z = z + self.pre_hook_fx(self.bias)
+            x = self.neuron(z)
+        if self.delay_shift is True:
+            x = step_delay(self, x)
+        if self.input_shape is None:
+            self.input_shape = self.neuron.shape if self.neuron is not None else x.shape[1:-1]
+        if self.count_log is True:
+            return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    @property
+    def shape(self):
+        return self.neuron.shape if self.neuron is not None else self.input_shape
+
+
+class AbstractAverage(torch.nn.Module):
+    """Population average (``block/base.py:210-259``): the mean over groups of
+    ``neurons / num_outputs`` consecutive neurons, per time step."""
+
+    def __init__(self, num_outputs, count_log=False):
+        super().__init__()
+        self.count_log = count_log
+        self.num_outputs = num_outputs
+
+    def forward(self, x):
+        N, T = x.shape[0], x.shape[-1]
+        mean = torch.mean(x.reshape((N, self.num_outputs, -1, T)), dim=2)
+        return (mean, None) if self.count_log is True else mean
+
+    @property
+    def shape(self):
+        return torch.Size([self.num_outputs, 1, 1])
 
 
 class AbstractDense(_Block):
@@ -207,6 +279,80 @@ class AbstractRecurrent(torch.nn.Module):
             x = delay(x, 1)
         if self.delay is not None:
             x = self.delay(x)
+        if self.count_log is True:
+            return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    @property
+    def shape(self):
+        return self.neuron.shape
+
+
+
+class AbstractKWTA(torch.nn.Module):
+    """K-winner-takes-all block (``block/base.py:1222-1364``):
+    ``s[t] = neuron(W x[t] + R s[t-1] + alpha (N - 2K))`` with the fixed lateral matrix
+    ``R = (1 + a) I - 1`` (self excitation ``a``, everybody else inhibits) on the weight grid of
+    the neuron.  The walk over time is the recurrent one (``utils.recurrent``).
+
+    Parameters
+    ----------
+    neuron_params : dict
+    in_neurons, out_neurons, num_winners : int
+    self_excitation : float
+    weight_scale, weight_norm, pre_hook_fx : synapse options
+    delay_shift : bool
+    requires_grad : bool
+        learnable self excitation.
+    count_log : bool
+    """
+
+    def __init__(self, neuron_params, in_neurons, out_neurons, num_winners, self_excitation=0.5, weight_scale=1,
+                 weight_norm=False, pre_hook_fx=None, delay_shift=True, requires_grad=True, count_log=False):
+        super().__init__()
+        self.neuron_params = dict(neuron_params, persistent_state=True)
+        self.synapse_params = dict(in_neurons=in_neurons, out_neurons=out_neurons, weight_scale=weight_scale,
+                                   weight_norm=weight_norm, pre_hook_fx=pre_hook_fx)
+        self.num_neurons = out_neurons
+        self.num_winners = num_winners
+        self.requires_grad = requires_grad
+        self.register_parameter('self_excitation', torch.nn.Parameter(torch.FloatTensor([self_excitation]),
+                                                                      requires_grad=requires_grad))
+        self.count_log = count_log
+        self.neuron = None
+        self.synapse = None
+        self.delay = None
+        self.bias = None
+        self.register_buffer('spike_state', torch.zeros(1, dtype=torch.float))
+        self.persistent_state = True
+        self.delay_shift = delay_shift
+
+    def clamp(self):
+        self.self_excitation.data.clamp_(0, 1)
+
+    def forward(self, x):
+        """``NCT`` input -> spikes (and event rate when ``count_log``)."""
+        from ..utils import recurrent
+        z = self.synapse(x)
+        if self.bias is not None:
+            z = z + self.bias
+        if isinstance(z, (tuple, list)):
+            # the reference allocates zeros_like(z) for its output (block/base.py:1323): a complex
+            # synapse's (real, imaginary) pair fails there in the same way
+            raise TypeError('zeros_like(): argument \'input\' (position 1) must be Tensor, not tuple')
+        self.clamp()
+        recurrent_weight = (1 + self.self_excitation) * torch.eye(self.num_neurons, device=z.device) - 1
+        recurrent_bias = self.neuron.threshold * (self.num_neurons - 2 * self.num_winners) \
+            / self.num_neurons / self.neuron.w_scale
+        recurrent_bias = torch.FloatTensor([recurrent_bias]).to(z.device)
+        if self.neuron.quantize_8bit is not None:
+            recurrent_weight = self.neuron.quantize_8bit(recurrent_weight)
+            recurrent_bias = self.neuron.quantize_8bit(recurrent_bias)
+        # the spike fed back at t = 0 is zero: the reference never stores a spike state
+        # (block/base.py:1352), only the neuron state survives between calls
+        x = recurrent.recurrent_walk(z + recurrent_bias, self.neuron, recurrent_weight)
+        if self.delay_shift is True:
+            x = step_delay(self, x)
         if self.count_log is True:
             return x, torch.mean((x > 0).to(x.dtype))
         return x

@@ -4,7 +4,9 @@ unless asked for, ``sigma_delta.py:24-29``) and the delta-encoding input block."
 
 import torch
 
+from . import base
 from ._family import make_blocks
+from .. import synapse
 from ..neuron import sigma_delta
 
 Dense, Conv, Pool, Flatten = make_blocks(sigma_delta.Neuron, default_delay_shift=False)
@@ -61,4 +63,40 @@ class Input(torch.nn.Module):
         return self.input_shape
 
 
-__all__ = ['Input', 'Dense', 'Conv', 'Pool', 'Flatten']
+class Average(base.AbstractAverage):
+    __doc__ = base.AbstractAverage.__doc__
+
+
+class Output(torch.nn.Module):
+    """Output block (``sigma_delta.py:168-220``): a dense synapse on the neuron's weight grid
+    followed by the neuron's sigma decoder, so that the network returns the accumulated signal
+    instead of its changes.
+
+    Parameters
+    ----------
+    neuron_params : dict
+    in_neurons, out_neurons : int
+    weight_scale : int
+    weight_norm, count_log : bool
+    """
+
+    def __init__(self, neuron_params, in_neurons, out_neurons, weight_scale=1, weight_norm=False, count_log=False):
+        super().__init__()
+        self.neuron = sigma_delta.Neuron(**neuron_params)
+        self.delay = None
+        self.synapse = synapse.Dense(in_neurons, out_neurons, weight_scale=weight_scale, weight_norm=weight_norm,
+                                     pre_hook_fx=self.neuron.quantize_8bit)
+        self.count_log = count_log
+
+    def forward(self, x):
+        x = self.neuron.sigma(self.synapse(x))
+        if self.count_log is True:
+            return x, torch.mean((x > 0).to(x.dtype))
+        return x
+
+    @property
+    def shape(self):
+        return self.neuron.sigma.shape
+
+
+__all__ = ['Input', 'Dense', 'Conv', 'Pool', 'Flatten', 'Average', 'Output']

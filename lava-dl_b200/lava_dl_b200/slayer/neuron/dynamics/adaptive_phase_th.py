@@ -11,7 +11,11 @@ def dynamics(re_input, im_input, im_state, ref_state, ref_decay, th_state, th_de
              debug=False):
     """Threshold and refractory traces of a resonator that spikes when the real
     part exceeds ``threshold + refractory`` while the imaginary part crosses
-    zero upwards.  Returns ``(threshold, refractory)``; no gradient."""
+    zero upwards.  Returns ``(threshold, refractory)``; no gradient.
+
+    ``debug=True`` does not run a second implementation (there is none to compare with): it checks that the
+    scaled states are integers below 2^30 in magnitude and that the device status word is clean.
+    """
     threshold, refractory = _APTHDynamics.apply(
         re_input, im_input, im_state, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)
     if debug:

@@ -13,7 +13,11 @@ def dynamics(real_input, imag_input, sin_decay, cos_decay, ref_decay, th_decay, 
     """Resonator plus adaptive threshold / refractory traces in one recurrence;
     the spike condition is ``imag >= threshold + refractory`` and the resonator
     state is not reset.  Returns ``(real, imag, threshold, refractory)``;
-    gradients flow to the inputs and to ``sin_decay`` / ``cos_decay``."""
+    gradients flow to the inputs and to ``sin_decay`` / ``cos_decay``.
+
+    ``debug=True`` does not run a second implementation (there is none to compare with): it checks that the
+    scaled states are integers below 2^30 in magnitude and that the device status word is clean.
+    """
     out = _AdResDynamics.apply(
         real_input, imag_input, sin_decay, cos_decay, ref_decay, th_decay, real_state, imag_state, ref_state,
         th_state, th_scale, th0, w_scale)

@@ -22,6 +22,9 @@ def dynamics(input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_s
         \\vartheta[t] &= \\vartheta[t] + \\vartheta_{\\text{step}}
 
     Returns ``(threshold, refractory)``; no gradient flows through this op.
+
+    ``debug=True`` does not run a second implementation (there is none to compare with): it checks that the
+    scaled states are integers below 2^30 in magnitude and that the device status word is clean.
     """
     threshold, refractory = _ATHDynamics.apply(
         input, ref_state, ref_decay, th_state, th_decay, th_scale, th0, w_scale)

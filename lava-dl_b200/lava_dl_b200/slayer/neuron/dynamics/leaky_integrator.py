@@ -30,7 +30,8 @@ def dynamics(input, decay, state, w_scale, threshold=None, debug=False):
     threshold : float or None
         reset threshold; ``None`` means no reset.
     debug : bool
-        check result invariants (see ``_debug``).
+        no second implementation is run (there is none to compare with): checks that the scaled
+        states are integers below 2^30 in magnitude and that the device status word is clean.
 
     Returns
     -------

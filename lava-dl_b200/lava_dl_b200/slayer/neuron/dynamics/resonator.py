@@ -21,6 +21,9 @@ def dynamics(real_input, imag_input, sin_decay, cos_decay, real_state, imag_stat
     ``sin_decay``/``cos_decay`` are the products with ``(1-\\alpha)`` scaled by
     4096.  With a ``threshold`` the Izhikevich reset is applied where the
     imaginary part reaches it.  Returns ``(real, imag)``.
+
+    ``debug=True`` does not run a second implementation (there is none to compare with): it checks that the
+    scaled states are integers below 2^30 in magnitude and that the device status word is clean.
     """
     real, imag = _ResDynamics.apply(
         real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold, w_scale)

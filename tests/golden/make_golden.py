@@ -534,6 +534,87 @@ def main():
     xr4 = randn(2, 3, 2, 2)
     save('replicate', x2=xr2, out2=replicate(xr2, 5), x4=xr4, out4=replicate(xr4, 3))
 
+    # ------------------------------------------------------------------
+    # blocks of the other families and the per-time-step callers:
+    # ALIF recurrent block, winner-takes-all blocks, resonator networks with complex synapses,
+    # input / average / sigma-delta output blocks
+    # ------------------------------------------------------------------
+    alif_p = dict(threshold=1.0, threshold_step=0.5, current_decay=0.2, voltage_decay=0.05, threshold_decay=0.1,
+                  refractory_decay=0.1, requires_grad=True)
+    torch.manual_seed(8)
+    rec = slayer.block.alif.Recurrent(dict(alif_p), 12, 20, weight_scale=3)
+    xr = (rand(2, 12, 30) < 0.3).float()
+    xin = xr.clone().requires_grad_(True)
+    y1 = rec(xin)
+    g_r = randn(*y1.shape)
+    (y1 * g_r).sum().backward()
+    with torch.no_grad():
+        y2 = rec(xr)
+    save('block_alif_recurrent', x=xr, weight_in=rec.input_synapse.weight.data,
+         weight_rec=rec.recurrent_synapse.weight.data, out1=y1, grad_out=g_r, grad_x=xin.grad,
+         grad_weight_in=rec.input_synapse.weight.grad, grad_weight_rec=rec.recurrent_synapse.weight.grad, out2=y2)
+
+    cuba_p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03, requires_grad=True)
+    for fam, params, name in ((slayer.block.cuba, cuba_p, 'block_cuba_kwta'), (slayer.block.alif, alif_p, 'block_alif_kwta')):
+        torch.manual_seed(9)
+        kw = fam.KWTA(dict(params), 10, 16, 3, self_excitation=0.4, weight_scale=4, delay_shift=False)  # with the
+        # step delay the reference cannot be differentiated (in-place write into a custom function's output)
+        xk = (rand(3, 10, 28) < 0.4).float()
+        xin = xk.clone().requires_grad_(True)
+        y1 = kw(xin)
+        g_k = randn(*y1.shape)
+        (y1 * g_k).sum().backward()
+        with torch.no_grad():
+            y2 = kw(xk)
+        save(name, x=xk, weight=kw.synapse.weight.data, out1=y1, grad_out=g_k, grad_x=xin.grad,
+             grad_weight=kw.synapse.weight.grad, grad_self_excitation=kw.self_excitation.grad, out2=y2)
+        print(name, 'spike counts:', int(y1.sum()), int(y2.sum()))
+
+    # shared parameters: per-channel ones on NCHWT input fail to broadcast on the reference's CPU path
+    rf_p = dict(threshold=0.5, period=7, decay=0.1, requires_grad=True)
+    adrf_p = dict(threshold=0.5, threshold_step=0.25, period=7, decay=0.1, threshold_decay=0.1,
+                  refractory_decay=0.1, requires_grad=True)
+    for fam, params, name in ((slayer.block.rf, rf_p, 'network_rf'), (slayer.block.adrf, adrf_p, 'network_adrf')):
+        torch.manual_seed(10)
+        net = [fam.Conv(dict(params), 2, 4, 3, padding=1, weight_scale=3), fam.Pool(dict(params), 2, weight_scale=2),
+               fam.Flatten(), fam.Dense(dict(params), 4 * 3 * 3, 10, weight_scale=4, delay=True), fam.Average(5)]
+        xn = (rand(2, 2, 6, 6, 40) < 0.3).float()
+        xin = xn.clone().requires_grad_(True)
+        acts, y = {}, xin
+        for i, layer in enumerate(net):
+            y = layer(y)
+            acts[f'act{i}'] = y
+        g_n = randn(*y.shape)
+        (y * g_n).sum().backward()
+        arrays = dict(x=xn, grad_out=g_n, grad_x=xin.grad, delay=net[3].delay.delay.data, **acts)
+        for i in (0, 1, 3):
+            for part in ('real', 'imag'):
+                syn = getattr(net[i].synapse, part)
+                arrays[f'weight{i}_{part}'] = syn.weight.data
+                if syn.weight.grad is not None:
+                    arrays[f'grad_weight{i}_{part}'] = syn.weight.grad
+            for pname in ('sin_decay', 'cos_decay'):
+                arrays[f'{pname}{i}'] = getattr(net[i].neuron, pname).data
+        save(name, **arrays)
+        print(name, 'spike counts per layer:', [int((acts[f'act{i}'] != 0).sum()) for i in range(4)])
+
+    torch.manual_seed(11)
+    inp = slayer.block.cuba.Input(dict(cuba_p), weight=1.5, bias=0.2)
+    xi = randn(2, 7, 25, mean=0.5)
+    xin = xi.clone().requires_grad_(True)
+    yi = inp(xin)
+    g_i = randn(*yi.shape)
+    (yi * g_i).sum().backward()
+    save('block_cuba_input', x=xi, out=yi, grad_out=g_i, grad_x=xin.grad, grad_weight=inp.weight.grad,
+         grad_bias=inp.bias.grad)
+    torch.manual_seed(12)
+    sd_p = dict(threshold=0.1, activation=relu, tau_grad=0.5, scale_grad=1.0, requires_grad=False)
+    outb = slayer.block.sigma_delta.Output(dict(sd_p), 9, 4, weight_scale=3)
+    xo = (rand(2, 9, 20) < 0.3).float() * torch.round(rand(2, 9, 20) * 8) / 16
+    with torch.no_grad():
+        yo = outb(xo)
+    save('block_sdnn_output', x=xo, weight=outb.synapse.weight.data, out=yo)
+
     total = 0
     for name, arrays in cases.items():
         path = os.path.join(out_dir, name + '.npz')

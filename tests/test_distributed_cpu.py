@@ -79,3 +79,43 @@ def test_allreduce_is_a_no_op_without_a_process_group():
     p.grad = torch.tensor([0.5, 0.25])
     assert _dist.allreduce_param_grads([p]) == 2
     assert p.grad.tolist() == [0.5, 0.25]
+
+
+def _leaving_worker(rank, world, port, out_dir):
+    """Rank 1 leaves between steps (no collective in flight); rank 0 must get an error from its next
+    all-reduce within the group's timeout instead of waiting forever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    p = torch.nn.Parameter(torch.tensor([1.0]))
+    p.grad = torch.tensor([float(rank + 1)])
+    _dist.allreduce_param_grads([p])          # step 1: both ranks
+    assert p.grad.item() == 3.0
+    if rank == 1:
+        os._exit(0)                           # the rank is gone before step 2 starts
+    time.sleep(0.5)
+    t0 = time.time()
+    try:
+        p.grad = torch.tensor([1.0])
+        _dist.allreduce_param_grads([p])      # step 2: the peer never joins
+        outcome = 'returned'
+    except Exception as e:                    # gloo reports the closed connection or the timeout
+        outcome = 'raised ' + type(e).__name__
+    with open(os.path.join(out_dir, 'rank0.txt'), 'w') as f:
+        f.write(f'{outcome} {time.time() - t0:.1f}')
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_collective_with_an_error(tmp_path):
+    port = _free_port()
+    ctx = mp.get_context('spawn')
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=60)
+        assert not pr.is_alive(), 'a rank hung'
+    outcome, seconds = (tmp_path / 'rank0.txt').read_text().split(' ', 1)[0], (tmp_path / 'rank0.txt').read_text().rsplit(' ', 1)[1]
+    assert outcome == 'raised', (tmp_path / 'rank0.txt').read_text()
+    assert float(seconds) < 30

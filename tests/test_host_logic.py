@@ -161,8 +161,8 @@ def test_delay_fusable_bound():
 
 
 def test_recurrent_block_host_side():
-    """Construction mirrors block.cuba.Recurrent of the reference; there is no CPU path, other neuron
-    families are refused, and the input must be [batch, neurons, time]."""
+    """Construction mirrors block.cuba.Recurrent of the reference; there is no CPU path (a CPU tensor is
+    refused whichever walk would take it), and every family has its recurrent and winner-takes-all blocks."""
     import lava_dl_b200.slayer as slayer
     p = dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03)
     blk = slayer.block.cuba.Recurrent(p, 6, 8, weight_scale=2, delay=True)
@@ -173,10 +173,17 @@ def test_recurrent_block_host_side():
     with pytest.raises(RuntimeError, match='no CPU fallback'):
         blk(torch.zeros(2, 6, 5))
     alif = slayer.neuron.alif.Neuron(1.0, 0.1, 0.3, 0.1, 0.9, 0.9, persistent_state=True)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match='no CPU fallback'):   # the stepwise walk calls the same kernels
         slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 5), alif, blk.recurrent_synapse)
-    with pytest.raises(ValueError):
-        slayer.utils.recurrent.custom_recurrent(torch.zeros(2, 8, 1, 1, 5), blk.neuron, blk.recurrent_synapse)
+    for fam in ('cuba', 'alif', 'rf', 'adrf', 'rf_iz', 'adrf_iz'):
+        mod = getattr(slayer.block, fam)
+        assert set(mod.__all__) == {'Input', 'Flatten', 'Average', 'Dense', 'Conv', 'Pool', 'KWTA', 'Recurrent'}
+    kw = slayer.block.cuba.KWTA(p, 6, 8, 3, self_excitation=1.7)
+    kw.clamp()
+    assert float(kw.self_excitation) == 1.0 and kw.neuron.persistent_state is True
+    assert slayer.block.rf.Dense(dict(threshold=0.5, period=10, decay=0.1), 6, 4).synapse.complex is True
+    avg = slayer.block.cuba.Average(2)
+    assert torch.equal(avg(torch.arange(8.).reshape(1, 4, 2)), torch.tensor([[[1., 2.], [5., 6.]]]))
 
 
 def test_replicate_matches_reference():
