@@ -101,6 +101,21 @@ class Workload:
             return shape[0] * shape[-1] * CFG4_NEURONS
         return int(np.prod(shape))
 
+    def bytes(self, shape):
+        """Algorithmic bytes of one launch."""
+        n = int(np.prod(shape))
+        if self.name.startswith('pool_'):
+            return 4 * (n + n // 16)                       # 4 x 4 windows
+        if self.name in ('conv5_fwd',):
+            return 4 * (n + n // shape[1] * 16)            # 2 -> 16 channels
+        if self.name == 'conv3_fwd':
+            return 4 * (n + n // shape[1] * 32)            # 16 -> 32 channels
+        if self.name == 'conv3_dgrad':
+            return 4 * (n + n // shape[1] * 16)            # gradient of 32 channels -> 16 channels
+        if self.name == 'conv3_wgrad':
+            return 4 * (n + n // shape[1] * 32)            # input and output gradient read once
+        return self.bpu * n
+
 
 def make_inputs(name, shape, device, seed):
     """Seeded synthetic inputs with the value distributions of the benchmark configs."""
@@ -155,6 +170,35 @@ WORKLOADS = {
     'delay_fir_fwd': Workload('delay_fir_fwd', (128, 16384, 1000), 8, 'elements/s'),
     'delay_fir_bwd': Workload('delay_fir_bwd', (128, 16384, 1000), 8, 'elements/s'),
 }
+# the kernels behind the public dynamics() / spike() calls and the training variants of the fused ones
+# (bytes per unit: every tensor the call reads or returns, once)
+WORKLOADS.update({
+    'cuba_fwd_train': Workload('cuba_fwd_train', (64, 8192, 2000), 16),   # x in; current, voltage, spike out
+    'cuba_bwd_dgrad': Workload('cuba_bwd_dgrad', (64, 8192, 2000), 16),   # g_spike, voltage, current in; g_x out
+    'li_bwd_dgrad': Workload('li_bwd_dgrad', (64, 8192, 2000), 12),       # g, saved output in; g_x out
+    'ath_fwd': Workload('ath_fwd', (64, 4096, 2000), 12),
+    'apth_fwd': Workload('apth_fwd', (64, 4096, 2000), 16),
+    'res_fwd': Workload('res_fwd', (64, 8192, 1000), 16),
+    'res_bwd': Workload('res_bwd', (64, 8192, 1000), 16),
+    'res_bwd_pgrad': Workload('res_bwd_pgrad', (64, 8192, 1000), 24),
+    'adres_fwd': Workload('adres_fwd', (64, 8192, 1000), 24),
+    'spike_fwd': Workload('spike_fwd', (64, 8192, 2000), 8),
+    'spike_bwd': Workload('spike_bwd', (64, 8192, 2000), 12),
+    'cspike_fwd': Workload('cspike_fwd', (64, 8192, 1000), 12),
+    'cspike_bwd': Workload('cspike_bwd', (64, 8192, 1000), 20),
+    'sdnn_bwd': Workload('sdnn_bwd', (64, 8192, 2000), 12),               # g, activation in; g_x out
+})
+# synapse kernels of the conv network at its own layer shapes (units = output elements; bytes per unit
+# = output written + input read, scaled to one output element)
+WORKLOADS.update({
+    'pool_fwd': Workload('pool_fwd', (32, 2, 128, 128, 300), 0, 'elements/s'),
+    'pool_bwd': Workload('pool_bwd', (32, 2, 128, 128, 300), 0, 'elements/s'),
+    'conv5_fwd': Workload('conv5_fwd', (32, 2, 32, 32, 300), 0, 'elements/s'),     # 2 -> 16, 5 x 5: fp32 kernel
+    'conv3_fwd': Workload('conv3_fwd', (32, 16, 16, 16, 300), 0, 'elements/s'),    # 16 -> 32, 3 x 3: tensor cores
+    'conv3_dgrad': Workload('conv3_dgrad', (32, 32, 16, 16, 300), 0, 'elements/s'),
+    'conv3_wgrad': Workload('conv3_wgrad', (32, 16, 16, 16, 300), 0, 'elements/s'),
+})
+SYNAPSE = ('pool_', 'conv5_', 'conv3_')
 # full CUBA conv network of the last benchmark config (blocks = this library's synapse kernels + fused neuron kernel +
 # one-step delay); units = neuron-steps over all seven spiking layers (33291 neurons per sample)
 WORKLOADS['cfg4_fwd'] = Workload('cfg4_fwd', (32, 2, 128, 128, 300), 0)
@@ -166,6 +210,9 @@ WORKLOADS['recurrent_train'] = Workload('recurrent_train', (128, 512, 300), 0)
 # neuron call with a single time step per step, here on this library's own neuron kernel
 WORKLOADS['recurrent_fwd_stepwise'] = Workload('recurrent_fwd_stepwise', (128, 512, 300), 0)
 NETWORKS = ('cfg4', 'recurrent')   # chains of kernels: no single roofline, no CPU port
+# workloads the CPU oracle is timed on (cpu_baseline, --impl reference)
+CPU_PORTED = ('cuba_fwd', 'cuba_fwd_cfg0', 'cuba_bwd', 'li_fwd', 'li_bwd', 'alif_fwd', 'alif_bwd', 'adrf_fwd', 'adrf_bwd',
+              'shift', 'fir_conv', 'delay_fir_fwd', 'delay_fir_bwd')
 CFG4_NEURONS = 2048 + 16384 + 4096 + 8192 + 2048 + 512 + 11
 
 
@@ -250,6 +297,102 @@ def build_step(name, shape, device, seed):
             blk(x).sum().backward()
             _dist.allreduce_param_grads(params)
         return step, (2 if train else 1), (blk, x)
+    if name.startswith(SYNAPSE):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        x = (torch.rand(shape, device=device, generator=gen) < 0.05).float()
+
+        def grid_weight(*wshape):   # weights on the 1/32 grid of the blocks' quantiser
+            return torch.randint(-64, 64, wshape, device=device, generator=gen).float() / 32
+        if name.startswith('pool_'):
+            w = torch.ones(1, 1, 4, 4, 1, device=device)
+            if name == 'pool_fwd':
+                return (lambda: _ops.pool_fwd(x, w)), 1, (x, w)
+            gy = _ops.pool_fwd(x, w)
+            return (lambda: _ops.pool_bwd(gy, w, tuple(shape))), 1, (gy, w)
+        if name == 'conv5_fwd':
+            w = grid_weight(16, 2, 5, 5, 1)
+            return (lambda: _ops.conv_fwd(x, w, (2, 2))), 1, (x, w)
+        if name == 'conv3_fwd':
+            w = grid_weight(32, 16, 3, 3, 1)
+            return (lambda: _ops.conv_fwd(x, w, (1, 1))), 1, (x, w)
+        if name == 'conv3_dgrad':
+            w = grid_weight(32, 16, 3, 3, 1)
+            gy = torch.empty(shape, device=device).normal_(0.0, 1.0, generator=gen)
+            return (lambda: _ops.conv_dgrad(gy, w, (1, 1))), 1, (gy, w)
+        if name == 'conv3_wgrad':
+            gy = torch.empty((shape[0], 32) + tuple(shape[2:]), device=device).normal_(0.0, 1.0, generator=gen)
+            return (lambda: _ops.conv_wgrad(x, gy, (32, 16, 3, 3, 1), (1, 1))), 2, (x, gy)
+    if name == 'cuba_fwd_train':
+        cd, vd = one(1024), one(123)
+
+        def step():
+            return _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=True, want_spike=True)
+        return step, 1, d
+    if name == 'cuba_bwd_dgrad':
+        cd, vd = one(1024), one(123)
+        r = _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=True, want_spike=True)
+        d.update(voltage=r['voltage'], current=r['current'])
+        del d['x'], r
+
+        def step():
+            return _ops.cuba_bwd(d['g'], d['voltage'], THR, d['current'], cd, vd, 125.0, 0.1, False, True)
+        return step, 5, d   # the reverse scan plus two two-step folds of the decay-gradient partials
+    if name == 'li_bwd_dgrad':
+        dec = one(1024)
+        d['x'] = torch.empty(shape, device=device).normal_(0.3, 1.0)
+        d['y'] = _ops.li_fwd(d['x'], dec, zeros, W_SCALE)
+        d['g'] = torch.empty(shape, device=device).normal_(0.0, 1.0)
+        del d['x']
+
+        def step():
+            return _ops.li_bwd(d['g'], d['y'], dec, True)
+        return step, 3, d
+    if name in ('ath_fwd', 'apth_fwd'):
+        d['x'] = torch.empty(shape, device=device).normal_(0.5, 1.5)
+        ths = torch.ones(lead, device=device)
+        if name == 'ath_fwd':
+            return (lambda: _ops.ath_fwd(d['x'], zeros, one(410), ths, one(410), 0.5, 1.0, W_SCALE)), 1, d
+        d['im'] = torch.empty(shape, device=device).normal_(0.0, 1.5)
+        return (lambda: _ops.apth_fwd(d['x'], d['im'], zeros, zeros, one(410), ths, one(410), 0.25, 0.5, W_SCALE)), 1, d
+    if name in ('res_fwd', 'res_bwd', 'res_bwd_pgrad', 'adres_fwd', 'cspike_fwd', 'cspike_bwd'):
+        gen = torch.Generator(device=device).manual_seed(seed + 1)
+        period = 10 + 30 * torch.rand(C, device=device, generator=gen)
+        sd = (4096 * torch.sin(2 * np.pi / period) * 0.9).round()
+        cdec = (4096 * torch.cos(2 * np.pi / period) * 0.9).round()
+        re = torch.empty(shape, device=device).normal_(0.0, 0.5, generator=gen)
+        im = torch.empty(shape, device=device).normal_(0.0, 0.5, generator=gen)
+        keep = dict(re=re, im=im)
+        if name == 'res_fwd':
+            return (lambda: _ops.res_fwd(re, im, sd, cdec, zeros, zeros, W_SCALE)), 1, keep
+        if name == 'adres_fwd':
+            ths = 0.5 * torch.ones(lead, device=device)
+            return (lambda: _ops.adres_fwd(re, im, sd, cdec, one(410), one(410), zeros, zeros, zeros, ths, 0.25, 0.5,
+                                           W_SCALE)), 1, keep
+        if name == 'cspike_fwd':
+            return (lambda: _ops.cspike_fwd(re, im, 0.5, zeros, False, 1)), 1, keep
+        g = torch.empty(shape, device=device).normal_(0.0, 1.0, generator=gen)
+        keep['g'] = g
+        if name == 'cspike_bwd':
+            return (lambda: _ops.cspike_bwd(re, im, 0.5, g, 0.25, 10.0, False)), 1, keep
+        if name == 'res_bwd':
+            return (lambda: _ops.res_bwd(g, g, None, None, sd, cdec, False)), 1, keep
+        return (lambda: _ops.res_bwd(g, g, re, im, sd, cdec, True)), 5, keep
+    if name in ('spike_fwd', 'spike_bwd'):
+        v = torch.empty(shape, device=device).normal_(1.0, 1.0)
+        if name == 'spike_fwd':
+            return (lambda: _ops.spike_fwd(v, THR, False, 1)), 1, v
+        g = torch.empty(shape, device=device).normal_(0.0, 1.0)
+        return (lambda: _ops.spike_bwd(v, THR, g, 125.0, 0.1, False)), 1, (v, g)
+    if name == 'sdnn_bwd':
+        thr = one(0.1)
+        r = _ops.sdnn_relu_fwd(d['x'], thr, None, None, None, None, 4096, want_act=True)
+        d['act'] = r['activation']
+        d['g'] = torch.empty(shape, device=device).normal_(0.0, 1.0)
+        del d['x'], r
+
+        def step():
+            return _ops.sdnn_relu_bwd(d['g'], d['act'], None, thr, 1.0, 1.0, False)
+        return step, 1, d
     if name == 'sigma_fwd':
         def step():
             return _ops.sigma_fwd(d['x'])
@@ -744,13 +887,13 @@ EXTRA_LEGS = ('cuba_bwd', 'alif_fwd', 'alif_bwd', 'adrf_fwd', 'adrf_bwd', 'shift
               'delay_fir_bwd', 'cuba_fwd_cfg0', 'cfg4_fwd', 'cfg4_train')
 
 
-def run_extra_legs(device, dist, world, rank, steps=5, warmup=3):
+def run_extra_legs(device, dist, world, rank, steps=5, warmup=3, legs=EXTRA_LEGS):
     """{name: {shape, ms, GB/s, frac}} for the other kernels of the path (full benchmark shapes, one
     shard per GPU) and for the conv network, whose global batch of 32 is split over the ranks
     (strong scaling, one flattened all-reduce of weight and decay gradients per training step)."""
     peak, _ = peaks()
     out = {}
-    for name in EXTRA_LEGS:
+    for name in legs:
         wl = WORKLOADS[name]
         shape = tuple(wl.shape)
         net = name.startswith(NETWORKS)
@@ -769,7 +912,7 @@ def run_extra_legs(device, dist, world, rank, steps=5, warmup=3):
                 nparam = sum(q.numel() for q in keep[0].parameters() if q.requires_grad)
                 leg['allreduce_bytes_per_step'] = 4 * nparam if world > 1 else 0
         else:
-            gbs = wl.bpu * units / (statistics.mean(per) / launches * 1e-3) / 1e9
+            gbs = wl.bytes(shape) / (statistics.mean(per) * 1e-3) / 1e9
             leg.update({'GBps': gbs, 'frac': gbs / peak, 'bytes_per_unit': wl.bpu})
         out[name] = leg
         del step, keep
@@ -803,8 +946,8 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        if wl.name.startswith(NETWORKS):
-            print(json.dumps({'impl': 'reference', 'unavailable': 'no CPU port of this workload (a network of kernels)'}))
+        if wl.name not in CPU_PORTED:
+            print(json.dumps({'impl': 'reference', 'unavailable': 'the CPU oracle is not timed on this workload'}))
             return
         cpu, sec = time_cpu(wl, max(1, args.steps), max(1, args.warmup))
         line = {
@@ -846,8 +989,8 @@ def main():
             parity['all_ranks_exact'] = bool(ok)
 
     peak, peak_kind = peaks()
-    kern_ms = statistics.mean(per) / (1 if net else launches_per_step)
-    achieved = wl.bpu * units / (kern_ms * 1e-3) / 1e9
+    kern_ms = statistics.mean(per)   # a step is one kernel (plus, with parameter gradients, two tiny fold kernels)
+    achieved = wl.bytes(shape) / (kern_ms * 1e-3) / 1e9
     tpu = NCU_TRAFFIC_PER_UNIT.get(wl.name)
     roofline = {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                 'traffic': None if tpu is None else tpu * units, 'peak_kind': f'of {peak_kind}',
@@ -917,7 +1060,7 @@ def main():
         line['roofline'] = None  # a chain of synapse and neuron kernels has no single roof
         line['config']['network'] = 'Pool4-Conv(2,16,5)-Pool2-Conv(16,32,3)-Pool2-Flatten-Dense(2048,512)-Dense(512,11), CUBA'
         line['config']['parallelism'] = f'global batch {shape[0] * world} split over {world} GPUs, one all-reduce of weight gradients'
-    if rank == 0 and not args.no_cpu and not net:
+    if rank == 0 and not args.no_cpu and wl.name in CPU_PORTED:
         cpu, _ = time_cpu(wl, steps=3, warmup=1)
         # context, not measured here: lava-dl's own Python loops ran this neuron at about 1e7
         # neuron-steps/s on 8 host threads when the path was surveyed (two orders below the C port)
