@@ -150,6 +150,8 @@ WORKLOADS = {
     # headline: fused CUBA forward, x in, spike + voltage out = 12 B per neuron-step
     'cuba_fwd': Workload('cuba_fwd', (64, 8192, 2000), 12),
     'cuba_fwd_cfg0': Workload('cuba_fwd_cfg0', (16, 512, 1000), 12),
+    # the same through slayer.neuron.cuba.Neuron.forward: the kernel plus the Python / ATen glue of one call
+    'cuba_fwd_cfg0_api': Workload('cuba_fwd_cfg0_api', (16, 512, 1000), 12),
     # block output path: spikes written one step late plus a per-neuron axonal delay of 0..62 steps, same 12 B
     'cuba_fwd_delayed': Workload('cuba_fwd_delayed', (64, 8192, 2000), 12),
     # backward of the same: g_spike + voltage in, g_x out
@@ -425,6 +427,14 @@ def build_step(name, shape, device, seed):
             return _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=False, want_spike=True,
                                  spike_delay=1, axon_delay=d['delay'])
         return step, 1, d
+    if name == 'cuba_fwd_cfg0_api':
+        import lava_dl_b200.slayer as slayer
+        neuron = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03).to(device)
+
+        def step():
+            with torch.no_grad():
+                return neuron(d['x'])
+        return step, 1, (d, neuron)
     if name.startswith('cuba_fwd'):
         cd, vd = one(1024), one(123)
 
@@ -884,7 +894,7 @@ def time_steps(step, steps, warmup, device, dist, sampler=None):
 
 # legs reported beside the headline in the default run: every benchmark configuration's kernels
 EXTRA_LEGS = ('cuba_bwd', 'alif_fwd', 'alif_bwd', 'adrf_fwd', 'adrf_bwd', 'shift', 'fir_conv', 'delay_fir_fwd',
-              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cfg4_fwd', 'cfg4_train')
+              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cfg4_fwd', 'cfg4_train')
 
 
 def run_extra_legs(device, dist, world, rank, steps=5, warmup=3, legs=EXTRA_LEGS):

@@ -200,28 +200,33 @@ int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_
 
 /* ALIF (neuron/alif.py:383-591).  mode 0: forward() -> spike, voltage,
  * thsum = threshold + refractory.  mode 1: dynamics() -> current, voltage,
- * threshold, refractory (out0..out3). */
+ * threshold, refractory (out0..out3).  spike_delay = 1 (mode 0, binary spikes):
+ * the spike series is written one step late, delay_head (nullable float[rows])
+ * supplying its first step, as in sb_cuba_fwd; sb_cuba_bwd undoes it. */
 int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* ref_decay, int64_t n_ref_decay, const float* th_decay, int64_t n_th_decay,
                 const float* cstate, const float* vstate, const float* ref_state, const float* th_state,
                 float* out0, float* out1, float* out2, float* out3, float* final_c, float* final_v,
                 float* final_th, float* final_ref, float* final_s, const sb_geom* g, int th_step, int th0,
-                int w_scale, int mode, int graded, float spike_scale, void* stream);
+                int w_scale, int mode, int graded, float spike_scale, int spike_delay, const float* delay_head,
+                void* stream);
 
 /* RF (neuron/rf.py) and ADRF (neuron/adrf.py:439-652).  adapt = 0: outputs
  * spike, re, im (out0..out2) with scalar threshold.  adapt = 1, mode 0:
- * spike, re, im, th + ref.  adapt = 1, mode 1: re, im, threshold, refractory. */
+ * spike, re, im, th + ref.  adapt = 1, mode 1: re, im, threshold, refractory.
+ * spike_delay / delay_head (mode 0, binary spikes) as in sb_cuba_fwd; sb_rf_bwd
+ * takes the same spike_delay to read the gradient of the late series. */
 int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
               int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
               int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,
               const float* th_state, float* out0, float* out1, float* out2, float* out3, float* final_re,
               float* final_im, float* final_th, float* final_ref, float* final_s, const sb_geom* g,
               float threshold, int th_step, int th0, int w_scale, int adapt, int mode, int graded,
-              float spike_scale, void* stream);
+              float spike_scale, int spike_delay, const float* delay_head, void* stream);
 int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const float* thr_tensor, float thr,
               const float* sin_decay, const float* cos_decay, int64_t n_decay, float* grad_re_in,
               float* grad_im_in, float* grad_sin, float* grad_cos, void* scratch_sin, void* scratch_cos,
-              const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream);
+              const sb_geom* g, float tau_rho, float scale_rho, int graded, int spike_delay, void* stream);
 
 /* ---- time shift --------------------------------------------------------------
  * Replaces shift.cu:80-175 / utils/time/shift.py:46-143:

@@ -104,6 +104,35 @@ __global__ void cspike_fwd_kernel(const float* __restrict__ re, const float* __r
   }
 }
 
+// The same on 128-bit words (T % 4 == 0, aligned tensors): a thread owns four consecutive steps of
+// one row and needs one extra value, the imaginary part just before its word.
+template <bool TT, bool GRADED>
+__global__ void cspike_fwd_vec_kernel(const float* __restrict__ re, const float* __restrict__ im,
+                                      const float* __restrict__ tht, float thr, const float* __restrict__ imag_last,
+                                      float* __restrict__ out, int64_t rows, int T, float scale) {
+  const int T4 = T >> 2;
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    const int64_t base = row * (int64_t)T;
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < T4; q += gridDim.x * blockDim.x) {
+      const float4 r = __ldg(reinterpret_cast<const float4*>(re + base) + q);
+      const float4 m = __ldg(reinterpret_cast<const float4*>(im + base) + q);
+      const float mp = (q == 0) ? __ldg(imag_last + row) : __ldg(im + base + 4 * q - 1);
+      float4 th = make_float4(thr, thr, thr, thr);
+      if (TT) th = __ldg(reinterpret_cast<const float4*>(tht + base) + q);
+      const bool s0 = (r.x >= th.x) && (mp < 0.f) && (m.x >= 0.f);
+      const bool s1 = (r.y >= th.y) && (m.x < 0.f) && (m.y >= 0.f);
+      const bool s2 = (r.z >= th.z) && (m.y < 0.f) && (m.z >= 0.f);
+      const bool s3 = (r.w >= th.w) && (m.z < 0.f) && (m.w >= 0.f);
+      float4 o;
+      o.x = GRADED ? __fdiv_rn(__fmul_rn(s0 ? 1.f : 0.f, r.x), scale) : (s0 ? 1.f : 0.f);
+      o.y = GRADED ? __fdiv_rn(__fmul_rn(s1 ? 1.f : 0.f, r.y), scale) : (s1 ? 1.f : 0.f);
+      o.z = GRADED ? __fdiv_rn(__fmul_rn(s2 ? 1.f : 0.f, r.z), scale) : (s2 ? 1.f : 0.f);
+      o.w = GRADED ? __fdiv_rn(__fmul_rn(s3 ? 1.f : 0.f, r.w), scale) : (s3 ? 1.f : 0.f);
+      reinterpret_cast<float4*>(out + base)[q] = o;
+    }
+  }
+}
+
 // Complex spike backward: spike/complex.py:144-167 (element-wise)
 template <bool TT, bool GRADED>
 __global__ void cspike_bwd_kernel(const float* __restrict__ re, const float* __restrict__ im,
@@ -260,8 +289,13 @@ int sb_cspike_fwd(const float* re, const float* im, const float* thr_tensor, flo
   SB_REQUIRE(re && im && imag_last && spike, "null tensor pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const dim3 grid = row_grid(rows, T, kThreads);
-#define SB_GO(TT, G) \
-  cspike_fwd_kernel<TT, G><<<grid, kThreads, 0, st>>>(re, im, thr_tensor, thr, imag_last, spike, rows, (int)T, scale);
+  const bool vec = (T & 3) == 0 && ((((uintptr_t)re) | ((uintptr_t)im) | ((uintptr_t)spike) | ((uintptr_t)thr_tensor)) & 15u) == 0;
+  const dim3 vgrid((unsigned)((T / 4 + kThreads - 1) / kThreads > 0 ? (T / 4 + kThreads - 1) / kThreads : 1), grid.y);
+#define SB_GO(TT, G)                                                                                                   \
+  if (vec)                                                                                                             \
+    cspike_fwd_vec_kernel<TT, G><<<vgrid, kThreads, 0, st>>>(re, im, thr_tensor, thr, imag_last, spike, rows, (int)T, scale); \
+  else                                                                                                                 \
+    cspike_fwd_kernel<TT, G><<<grid, kThreads, 0, st>>>(re, im, thr_tensor, thr, imag_last, spike, rows, (int)T, scale);
   if (thr_tensor) { if (graded) SB_GO(true, true) else SB_GO(true, false) }
   else            { if (graded) SB_GO(false, true) else SB_GO(false, false) }
 #undef SB_GO

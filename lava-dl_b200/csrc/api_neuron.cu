@@ -191,8 +191,12 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
                 const float* cstate, const float* vstate, const float* ref_state, const float* th_state,
                 float* out0, float* out1, float* out2, float* out3, float* final_c, float* final_v,
                 float* final_th, float* final_ref, float* final_s, const sb_geom* g, int th_step, int th0,
-                int w_scale, int mode, int graded, float spike_scale, void* stream) {
+                int w_scale, int mode, int graded, float spike_scale, int spike_delay, const float* delay_head,
+                void* stream) {
   RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || (spike_delay == 1 && mode == 0 && !graded),
+             "the fused one-step delay needs forward mode and binary spikes");
+  const BitDelay bd{spike_delay, delay_head, nullptr, 0, 1.f};
   SB_TRY(check_count(n_cdecay, "current decay"));
   SB_TRY(check_count(n_vdecay, "voltage decay"));
   SB_TRY(check_count(n_ref_decay, "refractory decay"));
@@ -216,7 +220,7 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
   {                                                                                                  \
     typename AlifFwd<D, G>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,     \
                                      final_c, final_v, final_th, final_ref, final_s, spike_scale, sc}; \
-    return launch_rowscan<AlifFwd<D, G>>(p, rg, in, out, st);                                        \
+    return launch_rowscan<AlifFwd<D, G>>(p, rg, in, out, st, bd);                                    \
   }
   if (mode == 1) SB_GO(true, false)
   else if (graded) SB_GO(false, true)
@@ -230,8 +234,11 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
               const float* th_state, float* out0, float* out1, float* out2, float* out3, float* final_re,
               float* final_im, float* final_th, float* final_ref, float* final_s, const sb_geom* g,
               float threshold, int th_step, int th0, int w_scale, int adapt, int mode, int graded,
-              float spike_scale, void* stream) {
+              float spike_scale, int spike_delay, const float* delay_head, void* stream) {
   RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || (spike_delay == 1 && mode == 0 && !graded),
+             "the fused one-step delay needs forward mode and binary spikes");
+  const BitDelay bd{spike_delay, delay_head, nullptr, 0, 1.f};
   SB_TRY(check_count(n_decay, "sin/cos decay"));
   if (!adapt) { n_ref_decay = 1; n_th_decay = 1; }
   SB_TRY(check_count(n_ref_decay, "refractory decay"));
@@ -260,7 +267,7 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
   {                                                                                                  \
     typename RfFwd<A, D, G>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,      \
                                       final_s, spike_scale, sc};                                     \
-    return launch_rowscan<RfFwd<A, D, G>>(p, rg, in, out, st);                                       \
+    return launch_rowscan<RfFwd<A, D, G>>(p, rg, in, out, st, bd);                                   \
   }
   if (adapt) {
     if (mode == 1) SB_GO(true, true, false)
@@ -276,8 +283,9 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
 int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const float* thr_tensor, float thr,
               const float* sin_decay, const float* cos_decay, int64_t n_decay, float* grad_re_in,
               float* grad_im_in, float* grad_sin, float* grad_cos, void* scratch_sin, void* scratch_cos,
-              const sb_geom* g, float tau_rho, float scale_rho, int graded, void* stream) {
+              const sb_geom* g, float tau_rho, float scale_rho, int graded, int spike_delay, void* stream) {
   RowGeom rg;
+  SB_REQUIRE(spike_delay == 0 || spike_delay == 1, "spike_delay is 0 or 1");
   SB_TRY(check_count(n_decay, "sin/cos decay"));
   SB_TRY(check_geom(g, &rg, n_decay));
   SB_REQUIRE(sin_decay && cos_decay, "null parameter pointer");
@@ -296,7 +304,7 @@ int sb_rf_bwd(const float* grad_spike, const float* re, const float* im, const f
 #define SB_GO(TT, G, P)                                                                              \
   {                                                                                                  \
     typename RfBwd<TT, G, P>::Params p{{sin_decay, n_decay}, {cos_decay, n_decay}, sg, thr,          \
-                                       (double*)scratch_sin, (double*)scratch_cos};                  \
+                                       (double*)scratch_sin, (double*)scratch_cos, spike_delay};     \
     const float* in[4] = {grad_spike, re, im, thr_tensor};                                           \
     SB_TRY((launch_rowscan<RfBwd<TT, G, P>>(p, rg, in, out, st)));                                   \
   }

@@ -61,37 +61,40 @@ pool_fwd_kernel(const float* __restrict__ x, const float* __restrict__ wgt, floa
   }
 }
 
+// One block per input image row (nc, h), looping over the row's words: the only divisions are
+// 32-bit and per thread, not per element (a flat index over NC * H * W * T costs four 64-bit
+// divisions per word).
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 pool_bwd_kernel(const float* __restrict__ gy, const float* __restrict__ wgt, float* __restrict__ gx, PoolGeom g) {
-  __shared__ float w[kMaxPoolTaps];
-  for (int i = threadIdx.x; i < g.kh * g.kw; i += blockDim.x) w[i] = __ldg(wgt + i);
-  __syncthreads();
   constexpr int V = VEC ? 4 : 1;
   const int TV = g.T / V;
-  const int64_t total = (int64_t)g.NC * g.H * g.W * TV;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int tv = (int)(idx % TV);
-    int64_t r = idx / TV;
-    const int ww = (int)(r % g.W); r /= g.W;
-    const int h = (int)(r % g.H);
-    const int64_t nc = r / g.H;
-    const int ho = h / g.kh, wo = ww / g.kw;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (ho < g.Ho && wo < g.Wo) {  // inputs past the last full window feed nothing
-      const float wv = w[(h - ho * g.kh) * g.kw + (ww - wo * g.kw)];
-      const float* src = gy + ((nc * g.Ho + ho) * (int64_t)g.Wo + wo) * g.T + (int64_t)tv * V;
-      if (VEC) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(src));
-        o = make_float4(__fmul_rn(wv, a.x), __fmul_rn(wv, a.y), __fmul_rn(wv, a.z), __fmul_rn(wv, a.w));
-      } else {
-        o.x = __fmul_rn(wv, __ldg(src));
+  const int per_row = g.W * TV;                        // words of one input row
+  const int64_t nrows = (int64_t)g.NC * g.H;
+  for (int64_t row = blockIdx.y; row < nrows; row += gridDim.y) {
+    const int64_t nc = row / g.H;                      // once per row
+    const int h = (int)(row - nc * g.H);
+    const int ho = h / g.kh, hk = h - ho * g.kh;
+    float* drow = gx + row * (int64_t)g.W * g.T;
+    const float* srow = gy + (nc * g.Ho + ho) * (int64_t)g.Wo * g.T;
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < per_row; q += gridDim.x * blockDim.x) {
+      const int ww = q / TV, tv = q - ww * TV;
+      const int wo = ww / g.kw;
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ho < g.Ho && wo < g.Wo) {  // inputs past the last full window feed nothing
+        const float wv = __ldg(wgt + hk * g.kw + (ww - wo * g.kw));
+        const float* src = srow + (int64_t)wo * g.T + tv * V;
+        if (VEC) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+          o = make_float4(__fmul_rn(wv, a.x), __fmul_rn(wv, a.y), __fmul_rn(wv, a.z), __fmul_rn(wv, a.w));
+        } else {
+          o.x = __fmul_rn(wv, __ldg(src));
+        }
       }
+      float* dst = drow + (int64_t)q * V;
+      if (VEC) *reinterpret_cast<float4*>(dst) = o;
+      else dst[0] = o.x;
     }
-    float* dst = gx + idx * V;
-    if (VEC) *reinterpret_cast<float4*>(dst) = o;
-    else dst[0] = o.x;
   }
 }
 
@@ -148,13 +151,19 @@ int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t
   SB_REQUIRE(NC < (1LL << 31), "too many channel planes");
   g.NC = (int)NC;
   const bool vec = vec_ok(grad_y, grad_x, T);
-  const int64_t total = NC * H * W * (vec ? T / 4 : T);
-  int64_t blocks = (total + 255) / 256;
-  const int64_t cap = (int64_t)sm_count() * 32;
-  if (blocks > cap) blocks = cap;
+  SB_REQUIRE(W * (vec ? T / 4 : T) < (1LL << 31), "input row too long");
+  const int64_t per_row = W * (vec ? T / 4 : T);
+  // whole rows per block; a row is split over several blocks only when there are too few rows to fill the GPU
+  int64_t gyr = NC * H;
+  if (gyr > 65535) gyr = 65535;
+  int64_t gx = ((int64_t)sm_count() * 8 + gyr - 1) / gyr;
+  const int64_t gx_max = (per_row + 255) / 256;
+  if (gx > gx_max) gx = gx_max;
+  if (gx < 1) gx = 1;
+  const dim3 grid((unsigned)gx, (unsigned)gyr);
   cudaStream_t st = (cudaStream_t)stream;
-  if (vec) pool_bwd_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(grad_y, weight, grad_x, g);
-  else pool_bwd_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(grad_y, weight, grad_x, g);
+  if (vec) pool_bwd_kernel<true><<<grid, 256, 0, st>>>(grad_y, weight, grad_x, g);
+  else pool_bwd_kernel<false><<<grid, 256, 0, st>>>(grad_y, weight, grad_x, g);
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

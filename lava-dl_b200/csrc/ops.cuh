@@ -176,7 +176,7 @@ struct LiBwd {
   static constexpr int NIN = DGRAD ? 2 : 1, NOUT = 1;
   static constexpr bool REVERSE = true;
   static constexpr int NBIT = 0;
-  SB_PIPE(3, (DGRAD ? 1 : 4), 32);
+  SB_PIPE((DGRAD ? 4 : 3), (DGRAD ? 2 : 4), 32);   // with the decay gradient (two input tiles): 0.86 -> 0.95
   struct Params {
     DecayVec decay;
     double* partial;  // scratch, see store_partial()
@@ -248,7 +248,7 @@ struct AthFwd {
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE(3, 1, 32);
+  SB_PIPE(5, 1, 32);   // 0.75 -> 0.80 of copy bandwidth against three stages
   struct Params {
     AthParams ath;
     Scale sc;
@@ -282,7 +282,7 @@ struct ApthFwd {
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE(3, 1, 32);
+  SB_PIPE(6, 1, 32);   // 0.79 -> 0.85
   struct Params {
     AthParams ath;
     const float* im_state;  // [rows]
@@ -361,7 +361,7 @@ struct ResFwd {
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE(3, 1, 32);
+  SB_PIPE(3, 2, 32);   // two boxes per stage: 0.83 -> 0.91
   struct Params {
     ResParams res;
     int k_thr;     // smallest int whose fp32 value reaches thr * w
@@ -402,7 +402,7 @@ struct ResBwd {
   static constexpr int NIN = PGRAD ? 4 : 2, NOUT = 2;  // in: g_re, g_im, [re, im]
   static constexpr bool REVERSE = true;
   static constexpr int NBIT = 0;
-  SB_PIPE(3, 1, (PGRAD ? 16 : 32));
+  SB_PIPE((PGRAD ? 4 : 3), 1, 32);   // with sin / cos gradients (four input tiles): 0.54 -> 0.57 against 16-step tiles
   struct Params {
     DecayVec sin_decay, cos_decay;
     double* partial_sin;
@@ -448,7 +448,7 @@ struct AdResFwd {
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE(3, 1, 16);
+  SB_PIPE(3, 1, 32);   // 32-step tiles although that leaves four warps per SM: 0.66 -> 0.79 against 16-step tiles
   struct Params {
     ResParams res;
     AthParams ath;
@@ -636,9 +636,12 @@ template <bool DYN, bool GRADED>
 struct AlifFwd {
   static constexpr int NIN = 1, NOUT = DYN ? 4 : 3;
   static constexpr bool REVERSE = false;
-  static constexpr int NBIT = 0;  // bit output measured slower here (0.72 against 0.76)
+  // binary spikes leave as bits (which is what lets the block's one-step delay ride on the store);
+  // with two boxes per stage that runs as fast as spikes on a TMA tile with four stages of one box
+  // (0.777 against 0.779 of copy bandwidth; one box per stage: 0.72)
+  static constexpr int NBIT = (!DYN && !GRADED) ? 1 : 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE((DYN ? 3 : 4), 1, (DYN ? 16 : 32));
+  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((!DYN && NBIT) ? 2 : 1), (DYN ? 16 : 32));
   struct Params {
     DecayVec cdecay, vdecay;
     const float* cstate;
@@ -798,19 +801,24 @@ struct RfBwd {
     float thr;
     double* partial_sin;
     double* partial_cos;
+    int spike_delay;      // 1: the forward wrote spikes one step late, so g_spike[t] is read from t + 1
   };
   ResBwd<PGRAD> scan;
   CSurrogate sg;
-  float thr;
+  float thr, gnext;
+  bool delayed;
   __device__ __forceinline__ void init(const Params& p, const RowGeom& g, int64_t row, bool valid) {
     typename ResBwd<PGRAD>::Params rp{p.sin_decay, p.cos_decay, p.partial_sin, p.partial_cos};
     scan.init(rp, g, row, valid);
-    sg = p.sg; thr = p.thr;
+    sg = p.sg; thr = p.thr; gnext = 0.f; delayed = p.spike_delay != 0;
   }
   __device__ __forceinline__ void step(const float (&a)[NIN], float (&b)[2]) {
     float dre, dim;
     csurrogate<GRADED>(sg, a[1], a[2], TENSOR_THR ? a[NIN - 1] : thr, dre, dim);
-    scan.scan(__fmul_rn(a[0], dre), __fmul_rn(a[0], dim), a[1], a[2]);
+    // the scan runs backwards, so the gradient of the delayed spike (time t + 1) was the previous input
+    const float gin = delayed ? gnext : a[0];
+    gnext = a[0];
+    scan.scan(__fmul_rn(gin, dre), __fmul_rn(gin, dim), a[1], a[2]);
     b[0] = scan.gre; b[1] = scan.gim;
   }
   __device__ __forceinline__ void tile_end() { scan.tile_end(); }

@@ -59,12 +59,12 @@ SIGNATURES = {
     'sb_cuba_recurrent_bwd': (c_int, [_P, _P, _P, _P, _I64, _I64, _I64, c_float, c_float, c_float, c_int, _P]),
     'sb_alif_fwd': (c_int, [_P, _P, _I64, _P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _P,
                             _P, _P, _P, _P, _P, _P, _P, _P, _P, _G,
-                            c_int, c_int, c_int, c_int, c_int, c_float, _P]),
+                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P]),
     'sb_rf_fwd': (c_int, [_P, _P, _P, _P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _P,
                           _P, _P, _P, _P, _P, _P, _P, _P, _P, _G,
-                          c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
+                          c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P]),
     'sb_rf_bwd': (c_int, [_P, _P, _P, _P, c_float, _P, _P, _I64, _P, _P, _P, _P, _P, _P, _G,
-                          c_float, c_float, c_int, _P]),
+                          c_float, c_float, c_int, c_int, _P]),
     'sb_shift': (c_int, [_P, _P, _I64, c_float, c_float, _P, _I64, _I64, _P]),
     'sb_sigma_fwd': (c_int, [_P, _P, _P, _P, _I64, _I64, _P]),
     'sb_sigma_bwd': (c_int, [_P, _P, _I64, _I64, _P]),

@@ -540,7 +540,7 @@ def cuba_recurrent_bwd(grad_spike, voltage, rec, threshold, tau_rho, scale_rho, 
 
 
 def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0, w_scale,
-             dynamics_mode, graded=False, spike_scale=1.0):
+             dynamics_mode, graded=False, spike_scale=1.0, spike_delay=0, delay_head=None):
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
@@ -550,17 +550,18 @@ def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, 
     outs = [torch.empty_like(x) for _ in range(4 if dynamics_mode else 3)]
     fin = [_vec(x) for _ in range(5)]
     g = geom(x, cd.numel(), vd.numel(), rd.numel(), td.numel())
+    head = None if delay_head is None else row_state(delay_head, x)
     N.call('sb_alif_fwd', x, N.ptr(x), N.ptr(cd), cd.numel(), N.ptr(vd), vd.numel(), N.ptr(rd), rd.numel(),
            N.ptr(td), td.numel(), N.ptr(cs), N.ptr(vs), N.ptr(rs), N.ptr(ts),
            N.ptr(outs[0]), N.ptr(outs[1]), N.ptr(outs[2]), N.ptr(outs[3]) if dynamics_mode else None,
            N.ptr(fin[0]), N.ptr(fin[1]), N.ptr(fin[2]), N.ptr(fin[3]), None if dynamics_mode else N.ptr(fin[4]),
            g, int(th_step * w_scale), int(th0 * w_scale), int(w_scale), int(bool(dynamics_mode)),
-           int(bool(graded)), float(spike_scale), N.stream_of(x))
+           int(bool(graded)), float(spike_scale), int(spike_delay), N.ptr(head), N.stream_of(x))
     return outs, dict(final_c=fin[0], final_v=fin[1], final_th=fin[2], final_ref=fin[3], final_s=fin[4])
 
 
 def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_scale, graded=False,
-           spike_scale=1.0, adaptive=None, dynamics_mode=False):
+           spike_scale=1.0, adaptive=None, dynamics_mode=False, spike_delay=0, delay_head=None):
     """``adaptive`` = None for RF, else dict(ref_decay, th_decay, ref_state, th_state, th_step, th0)."""
     N.require_cuda(re_in, im_in)
     re_in, im_in = _c(re_in), _c(im_in)
@@ -580,17 +581,20 @@ def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_
     outs = [torch.empty_like(re_in) for _ in range(nout)]
     fin = [_vec(re_in) for _ in range(5)]
     g = geom(re_in, *counts)
+    head = None if delay_head is None else row_state(delay_head, re_in)
     N.call('sb_rf_fwd', re_in, N.ptr(re_in), N.ptr(im_in), N.ptr(sd), N.ptr(cd), sd.numel(),
            N.ptr(rd), rd.numel() if adapt else 1, N.ptr(td), td.numel() if adapt else 1,
            N.ptr(rs), N.ptr(ims), N.ptr(refs), N.ptr(ths),
            N.ptr(outs[0]), N.ptr(outs[1]), N.ptr(outs[2]), N.ptr(outs[3]) if adapt else None,
            N.ptr(fin[0]), N.ptr(fin[1]), N.ptr(fin[2]) if adapt else None, N.ptr(fin[3]) if adapt else None,
            None if dynamics_mode else N.ptr(fin[4]), g, f32(threshold), th_step, th0, int(w_scale), int(adapt),
-           int(bool(dynamics_mode)), int(bool(graded)), float(spike_scale), N.stream_of(re_in))
+           int(bool(dynamics_mode)), int(bool(graded)), float(spike_scale), int(spike_delay), N.ptr(head),
+           N.stream_of(re_in))
     return outs, dict(final_re=fin[0], final_im=fin[1], final_th=fin[2], final_ref=fin[3], final_s=fin[4])
 
 
-def rf_bwd(grad_spike, re, im, threshold, sin_decay, cos_decay, tau_rho, scale_rho, graded, need_param_grad):
+def rf_bwd(grad_spike, re, im, threshold, sin_decay, cos_decay, tau_rho, scale_rho, graded, need_param_grad,
+           spike_delay=0):
     N.require_cuda(grad_spike, re, im)
     grad_spike, re, im = _c(grad_spike), _c(re), _c(im)
     sd, cd = _param(sin_decay, re), _param(cos_decay, re)
@@ -606,7 +610,7 @@ def rf_bwd(grad_spike, re, im, threshold, sin_decay, cos_decay, tau_rho, scale_r
         s2 = N.scratch(g.rows, sd.numel(), re.device)
     N.call('sb_rf_bwd', re, N.ptr(grad_spike), N.ptr(re), N.ptr(im), N.ptr(tt), ts, N.ptr(sd), N.ptr(cd),
            sd.numel(), N.ptr(gre), N.ptr(gim), N.ptr(gs), N.ptr(gc), N.ptr(s1), N.ptr(s2), g, f32(tau_rho),
-           f32(scale_rho), int(bool(graded)), N.stream_of(re))
+           f32(scale_rho), int(bool(graded)), int(spike_delay), N.stream_of(re))
     if need_param_grad:
         return gre, gim, gs.reshape(sin_decay.shape), gc.reshape(cos_decay.shape)
     return gre, gim, None, None

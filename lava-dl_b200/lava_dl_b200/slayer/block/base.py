@@ -51,7 +51,7 @@ class _Block(torch.nn.Module):
         if self.delay_shift is True and getattr(self.neuron, 'fuses_step_delay', False):
             # a bounded axonal delay (at most 62 steps) is written by the neuron kernel as well
             steps = None if self.delay is None else self.delay.fusable_steps
-            fuse_axon = steps is not None and 0 <= steps <= 62
+            fuse_axon = steps is not None and 0 <= steps <= 62 and getattr(self.neuron, 'fuses_axon_delay', False)
             x = self._neuron_with_step_delay(z, self.delay if fuse_axon else None)
             if self.delay is not None and not fuse_axon:
                 x = self.delay(x)

@@ -183,13 +183,30 @@ class Neuron(ResonatorBase):
         if not self._fusable:
             real, imag, threshold, refractory = self.dynamics(input)
             return self.spike(real, imag, threshold, refractory)
+        spike, _ = self._fused_forward(input, 0, None)
+        if self.drop is not None:
+            spike = self.drop(spike)
+        return spike
+
+    @property
+    def fuses_step_delay(self):
+        """True when ``forward_step_delayed`` can write the spikes one step late inside the kernel."""
+        return self._fusable and self.graded_spike is not True and self.drop is None
+
+    fuses_axon_delay = False   # a block's axonal delay stays a separate shift for this neuron
+
+    def forward_step_delayed(self, input, delay_head=None):
+        """``forward`` with the blocks' one-step delay folded in: ``(delayed_spike, last_spike)``."""
+        return self._fused_forward(input, 1, delay_head)
+
+    def _fused_forward(self, input, spike_delay, delay_head):
         real_input, imag_input = self._prepare(input)
         spike, final_re, final_im, final_s, final_th, final_ref = _FusedForward.apply(
             real_input, imag_input, quantize(self.sin_decay), quantize(self.cos_decay), self.real_state,
             self.imag_state, self.threshold, self.s_scale, self.tau_rho * TAU_RHO_MULT,
             self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, quantize(self.refractory_decay),
             quantize(self.threshold_decay), self.refractory_state, self.threshold_state, self.threshold_step,
-            self.threshold)
+            self.threshold, spike_delay, delay_head)
         if self.persistent_state:
             with torch.no_grad():
                 self.real_state = final_re
@@ -197,6 +214,4 @@ class Neuron(ResonatorBase):
                 self.threshold_state = final_th
                 self.refractory_state = final_ref
                 self._carry_spike(final_s)
-        if self.drop is not None:
-            spike = self.drop(spike)
-        return spike
+        return spike, final_s

@@ -51,12 +51,13 @@ class _FusedForward(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step,
-                th0, w_scale, tau_rho, scale_rho, graded):
+                th0, w_scale, tau_rho, scale_rho, graded, spike_delay=0, delay_head=None):
         (spike, voltage, thsum), fin = _ops.alif_fwd(
             input, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0,
-            w_scale, dynamics_mode=False, graded=graded, spike_scale=1.0)
+            w_scale, dynamics_mode=False, graded=graded, spike_scale=1.0, spike_delay=spike_delay,
+            delay_head=delay_head)
         ctx.save_for_backward(voltage, thsum, cdecay, vdecay)
-        ctx.consts = (tau_rho, scale_rho, graded)
+        ctx.consts = (tau_rho, scale_rho, graded, spike_delay)
         extras = (fin['final_c'], fin['final_v'], fin['final_th'], fin['final_ref'], fin['final_s'])
         ctx.mark_non_differentiable(*extras)
         return (spike,) + extras
@@ -64,10 +65,10 @@ class _FusedForward(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_spike, *_):
         voltage, thsum, cdecay, vdecay = ctx.saved_tensors
-        tau_rho, scale_rho, graded = ctx.consts
+        tau_rho, scale_rho, graded, spike_delay = ctx.consts
         g_in, _, _ = _ops.cuba_bwd(grad_spike, voltage, thsum, None, cdecay, vdecay, tau_rho, scale_rho, graded,
-                                   False)
-        return (g_in,) + (None,) * 14
+                                   False, spike_delay=spike_delay)
+        return (g_in,) + (None,) * 16
 
 
 class Neuron(base.Neuron):
@@ -241,12 +242,35 @@ class Neuron(base.Neuron):
             spike = self.drop(spike)
         return spike
 
+    def _learnable_decays(self):
+        return self.requires_grad and any(getattr(self, f'{k}_decay').requires_grad for k in self._decays)
+
     def forward(self, input):
         """Spike response to ``input`` (``[batch, ..., time]``)."""
-        learn = self.requires_grad and any(getattr(self, f'{k}_decay').requires_grad for k in self._decays)
-        if not self._fusable or learn:
+        if not self._fusable or self._learnable_decays():
             _, voltage, threshold, refractory = self.dynamics(input)
             return self.spike(voltage, threshold, refractory)
+        spike, _ = self._fused_forward(input, 0, None)
+        if self.drop is not None:
+            spike = self.drop(spike)
+        return spike
+
+    @property
+    def fuses_step_delay(self):
+        """True when ``forward_step_delayed`` can write the spikes one step late inside the kernel
+        (binary spikes, one-pass forward, no dropout)."""
+        return self._fusable and not self._learnable_decays() and self.graded_spike is not True \
+            and self.drop is None
+
+    fuses_axon_delay = False   # a block's axonal delay stays a separate shift for this neuron
+
+    def forward_step_delayed(self, input, delay_head=None):
+        """``forward`` with the blocks' one-step delay folded in: ``(delayed_spike, last_spike)`` with
+        ``delayed_spike[..., t] = spike[..., t - 1]`` and ``delayed_spike[..., 0] = delay_head`` (0 when
+        ``None``); ``last_spike`` is the undelayed spike of the last time bin."""
+        return self._fused_forward(input, 1, delay_head)
+
+    def _fused_forward(self, input, spike_delay, delay_head):
         self._prepare(input)
         if self.norm is not None:
             input = self.norm(input)
@@ -254,7 +278,8 @@ class Neuron(base.Neuron):
         spike, final_c, final_v, final_th, final_ref, final_s = _FusedForward.apply(
             input, cd, vd, rd, td, self.current_state, self.voltage_state, self.refractory_state,
             self.threshold_state, self.threshold_step, self.threshold, self.s_scale,
-            self.tau_rho * TAU_RHO_MULT, self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True)
+            self.tau_rho * TAU_RHO_MULT, self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True,
+            spike_delay, delay_head)
         if self.persistent_state:
             with torch.no_grad():
                 self.current_state = final_c
@@ -262,6 +287,4 @@ class Neuron(base.Neuron):
                 self.threshold_state = final_th
                 self.refractory_state = final_ref
                 self._carry_spike(final_s)
-        if self.drop is not None:
-            spike = self.drop(spike)
-        return spike
+        return spike, final_s

@@ -282,6 +282,8 @@ class Neuron(base.Neuron):
         inside the kernel (binary spikes, no normalisation, no dropout)."""
         return self.norm is None and self._fusable and self.graded_spike is not True and self.drop is None
 
+    fuses_axon_delay = True   # a bounded axonal delay of the block rides on the same store
+
     def forward_step_delayed(self, input, delay_head=None, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         """``forward`` with the blocks' one-step delay folded in: returns
         ``(delayed_spike, last_spike)`` where ``delayed_spike[..., t] = spike[..., t - 1]``,

@@ -34,13 +34,14 @@ class _FusedForward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold, w_scale,
                 tau_rho, scale_rho, graded, ref_decay=None, th_decay=None, ref_state=None, th_state=None,
-                th_step=0.0, th0=0.0):
+                th_step=0.0, th0=0.0, spike_delay=0, delay_head=None):
         ad = None
         if ref_decay is not None:
             ad = dict(ref_decay=ref_decay, th_decay=th_decay, ref_state=ref_state, th_state=th_state,
                       th_step=th_step, th0=th0)
         outs, fin = _ops.rf_fwd(real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold,
-                                w_scale, graded=graded, spike_scale=1.0, adaptive=ad)
+                                w_scale, graded=graded, spike_scale=1.0, adaptive=ad, spike_delay=spike_delay,
+                                delay_head=delay_head)
         spike, real, imag = outs[:3]
         if ad is None:
             ctx.save_for_backward(real, imag, sin_decay, cos_decay)
@@ -48,7 +49,7 @@ class _FusedForward(torch.autograd.Function):
         else:
             ctx.save_for_backward(real, imag, sin_decay, cos_decay, outs[3])
             ctx.threshold = None
-        ctx.consts = (tau_rho, scale_rho, graded)
+        ctx.consts = (tau_rho, scale_rho, graded, spike_delay)
         extras = [fin['final_re'], fin['final_im'], fin['final_s']]
         if ad is not None:
             extras += [fin['final_th'], fin['final_ref']]
@@ -59,12 +60,12 @@ class _FusedForward(torch.autograd.Function):
     def backward(ctx, grad_spike, *_):
         real, imag, sin_decay, cos_decay = ctx.saved_tensors[:4]
         threshold = ctx.saved_tensors[4] if ctx.threshold is None else ctx.threshold
-        tau_rho, scale_rho, graded = ctx.consts
+        tau_rho, scale_rho, graded, spike_delay = ctx.consts
         need = ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
         gre, gim, gsin, gcos = _ops.rf_bwd(grad_spike, real, imag, threshold, sin_decay, cos_decay, tau_rho,
-                                           scale_rho, graded, need)
+                                           scale_rho, graded, need, spike_delay=spike_delay)
         resonator._raise_on_nan(grad_sin_decay=gsin, grad_cos_decay=gcos)
-        return (gre, gim, gsin, gcos) + (None,) * 13
+        return (gre, gim, gsin, gcos) + (None,) * 15
 
 
 class ResonatorBase(base.Neuron):
@@ -249,15 +250,31 @@ class Neuron(ResonatorBase):
         if not self._fusable:
             real, imag = self.dynamics(input)
             return self.spike(real, imag)
+        spike, _ = self._fused_forward(input, 0, None)
+        if self.drop is not None:
+            spike = self.drop(spike)
+        return spike
+
+    @property
+    def fuses_step_delay(self):
+        """True when ``forward_step_delayed`` can write the spikes one step late inside the kernel."""
+        return self._fusable and self.graded_spike is not True and self.drop is None
+
+    fuses_axon_delay = False   # a block's axonal delay stays a separate shift for this neuron
+
+    def forward_step_delayed(self, input, delay_head=None):
+        """``forward`` with the blocks' one-step delay folded in: ``(delayed_spike, last_spike)``."""
+        return self._fused_forward(input, 1, delay_head)
+
+    def _fused_forward(self, input, spike_delay, delay_head):
         real_input, imag_input = self._prepare(input)
-        spike, final_re, final_im, _ = _FusedForward.apply(
+        spike, final_re, final_im, final_s = _FusedForward.apply(
             real_input, imag_input, quantize(self.sin_decay), quantize(self.cos_decay), self.real_state,
             self.imag_state, self.threshold, self.s_scale, self.tau_rho * TAU_RHO_MULT,
-            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, None, None, None, None, 0.0, 0.0)
+            self.scale_rho * SCALE_RHO_MULT, self.graded_spike is True, None, None, None, None, 0.0, 0.0,
+            spike_delay, delay_head)
         if self.persistent_state:
             with torch.no_grad():
                 self.real_state = final_re
                 self.imag_state = final_im
-        if self.drop is not None:
-            spike = self.drop(spike)
-        return spike
+        return spike, final_s

@@ -16,6 +16,10 @@ class MODE(IntEnum):
 class _StraightThrough(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, step, floor):
+        if step == 1:
+            # x / 1 and y * 1 are identities in fp32: one kernel instead of three (the neuron classes
+            # quantise every decay with step 1 on every call)
+            return torch.floor(input) if floor else torch.round(input)
         scaled = input / step
         return (torch.floor(scaled) if floor else torch.round(scaled)) * step
 

@@ -493,6 +493,71 @@ def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
     assert_close(gvd, ref['grad_voltage_decay'], 'grad voltage decay', scale=pgrad_scale(1, (g_c, want['voltage'])))
 
 
+@pytest.mark.parametrize('shape', SHAPES)
+def test_alif_and_resonator_fused_step_delay(shape, cuda, ops):
+    """The one-step delay on the spike store of the ALIF, RF and ADRF forward kernels, and the
+    backward passes reading the gradient of the late series: same results as delaying the spikes
+    (advancing the gradient) in a separate pass."""
+    rng = rng_for('other_delay', shape)
+    B, C, T = shape
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    gs = rng.normal(size=shape).astype(np.float32)
+    g_early = O.shift(gs, -1)
+    zeros = dev(np.zeros(shape[:-1]), cuda)
+
+    def late_of(spike, h):
+        out = O.shift(spike, 1)
+        if h is not None:
+            out[..., 0] = h
+        return out
+
+    # ALIF
+    x = rng.normal(0.2, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, C, 700, 900), decays(rng, C, 150, 250)
+    td, rd = decays(rng, C, 300, 500), decays(rng, C, 300, 500)
+    ths = quant(rng.uniform(0.8, 1.5, size=shape[:-1]))
+    want = O.alif(x, 1.0, 0.5, cd, vd, td, rd, th_state=ths, grad_spike=g_early)
+    args = (dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(rd, cuda), dev(td, cuda), zeros, zeros, zeros,
+            dev(ths, cuda), 0.5, 1.0, W)
+    for h in (None, head):
+        (spike, voltage, thsum), fin = ops.alif_fwd(*args, dynamics_mode=False, spike_delay=1,
+                                                    delay_head=None if h is None else dev(h, cuda))
+        assert_exact(spike, late_of(want['spike'], h), 'late ALIF spikes')
+        assert_exact(fin['final_s'], want['spike'][..., -1], 'undelayed last spike')
+        assert_quantised_equal(voltage, want['voltage'], W, 'voltage')
+    gx, _, _ = ops.cuba_bwd(dev(gs, cuda), voltage, thsum, None, dev(cd, cuda), dev(vd, cuda), 100.0, 0.1, False, False,
+                            spike_delay=1)
+    g_v = O.spike_bwd(want['voltage'], want['threshold'] + want['refractory'], g_early, 100.0, 0.1, False)
+    assert_close(gx, want['grad_x'], 'ALIF grad_x of the late series', scale=li_scale(li_scale(g_v, vd), cd))
+
+    # RF and ADRF
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    sd, cdk = sincos(rng, C)
+    for adaptive in (False, True):
+        if adaptive:
+            want = O.adrf(re_in, im_in, 0.5, 0.25, sd, cdk, td, rd, th_state=ths, grad_spike=g_early)
+            ad = dict(ref_decay=dev(rd, cuda), th_decay=dev(td, cuda), ref_state=zeros, th_state=dev(ths, cuda),
+                      th_step=0.25, th0=0.5)
+            tau, srho = 50.0, 0.1
+        else:
+            want = O.rf(re_in, im_in, 0.5, sd, cdk, grad_spike=g_early)
+            ad, tau, srho = None, 0.25, 10.0
+        for h in (None, head):
+            outs, fin = ops.rf_fwd(dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cdk, cuda), zeros, zeros, 0.5,
+                                   W, adaptive=ad, spike_delay=1, delay_head=None if h is None else dev(h, cuda))
+            assert_exact(outs[0], late_of(want['spike'], h), f'late resonator spikes (adaptive={adaptive})')
+            assert_exact(fin['final_s'], want['spike'][..., -1], 'undelayed last spike')
+        thr = outs[3] if adaptive else 0.5
+        gre, gim, _, _ = ops.rf_bwd(dev(gs, cuda), outs[1], outs[2], thr, dev(sd, cuda), dev(cdk, cuda), tau, srho,
+                                    False, False, spike_delay=1)
+        thr_np = (want['threshold'] + want['refractory']) if adaptive else 0.5
+        s_re, s_im = cspike_term_scale(want['real'], want['imag'], thr_np, g_early, tau, srho, False)
+        S_re, S_im = res_scale(s_re, s_im, sd, cdk)
+        assert_close(gre, want['grad_re'], 'resonator grad_re of the late series', scale=S_re)
+        assert_close(gim, want['grad_im'], 'resonator grad_im of the late series', scale=S_im)
+
+
 @pytest.mark.parametrize('shape', [(2, 5, 50), (1, 257, 64), (4, 64, 128), (2, 8, 200), (3, 11, 33), (2, 3, 2)])
 @pytest.mark.parametrize('misalign', [False, True])
 def test_cuba_fused_axon_delay(shape, misalign, cuda, ops):
