@@ -62,20 +62,34 @@ THR = 1.25 + 0.01 / 4096
 # proportion to the batch: roofline.traffic = this figure x the units of a launch.
 NCU_TRAFFIC_PER_UNIT = {
     'cuba_fwd': 11.70,
+    'cuba_fwd_delayed': 11.70,
     'cuba_bwd': 11.88,
     'alif_fwd': 15.28,
-    'alif_bwd': 15.84,
-    'adrf_fwd': 24.16,
-    'adrf_bwd': 24.23,
-    'li_fwd': 7.76,
-    'li_bwd': 7.74,
-    'shift': 7.63,
-    'fir_conv': 7.76,
-    'delay_fir_fwd': 7.75,
-    'sigma_fwd': 7.75,
+    'alif_bwd': 15.82,
+    'adrf_fwd': 23.61,
+    'adrf_bwd': 24.04,
+    'li_fwd': 7.75,
+    'li_bwd': 7.73,
+    'sigma_fwd': 7.74,
     'delta_fwd': 7.74,
-    'sdnn_fwd': 7.75,
-    'cuba_fwd_delayed': 11.70,
+    'delta_bwd': 7.74,
+    'sdnn_fwd': 7.76,
+    'shift': 7.64,
+    'fir_conv': 7.78,
+    'delay_fir_fwd': 7.75,
+    'delay_fir_bwd': 7.76,
+    'cuba_fwd_train': 15.67,
+    'cuba_bwd_dgrad': 15.99,
+    'li_bwd_dgrad': 11.88,
+    'ath_fwd': 11.29,
+    'apth_fwd': 15.45,
+    'res_fwd': 15.70,
+    'adres_fwd': 23.63,
+    'spike_fwd': 7.67,
+    'spike_bwd': 11.76,
+    'cspike_fwd': 11.51,
+    'cspike_bwd': 19.45,
+    'sdnn_bwd': 11.92,
 }
 
 
@@ -376,9 +390,12 @@ def build_step(name, shape, device, seed):
         keep['g'] = g
         if name == 'cspike_bwd':
             return (lambda: _ops.cspike_bwd(re, im, 0.5, g, 0.25, 10.0, False)), 1, keep
+        # the two gradient streams are separate tensors: the same tensor twice would be read from HBM once
+        g2 = torch.empty(shape, device=device).normal_(0.0, 1.0, generator=gen)
+        keep['g2'] = g2
         if name == 'res_bwd':
-            return (lambda: _ops.res_bwd(g, g, None, None, sd, cdec, False)), 1, keep
-        return (lambda: _ops.res_bwd(g, g, re, im, sd, cdec, True)), 5, keep
+            return (lambda: _ops.res_bwd(g, g2, None, None, sd, cdec, False)), 1, keep
+        return (lambda: _ops.res_bwd(g, g2, re, im, sd, cdec, True)), 3, keep   # the scan and one fold per decay gradient
     if name in ('spike_fwd', 'spike_bwd'):
         v = torch.empty(shape, device=device).normal_(1.0, 1.0)
         if name == 'spike_fwd':

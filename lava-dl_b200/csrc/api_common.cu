@@ -335,15 +335,44 @@ __global__ void fold_stage2(const double* __restrict__ stage, float* __restrict_
   if (lane == 0) out[c] = (float)acc;
 }
 
+// One parameter per row of a [batch, n] problem (time-major rows, no spatial block under the
+// channel): thread (x, y) of a 32 x 8 block adds every eighth batch entry of channel x, so a warp
+// reads 32 neighbouring partials, and the eight slices meet in shared memory.  One launch, no stage
+// buffer: with 64 batch entries per channel the sliced fold below would start 64 x n blocks to add
+// 64 numbers each.
+__global__ void fold_columns(const double* __restrict__ partial, float* __restrict__ out, int64_t n, int64_t batches) {
+  __shared__ double part[8][33];
+  const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
+  double acc = 0.0;
+  if (c < n)
+    for (int64_t b = threadIdx.y; b < batches; b += 8) acc += partial[b * n + c];
+  part[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < n) {
+#pragma unroll
+    for (int y = 1; y < 8; ++y) acc += part[y][threadIdx.x];
+    out[c] = (float)acc;
+  }
+}
+
 int fold_param_grad(double* scratch, float* out, const RowGeom& g, int64_t n, cudaStream_t st) {
   if (n < 1) n = 1;
+  if (n > 1 && g.decay_block == 1 && g.rows_per_batch == n) {
+    fold_columns<<<(unsigned)((n + 31) / 32), dim3(32, 8), 0, st>>>(scratch, out, n, g.rows / g.rows_per_batch);
+    SB_CUDA(cudaGetLastError());
+    return SB_OK;
+  }
   const int64_t nparts = (n <= 1) ? (g.rows + kTileR - 1) / kTileR : g.rows;
   double* stage = scratch + nparts;
-  dim3 grid1(kFoldSlices, (unsigned)(n > 65535 ? 65535 : n));
+  // slices of about 2048 partials each, at most kFoldSlices (the stage buffer's size)
+  const int64_t per = (n <= 1) ? nparts : (g.rows / g.rows_per_batch) * g.decay_block;
+  int slices = (int)((per + 2047) / 2048);
+  slices = slices < 1 ? 1 : (slices > kFoldSlices ? kFoldSlices : slices);
+  dim3 grid1(slices, (unsigned)(n > 65535 ? 65535 : n));
   fold_stage1<<<grid1, 256, 0, st>>>(scratch, stage, g, n, nparts);
   SB_CUDA(cudaGetLastError());
   const int wpb = 4;
-  fold_stage2<<<(unsigned)((n + wpb - 1) / wpb), wpb * 32, 0, st>>>(stage, out, kFoldSlices, n);
+  fold_stage2<<<(unsigned)((n + wpb - 1) / wpb), wpb * 32, 0, st>>>(stage, out, slices, n);
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

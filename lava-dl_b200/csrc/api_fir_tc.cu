@@ -35,7 +35,7 @@
 //     stage the row's eight 128-bit words in shared memory (4 KB per warp) and
 //     write them with a (4 rows x 128 bytes) per instruction mapping -- one row
 //     per lane would cost 32 L1 wavefronts per store instruction.
-//   TMEM columns: 2 x 64 accumulators, 6 x 32 A_hi, 6 x 32 A_lo = 512.
+//   TMEM columns: 2 x 64 accumulators, 6 operand slots of 32 A_hi | 32 A_lo = 512.
 // Fused delay (axon.delay): shift(corr(g), -d) shifts the output, and
 // conv(shift(x, d)) equals shift(conv(x), d) for d >= 0 (a delay only prepends
 // zeros), so both are the same tiles written at a per-row offset s = 4 sq + e.
@@ -62,8 +62,7 @@ constexpr int kBoxBytes = kM * kN * 4;   // 16 KB
 constexpr int kARing = 6;                // operand slots in TMEM: 3 in use + 3 ahead
 constexpr int kBBoxBytes = 2 * kN * 128; // one 64 x 32 box of the Toeplitz factor: rows 0-31 hi, 32-63 lo
 constexpr int kAccCols = 2 * kN;         // hi*hi + lo*hi | hi*lo
-constexpr int kColAhi = 2 * kAccCols;            // 128
-constexpr int kColAlo = kColAhi + kARing * kN;   // 320
+constexpr int kColA = 2 * kAccCols;              // 128: operand slot s at kColA + 64 s, hi | lo
 constexpr int kTmemCols = 512;
 
 // warps: split 0-3, drain 4-7, two issue warps, producer warp
@@ -80,7 +79,7 @@ constexpr int kOffBar = kOffSq + kM * 4;
 constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
 constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-static_assert(kColAlo + kARing * kN == kTmemCols, "TMEM column budget");
+static_assert(kColA + kARing * 2 * kN == kTmemCols, "TMEM column budget");
 
 __host__ __device__ constexpr uint32_t idesc_n(int n) { return idesc_tf32(kM, n); }
 
@@ -109,7 +108,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     }
     for (int i = 0; i < kARing; ++i) {
       mbar_init(bar_aready + 8 * i, kM);
-      mbar_init(bar_afree + 8 * i, 2);
+      mbar_init(bar_afree + 8 * i, 4);   // one arrival per drain warp
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_mma + 8 * i, 1);
@@ -204,8 +203,8 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
               const int slots[3] = {as2, as1, as};
 #pragma unroll
               for (int c = 0; c < 3; ++c) {
-                const uint32_t ah = tmem + kColAhi + (uint32_t)slots[c] * kN;
-                const uint32_t al = tmem + kColAlo + (uint32_t)slots[c] * kN;
+                const uint32_t ah = tmem + kColA + (uint32_t)slots[c] * (2 * kN);
+                const uint32_t al = ah + kN;
                 const uint32_t bb = b0 + c * (kBBoxBytes >> 4);
                 const bool lo = has_lo[slots[c]] != 0;
 #pragma unroll
@@ -217,14 +216,6 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
               }
             }
             umma_commit(bar_mma + 8 * acc);
-          }
-          // Operand slots nobody reads after the tile of this arrival: its oldest
-          // box, and at the end of a block the two newer ones as well.  Both issue
-          // threads commit (the barrier counts 2): each covers the tiles it issued.
-          umma_commit(bar_afree + 8 * as2);
-          if (a == narr - 1) {
-            umma_commit(bar_afree + 8 * as1);
-            umma_commit(bar_afree + 8 * as);
           }
           ++tcount;
         }
@@ -301,18 +292,19 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       if (ause >= 1) wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
       tc_fence_after();
       if (any) {
-        uint32_t lo[32];
+        uint32_t hl[64];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           // hi = x truncated to TF32 (exact in the operand format), lo = x - hi exactly (13
           // bits, of which the tensor core keeps 11): two instructions per value
           const uint32_t h = xr[j] & kTf32Mask;
-          lo[j] = __float_as_uint(__fsub_rn(__uint_as_float(xr[j]), __uint_as_float(h)));
-          xr[j] = h;
+          hl[32 + j] = __float_as_uint(__fsub_rn(__uint_as_float(xr[j]), __uint_as_float(h)));
+          hl[j] = h;
         }
-        tmem_st32(tmem + lane_base + kColAlo + as * kN, lo);
+        tmem_st64(tmem + lane_base + kColA + as * (2 * kN), hl);   // hi | lo side by side: one store
+      } else {
+        tmem_st32(tmem + lane_base + kColA + as * (2 * kN), xr);
       }
-      tmem_st32(tmem + lane_base + kColAhi + as * kN, xr);
       tmem_st_wait();
       tc_fence_before();
       if (tid == 0) has_lo[as] = any;
@@ -328,6 +320,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     int s_row = 0;
     int64_t blk = blockIdx.x;
     uint32_t tcount = 0;
+    int oldest = 0;                              // operand slot of the oldest box of the current tile
     uint8_t* stage = sm + kOffStage;                        // rows 32 ew .. 32 ew + 31 are this warp's
     int* sq_s = reinterpret_cast<int*>(sm + kOffSq);
     for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
@@ -337,16 +330,27 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         bool ok;
         ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead);
         tc_fence_after();
-        uint32_t r0[32], r1[32];
+        // This warp has now seen every tile up to this one complete, so nothing reads the tile's
+        // oldest box any more (nor, after a block's last tile, the two newer ones): the operand
+        // slots go back to the split warps from here.  A commit per slot from the issue threads
+        // would do the same, but every tcgen05 instruction takes its turn on the issue path that
+        // the MMAs need, and three commits per tile cost as much there as five MMAs.
+        if (lane == 0) {
+          const int nfree = (tile == ntile - 1) ? 3 : 1;
+          for (int i = 0; i < nfree; ++i) {
+            mbar_arrive(bar_afree + 8 * oldest);
+            if (++oldest == kARing) oldest = 0;
+          }
+        }
+        uint32_t r[64];
         const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccCols);
-        tmem_ld32(taddr, r0);
-        tmem_ld32(taddr + kN, r1);
+        tmem_ld64(taddr, r);
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(bar_free + 8 * acc);
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
+        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(__uint_as_float(r[j]), __uint_as_float(r[32 + j]));
 
         const bool live = row < rows && ok;
         float* rowp = out + (live ? row : 0) * (int64_t)T;

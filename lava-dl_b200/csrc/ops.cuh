@@ -13,12 +13,14 @@
 // Every op also states the pipeline shape its TMA kernel runs with: STAGES per
 // warp, BOXES of TILE steps per stage (shared memory per warp = STAGES *
 // max(NIN, NOUT - NBIT) * BOXES * TILE * 128 B).  The values were picked by
-// sweeping shapes on a B200 (fractions are of the measured copy bandwidth):
-// light single-stream ops want long row segments and deep prefetch (LI backward
-// 3 x 4 x 32: 0.94), heavier ones more resident warps (CUBA forward 3 x 3 x 32:
-// 0.85, LI forward 0.91), multi-stream ops one box of 32 steps (CUBA backward
-// 0.84) or of 16 steps when four streams would leave too few warps (ADRF
-// backward 0.79 against 0.51 with 32).
+// sweeping shapes on a B200; where a comment beside SB_PIPE gives two numbers
+// they are fractions of the measured copy bandwidth before and after.  The
+// pattern: one-stream ops want long row segments (three or four boxes per
+// stage) and three stages; ops that write two full-width streams per input
+// stream want five or six stages of one box; ops with two input tiles want two
+// boxes and three or four stages; ops with four or more full-width streams fall
+// to 16-step tiles only when 32-step tiles would leave fewer than four warps
+// per SM.
 #pragma once
 
 #include "common.cuh"
@@ -402,7 +404,7 @@ struct ResBwd {
   static constexpr int NIN = PGRAD ? 4 : 2, NOUT = 2;  // in: g_re, g_im, [re, im]
   static constexpr bool REVERSE = true;
   static constexpr int NBIT = 0;
-  SB_PIPE((PGRAD ? 4 : 3), 1, 32);   // with sin / cos gradients (four input tiles): 0.54 -> 0.57 against 16-step tiles
+  SB_PIPE((PGRAD ? 3 : 4), 2, 32);   // two boxes per stage: 0.80 -> 0.92 (four stages), 0.89 -> 0.93 with sin / cos gradients (three)
   struct Params {
     DecayVec sin_decay, cos_decay;
     double* partial_sin;
