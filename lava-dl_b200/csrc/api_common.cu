@@ -162,26 +162,32 @@ int make_row_map_box(CUtensorMap* out, const void* base, int64_t rows, int64_t T
 
 // [d4][d3][d2][d1][d0] fp32 tensor, d0 contiguous, dense strides; boxes are stored unswizzled and
 // out-of-range elements read as zero (which is how the convolution gets its padding).
-int make_map_5d(CUtensorMap* out, const void* base, const uint64_t (&dims)[5], const uint32_t (&box)[5]) {
+// 5-D fp32 tensor map with explicit strides: dims[0] is the contiguous dimension, strides[i] is the
+// byte stride of dims[i + 1] (multiples of 16; they need not grow with i, so the dimensions can be
+// listed in the order the box should have in shared memory).  swizzle: 0 none, 1 the 128-byte pattern
+// over 16-byte chunks, 2 the 128-byte pattern over 32-byte chunks (what an M-major TF32 operand of
+// tcgen05.mma wants); the box's inner extent must then be 128 bytes.  Out-of-range coordinates read zeros.
+int make_map_5d(CUtensorMap* out, const void* base, const uint64_t (&dims)[5], const uint64_t (&strides)[4],
+                const uint32_t (&box)[5], int swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return SB_ERR_UNSUPPORTED;
   }
   bind_primary_context();
-  cuuint64_t gdims[5], strides[4];
+  cuuint64_t gdims[5], gstr[4];
   cuuint32_t gbox[5], estr[5];
-  cuuint64_t pitch = 4;
   for (int i = 0; i < 5; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];
     estr[i] = 1;
-    pitch *= dims[i];
-    if (i < 4) strides[i] = pitch;
+    if (i < 4) gstr[i] = strides[i];
   }
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), gdims, strides, gbox, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), gdims, gstr, gbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                               : (swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled (5-D) failed with CUresult %d (dims %llu %llu %llu %llu %llu, base %p)", (int)r,
               (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],

@@ -3,38 +3,44 @@
 // GEMM with time kept innermost:
 //
 //   y[n, co, ho, wo, t] = sum_{ci, i, j} w[co, ci, i, j] * x[n, ci, ho + i - ph, wo + j - pw, t]
-//   D[m, co]            = sum_k A[m, k] * B[co, k]        m = (wo, t) position, k = (ci, i, j)
+//   D[m, co]            = sum_k A[m, k] * B[co, k]        m = (wo, t) position, k = (i, j, ci)
 //
 // A tile is M = 128 positions (4 output columns x 32 time steps) of one output
-// row, N = up to 64 output channels, and K = Ci * kh * kw in chunks of CIG input
-// channels (<= 96 operand columns).  Spikes are 0 / 1 and block weights sit on a
-// 1/32 grid, both exact in TF32, so the fp32 accumulation gives bit for bit the
-// sums of the fp32 kernel and of the CPU; any other operand is split v = hi + lo
-// (two TF32 values) and the tile accumulates hi*hi + lo*hi + hi*lo, as the
-// temporal filter does, so float inputs (the input-gradient pass) keep fp32
-// accuracy.  A box whose values are all exact skips its lo products.
+// row and N = up to 64 output channels.  Nothing gathers the A operand: an input
+// row lands in shared memory as [column][channel][32 steps] (a 5-D TMA box whose
+// dimensions are listed in that order, 128-byte swizzle over 32-byte chunks), which is exactly the
+// M-major TF32 operand layout of tcgen05.mma -- 32 positions contiguous, channels 128
+// bytes apart in atoms of four, the next output column one column stride further on.  Tap
+// (i, j) over channels 8 g .. 8 g + 7 is then one MMA (K = 8) whose descriptor
+// starts j columns and g channel groups into the slot of row ho + i; the padding
+// is the zero fill of the TMA box, in space and in the channel count alike.
 //
-// Data flow per CTA (persistent over work items, one CTA per SM, 10 warps).  A
+// Spikes are 0 / 1 and block weights sit on a 1/32 grid, both exact in TF32, so
+// the fp32 accumulation gives bit for bit the sums of the fp32 kernel and of the
+// CPU.  Any other operand is split v = hi + lo (two TF32 values): the scan warps
+// look at every row that lands and, if a value has low mantissa bits, leave its
+// hi parts in place and write the lo parts to a second slot; the tile then
+// accumulates hi*hi + lo*hi + hi*lo, so float inputs keep fp32 accuracy.
+//
+// Data flow per CTA (persistent over work items, one CTA per SM, 12 warps).  A
 // work item is (sample, group of 4 output columns, chunk of 32 steps); the CTA
 // walks down its output rows, so every input row is fetched once per item (the
 // only re-read is the kw - 1 column halo between neighbouring items):
-//   producer (1 thread): one 5-D TMA box per input row -- 32 steps x (4 + kw - 1)
-//     columns x all Ci channels, zero filled outside the image, which is the
-//     padding -- into a ring of row slots in shared memory: the kh rows a tile reads plus up to 16
-//     rows requested ahead (a row is a few KB, so the ring has to be deep to cover the TMA latency).
-//   split (4 warps, one position per thread): gathers the thread's K values of
-//     the chunk from the kh live row slots, splits them, and writes them to TMEM
-//     (tcgen05.st): the A operand of the MMAs is read from TMEM, K along columns.
-//   issue (1 thread): KC / 8 x tcgen05.mma kind::tf32 (M128, N = Co padded to 16) per chunk into
-//     a ring of TMEM accumulators; B (the weights, split, K-major, 128-byte swizzle) is built once
-//     per CTA in shared memory.  (Two issue threads on alternating tiles, each with half of the
-//     rings, measured slower: the rings get too shallow.)
+//   producer (1 thread): one TMA box per input row into a ring of row slots --
+//     the kh rows a tile reads plus the rows requested ahead.
+//   scan (4 warps): reads each landed row once with 128-bit loads, decides
+//     whether it needs lo parts and writes them if so (ring of kh + 2 lo slots).
+//   issue (3 threads, taking tiles in turn): kh x kw x ceil(Ci / 8) MMAs (kind::tf32, M128, N = Co
+//     padded to 16) per tile into a ring of TMEM accumulators; B (the weights, split, K-major,
+//     128-byte swizzle) is built once per CTA in shared memory.  An MMA with an M-major operand
+//     holds its thread for well over a hundred cycles while the pipe accepts the next thread's
+//     (16 -> 32 channels, 3 x 3, [32, 16, 16, 16, 300]: 0.42 / 0.23 / 0.19 / 0.31 ms with 1 / 2 / 3 / 4
+//     issue threads; 0.11 ms with the MMAs taken out).
 //   drain (4 warps): tcgen05.ld of the accumulator, one coalesced 128-byte store
-//     per warp and output channel.
-// TMEM columns: 128 for a ring of accumulators (2 for 64 output channels, 8 for 16), 384 for a
-// ring of operand slots of one chunk each (4 to 8 slots).  A chunk of exact values takes one slot;
-// a chunk that needs lo parts takes the next slot as well.  The rings are what hides the latency of
-// the hand-offs (split -> MMA -> drain take about a microsecond per round trip).
+//     per warp and output channel; having seen a tile complete they also hand its
+//     oldest row slot back to the producer -- every tcgen05 instruction, commits
+//     included, queues behind the MMAs, so the issue thread commits once per tile.
+// TMEM holds accumulators only (up to 8 of npad columns).
 // Every wait is bounded; a wait that runs out sets a CTA-wide flag that ends all
 // other waits, SB_DEV_TMA_TIMEOUT is recorded, loads and MMAs in flight are
 // waited for, TMEM is freed.  Tensor maps cover this GPU's memory only; no
@@ -45,7 +51,8 @@
 using namespace sb;
 
 namespace sb {
-int make_map_5d(CUtensorMap* out, const void* base, const uint64_t (&dims)[5], const uint32_t (&box)[5]);
+int make_map_5d(CUtensorMap* out, const void* base, const uint64_t (&dims)[5], const uint64_t (&strides)[4],
+                const uint32_t (&box)[5], int swizzle);
 }
 
 namespace {
@@ -53,23 +60,22 @@ namespace {
 constexpr int kM = 128;
 constexpr int kWG = 4;                       // output columns per tile
 constexpr int kTT = 32;                      // time steps per tile
-constexpr int kKCmax = 96;                   // operand columns per K-chunk
 constexpr int kAccCols = 64;                 // output channels per launch group
-constexpr int kAccSpace = 128;               // TMEM columns of the accumulator ring
-constexpr int kColA = kAccSpace;             // operand slots start here
 constexpr int kTmemCols = 512;
-constexpr int kMaxSlots = 8;                 // operand slots / accumulators at most
+constexpr int kMaxAcc = 8;                   // accumulators at most
 
-constexpr int kIssueWarp = 8, kProdWarp = 9;
+constexpr int kNumIssue = 3;                 // MMA-issuing threads, taking tiles in turn
+constexpr int kIssueWarp = 8, kProdWarp = kIssueWarp + kNumIssue;
 constexpr int kThreads = 32 * (kProdWarp + 1);
 constexpr int kMaxRing = 24;                 // row slots: the kh live rows plus the rows in flight
+constexpr int kMaxLo = 8;                    // lo slots: kh + 2
 
 struct ConvTc {
   int N, Ci, Co, H, W, Ho, Wo, ph, pw, T;
-  int nchunk;      // K-chunks per tile
+  int cg;          // groups of 8 input channels (the last one zero filled past Ci)
   int npad;        // MMA N: output channels of this launch's channel groups, padded to 16
   int nwg, ntc;    // work-item grid: column groups, time chunks
-  int slot_bytes;  // one input row in shared memory: Ci x (4 + kw - 1) x 128 B
+  int slot_bytes;  // one input row in shared memory: (4 + kw - 1) columns x 8 cg channels x 128 B
   int ring;        // row slots: kh live rows + rows requested ahead (the TMA latency to hide)
   int b_bytes;     // one of the two weight factors in shared memory
 };
@@ -92,47 +98,47 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-template <int KH, int KW, int CIG>
+template <int KH, int KW>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ wgt, float* __restrict__ y,
                const ConvTc g, unsigned int* status) {
-  constexpr int KC = CIG * KH * KW;
-  constexpr int KCpad = (KC + 7) & ~7;
-  constexpr int WB = kWG + KW - 1;
-  static_assert(KCpad <= kKCmax && KH + 2 <= kMaxRing, "chunk or ring too large");
+  constexpr uint32_t RL = KH + 2;              // lo slots
+  static_assert(KH + 2 <= kMaxLo && KH + 2 <= kMaxRing, "ring too small for the kernel height");
   const uint32_t R = (uint32_t)g.ring;
+  const uint32_t G = (uint32_t)g.cg;
+  const uint32_t col_bytes = G * 1024u;        // one column of a row slot: 8 G channels x 128 B
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // layout: weights hi | weights lo | row ring | barriers | words
+  // layout: weights hi | weights lo | row ring | lo ring | barriers | words
   const int off_bhi = 0, off_blo = g.b_bytes, off_ring = 2 * g.b_bytes;
-  const int off_bar = off_ring + R * g.slot_bytes;
-  const uint32_t bar_full = base + off_bar;              // [R]
-  const uint32_t bar_rawfree = bar_full + 8 * kMaxRing;  // [R]
-  const uint32_t bar_aready = bar_rawfree + 8 * kMaxRing;  // [NA]
-  const uint32_t bar_afree = bar_aready + 8 * kMaxSlots;   // [NA]
-  const uint32_t bar_mma = bar_afree + 8 * kMaxSlots;      // [NACC]
-  const uint32_t bar_accfree = bar_mma + 8 * kMaxSlots;    // [NACC]
-  constexpr int kBarBytes = 8 * (2 * kMaxRing + 4 * kMaxSlots);
+  const int off_lo = off_ring + R * g.slot_bytes;
+  const int off_bar = off_lo + RL * g.slot_bytes;
+  const uint32_t bar_full = base + off_bar;                // [R]   a row has landed
+  const uint32_t bar_rawfree = bar_full + 8 * kMaxRing;    // [R]   no MMA reads the row any more
+  const uint32_t bar_ready = bar_rawfree + 8 * kMaxRing;   // [RL]  the row is scanned (and split)
+  const uint32_t bar_lofree = bar_ready + 8 * kMaxLo;      // [RL]
+  const uint32_t bar_mma = bar_lofree + 8 * kMaxLo;        // [NACC]
+  const uint32_t bar_accfree = bar_mma + 8 * kMaxAcc;      // [NACC]
+  constexpr int kBarBytes = 8 * (2 * kMaxRing + 2 * kMaxLo + 2 * kMaxAcc);
   volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(sm + off_bar + kBarBytes);
   volatile int* dead = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 4);
-  volatile int* has_lo = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 8);  // [NA]
-  // operand slots of KCpad columns; accumulators of npad columns
-  constexpr uint32_t NA = (kTmemCols - kColA) / KCpad < kMaxSlots ? (kTmemCols - kColA) / KCpad : kMaxSlots;
-  static_assert(NA >= 4, "at least four operand slots");
-  const uint32_t NACC = (uint32_t)(kAccSpace / g.npad) < (uint32_t)kMaxSlots ? (uint32_t)(kAccSpace / g.npad)
-                                                                             : (uint32_t)kMaxSlots;
+  volatile int* has_lo = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 8);  // [RL]
+  const uint32_t NACC = (uint32_t)(kTmemCols / g.npad) < (uint32_t)kMaxAcc ? (uint32_t)(kTmemCols / g.npad)
+                                                                           : (uint32_t)kMaxAcc;
 
   if (tid == 0) {
     for (uint32_t i = 0; i < R; ++i) {
       mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_rawfree + 8 * i, kM);
+      mbar_init(bar_rawfree + 8 * i, 4);     // one arrival per drain warp
     }
-    for (int i = 0; i < kMaxSlots; ++i) {
-      mbar_init(bar_aready + 8 * i, kM);
-      mbar_init(bar_afree + 8 * i, 1);
+    for (uint32_t i = 0; i < RL; ++i) {
+      mbar_init(bar_ready + 8 * i, kM);
+      mbar_init(bar_lofree + 8 * i, 4);
+    }
+    for (int i = 0; i < kMaxAcc; ++i) {
       mbar_init(bar_mma + 8 * i, 1);
       mbar_init(bar_accfree + 8 * i, kM);
     }
@@ -146,19 +152,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   }
 
   // Weight factor of this CTA's channel group, split into two TF32 values, K-major with the
-  // 128-byte swizzle: column k' = chunk * KCpad + (cl * KH + i) * KW + j, rows = output channels.
+  // 128-byte swizzle: column k' = ((i * KW + j) * G + group) * 8 + channel in group, rows = output channels.
   const int co0 = blockIdx.y * kAccCols;
-  const int ktot = g.nchunk * KCpad;
+  const int ktot = KH * KW * (int)G * 8;
   int any_blo = 0;
   for (int e = tid; e < g.npad * ktot; e += kThreads) {
     const int co = e / ktot, kp = e - co * ktot;
-    const int c = kp / KCpad, kl = kp - c * KCpad;
+    const int q = kp >> 3, tap = q / (int)G, ci = (q - tap * (int)G) * 8 + (kp & 7);
     float v = 0.f;
-    if (kl < KC) {
-      const int cl = kl / (KH * KW), r = kl - cl * (KH * KW);
-      const int ci = c * CIG + cl;
-      if (ci < g.Ci && co0 + co < g.Co) v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + ci) * (KH * KW) + r);
-    }
+    if (ci < g.Ci && co0 + co < g.Co) v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + ci) * (KH * KW) + tap);
     const uint32_t hi = tf32_rn(v), lo = tf32_rn(__fsub_rn(v, __uint_as_float(hi)));
     any_blo |= (lo != 0u);
     const int kk = kp & 31;
@@ -174,7 +176,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
 
   const int64_t nitems = (int64_t)g.N * g.nwg * g.ntc;
   const int Q = g.Ho + KH - 1;                  // input rows an item walks through
-  const uint32_t idesc = idesc_tf32(kM, g.npad);
+  const uint32_t idesc = idesc_tf32(kM, g.npad) | kIdescAMajorM;
 
   if (warp == kProdWarp) {
     // ---------------- producer: one TMA box per input row ----------------
@@ -187,7 +189,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           if (rq.wraps >= 1 && !wait_or_dead(bar_rawfree + 8 * rq.slot, (rq.wraps - 1u) & 1u, dead)) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * rq.slot;
           mbar_expect_tx(bar, (uint32_t)g.slot_bytes);
-          tma_load_5d(base + off_ring + rq.slot * g.slot_bytes, &xmap, tc * kTT, wg * kWG - g.pw, q - g.ph, 0, n, bar);
+          // box dimensions: steps, channels, columns, rows, samples
+          tma_load_5d(base + off_ring + rq.slot * g.slot_bytes, &xmap, tc * kTT, 0, wg * kWG - g.pw, q - g.ph, n, bar);
         }
       }
       if (*dead) {
@@ -196,157 +199,143 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
       }
     }
     __syncwarp();
-  } else if (warp == kIssueWarp) {
-    // ---------------- issue: the MMAs of every tile (one thread) ----------------
+  } else if (warp >= kIssueWarp && warp < kIssueWarp + kNumIssue) {
+    // ---------------- issue: the MMAs of every kNumIssue-th tile (one thread per warp) ----------------
+    // A thread waits well over a hundred cycles on each MMA it issues; the tensor pipe takes the next
+    // thread's MMA meanwhile.
+    const uint32_t me = (uint32_t)(warp - kIssueWarp);
     if (lane == 0) {
       const uint32_t bhi = desc_lo(base + off_bhi), blo = desc_lo(base + off_blo);
+      const uint32_t a_deschi = kDescHiMMajor;
       const uint32_t box16 = (uint32_t)(g.npad * 128) >> 4;   // one 32-column box of the factor, in 16-byte units
-      Cursor ca{0, 0}, cd{0, 0};   // operand slots, accumulators
-      uint32_t last_acc = 0, last_phase = 0, tiles = 0;
+      Cursor rq{0, 0}, lq{0, 0}, cd{0, 0};   // oldest live row, its lo slot, accumulators
+      uint32_t last_acc = 0, last_phase = 0, tiles = 0, turn = 0;   // turn: whose tile this is
       bool ok = true;
       for (int64_t item = blockIdx.x; item < nitems; item += gridDim.x) {
         for (int ho = 0; ho < g.Ho; ++ho) {
+          const bool mine = turn == me;
+          if (++turn == (uint32_t)kNumIssue) turn = 0;
+          if (!mine) {
+            cd.next(NACC);
+            rq.next(R);
+            lq.next(RL);
+            continue;
+          }
           const uint32_t acc = cd.slot;
           if (cd.wraps >= 1) ok = wait_or_dead(bar_accfree + 8 * acc, (cd.wraps - 1u) & 1u, dead) && ok;
           const uint32_t d_tmem = tmem + acc * (uint32_t)g.npad;
-          for (int c = 0; c < g.nchunk; ++c) {
-            // the chunk's hi values sit in the next slot; its lo values, if it has any, in the slot after
-            uint32_t as = ca.slot;
-            ok = wait_or_dead(bar_aready + 8 * as, ca.wraps & 1u, dead) && ok;
-            tc_fence_after();
-            const bool alo = has_lo[as] != 0;
-            if (ok) {
-              const uint32_t ah = tmem + kColA + as * KCpad;
+          // rows ho .. ho + KH - 1 of this item (all of them are waited for: the tile before this one was
+          // another thread's)
+          uint32_t rs[KH], ls[KH];
+          {
+            Cursor r = rq, l = lq;
 #pragma unroll
-              for (int ks = 0; ks < KCpad / 8; ++ks) {
-                const uint32_t kp = (uint32_t)(c * KCpad + 8 * ks);
-                const uint32_t boff = (kp >> 5) * box16 + ((kp & 31u) >> 2);
-                umma_ts(d_tmem, ah + 8 * ks, bhi + boff, idesc, (c | ks) ? 1u : 0u);
-                if (any_blo) umma_ts(d_tmem, ah + 8 * ks, blo + boff, idesc, 1u);
-              }
+            for (int i = 0; i < KH; ++i, r.next(R), l.next(RL)) {
+              ok = wait_or_dead(bar_ready + 8 * l.slot, l.wraps & 1u, dead) && ok;
+              rs[i] = r.slot;
+              ls[i] = l.slot;
             }
-            umma_commit(bar_afree + 8 * as);
-            ca.next(NA);
-            if (alo) {
-              as = ca.slot;
-              ok = wait_or_dead(bar_aready + 8 * as, ca.wraps & 1u, dead) && ok;
-              tc_fence_after();
-              if (ok) {
-                const uint32_t al = tmem + kColA + as * KCpad;
+          }
+          tc_fence_after();
+          if (ok) {
+            uint32_t first = 0u;
 #pragma unroll
-                for (int ks = 0; ks < KCpad / 8; ++ks) {
-                  const uint32_t kp = (uint32_t)(c * KCpad + 8 * ks);
-                  umma_ts(d_tmem, al + 8 * ks, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
+            for (int i = 0; i < KH; ++i) {
+              const uint32_t row_hi = base + off_ring + rs[i] * g.slot_bytes;
+              const uint32_t row_lo = base + off_lo + ls[i] * g.slot_bytes;
+              const bool alo = has_lo[ls[i]] != 0;
+#pragma unroll
+              for (int j = 0; j < KW; ++j) {
+                // tap (i, j), channels 8 cgi ..: the operand starts j columns and cgi atoms into the row.
+                // Three loops with run-time trip counts rather than three conditional MMAs per
+                // channel group: a predicated-off MMA still takes its ~46 cycles on the issue path.
+                const uint32_t a_hi = row_hi + (uint32_t)j * col_bytes, a_lo = row_lo + (uint32_t)j * col_bytes;
+                const uint32_t kp0 = (uint32_t)(i * KW + j) * G * 8u;
+#pragma unroll 1
+                for (uint32_t cgi = 0; cgi < G; ++cgi) {
+                  const uint32_t kp = kp0 + cgi * 8u;
+                  umma_ss(d_tmem, desc_lo_mmajor(a_hi + cgi * 1024u, col_bytes),
+                          a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, first);
+                  first = 1u;
+                }
+                const uint32_t nblo = any_blo ? G : 0u, nalo = alo ? G : 0u;
+#pragma unroll 1
+                for (uint32_t cgi = 0; cgi < nblo; ++cgi) {
+                  const uint32_t kp = kp0 + cgi * 8u;
+                  umma_ss(d_tmem, desc_lo_mmajor(a_hi + cgi * 1024u, col_bytes),
+                          a_deschi, blo + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
+                }
+#pragma unroll 1
+                for (uint32_t cgi = 0; cgi < nalo; ++cgi) {
+                  const uint32_t kp = kp0 + cgi * 8u;
+                  umma_ss(d_tmem, desc_lo_mmajor(a_lo + cgi * 1024u, col_bytes),
+                          a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
                 }
               }
-              umma_commit(bar_afree + 8 * as);
-              ca.next(NA);
             }
           }
           umma_commit(bar_mma + 8 * acc);
           last_acc = acc; last_phase = cd.wraps & 1u; ++tiles;
           cd.next(NACC);
+          rq.next(R);
+          lq.next(RL);
         }
+        // the item's last KH - 1 rows belong to no further tile
+        for (int q = g.Ho; q < Q; ++q) { rq.next(R); lq.next(RL); }
       }
-      // nothing may still be writing TMEM when it is freed: wait for the last tile's MMAs
+      // nothing may still be writing TMEM when it is freed: wait for this thread's last tile
       if (tiles >= 1) mbar_wait(bar_mma + 8 * last_acc, last_phase);
     }
     __syncwarp();
   } else if (warp < 4) {
-    // ---------------- split warps: row slots -> K values of this position -> TMEM ----------------
-    const int wl = tid >> 5, tl = tid & 31;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    Cursor rq{0, 0};               // oldest live row of the tile
-    Cursor ca{0, 0};               // operand slots
+    // ---------------- scan warps: does a landed row need lo parts? ----------------
+    // Each thread reads its 16-byte words of the slot (the same offsets in the lo slot: both
+    // start on a 1024-byte boundary, so the swizzle pattern is the same).
+    Cursor rq{0, 0}, lq{0, 0};
     for (int64_t item = blockIdx.x; item < nitems; item += gridDim.x) {
-      for (int ho = 0; ho < g.Ho; ++ho) {
-        // rows ho .. ho + KH - 1 of this item; only the newest one can still be in flight
-        const uint8_t* rowp[KH];
-        {
-          Cursor r = rq;
-#pragma unroll
-          for (int i = 0; i < KH; ++i, r.next(R)) {
-            if (ho == 0 || i == KH - 1) wait_or_dead(bar_full + 8 * r.slot, r.wraps & 1u, dead);
-            rowp[i] = sm + off_ring + r.slot * g.slot_bytes + wl * 128 + tl * 4;
-          }
+      for (int q = 0; q < Q; ++q, rq.next(R), lq.next(RL)) {
+        wait_or_dead(bar_full + 8 * rq.slot, rq.wraps & 1u, dead);
+        uint8_t* row = sm + off_ring + rq.slot * g.slot_bytes;
+        uint32_t low = 0;
+        for (int off = tid * 16; off < g.slot_bytes; off += kM * 16) {
+          const uint4 v = *reinterpret_cast<const uint4*>(row + off);
+          low |= v.x | v.y | v.z | v.w;
         }
-        for (int c = 0; c < g.nchunk; ++c) {
-          const int ci0 = c * CIG;
-          uint32_t v[KCpad];
-          uint32_t low = 0;
-#pragma unroll
-          for (int k = 0; k < KCpad; ++k) {
-            uint32_t val = 0u;
-            if (k < KC) {
-              constexpr int KK = KH * KW;
-              const int cl = k / KK, r = k % KK, i = r / KW, j = r % KW;
-              if (ci0 + cl < g.Ci)
-                val = *reinterpret_cast<const uint32_t*>(rowp[i] + ((ci0 + cl) * WB + j) * 128);
-            }
-            v[k] = val;
-            low |= val;
+        int any;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "bar.red.or.pred p, 1, %2, q;\n\t"
+            "selp.s32 %0, 1, 0, p;\n\t}"
+            : "=r"(any)
+            : "r"(low & ~kTf32Mask), "n"(kM)
+            : "memory");
+        // the lo slot (and its flag) of the row that used it KH + 2 rows ago is free?
+        if (lq.wraps >= 1) wait_or_dead(bar_lofree + 8 * lq.slot, (lq.wraps - 1u) & 1u, dead);
+        if (any) {
+          // hi = x truncated to TF32 stays in the row's own slot, lo = x - hi (exact) goes to the lo slot
+          uint8_t* lorow = sm + off_lo + lq.slot * g.slot_bytes;
+          for (int off = tid * 16; off < g.slot_bytes; off += kM * 16) {
+            uint4 v = *reinterpret_cast<const uint4*>(row + off);
+            uint4 h, l;
+            h.x = v.x & kTf32Mask; l.x = __float_as_uint(__fsub_rn(__uint_as_float(v.x), __uint_as_float(h.x)));
+            h.y = v.y & kTf32Mask; l.y = __float_as_uint(__fsub_rn(__uint_as_float(v.y), __uint_as_float(h.y)));
+            h.z = v.z & kTf32Mask; l.z = __float_as_uint(__fsub_rn(__uint_as_float(v.z), __uint_as_float(h.z)));
+            h.w = v.w & kTf32Mask; l.w = __float_as_uint(__fsub_rn(__uint_as_float(v.w), __uint_as_float(h.w)));
+            *reinterpret_cast<uint4*>(row + off) = h;
+            *reinterpret_cast<uint4*>(lorow + off) = l;
           }
-          // does any value of the chunk need a lo part?  (spike trains do not)
-          int any;
-          asm volatile(
-              "{\n\t.reg .pred p, q;\n\t"
-              "setp.ne.b32 q, %1, 0;\n\t"
-              "bar.red.or.pred p, 1, %2, q;\n\t"
-              "selp.s32 %0, 1, 0, p;\n\t}"
-              : "=r"(any)
-              : "r"(low & ~kTf32Mask), "n"(kM)
-              : "memory");
-          // `any` is the same in every thread of the four warps: one slot for the hi values and, only
-          // when some value needs it, the next slot for the lo values
-          const uint32_t as = ca.slot;
-          if (ca.wraps >= 1) wait_or_dead(bar_afree + 8 * as, (ca.wraps - 1u) & 1u, dead);
-          tc_fence_after();
-          const uint32_t ah = tmem + lane_base + kColA + as * KCpad;
-#pragma unroll
-          for (int g8 = 0; g8 < KCpad / 8; ++g8) {
-            uint32_t hi[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) hi[e] = v[g8 * 8 + e] & kTf32Mask;
-            tmem_st8(ah + g8 * 8, hi);
-          }
-          tmem_st_wait();
-          tc_fence_before();
-          if (tid == 0) has_lo[as] = any;
-          mbar_arrive(bar_aready + 8 * as);
-          ca.next(NA);
-          if (any) {
-            const uint32_t as2 = ca.slot;
-            if (ca.wraps >= 1) wait_or_dead(bar_afree + 8 * as2, (ca.wraps - 1u) & 1u, dead);
-            tc_fence_after();
-            const uint32_t al = tmem + lane_base + kColA + as2 * KCpad;
-#pragma unroll
-            for (int g8 = 0; g8 < KCpad / 8; ++g8) {
-              uint32_t lo[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const uint32_t h = v[g8 * 8 + e] & kTf32Mask;
-                lo[e] = __float_as_uint(__fsub_rn(__uint_as_float(v[g8 * 8 + e]), __uint_as_float(h)));
-              }
-              tmem_st8(al + g8 * 8, lo);
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bar_aready + 8 * as2);
-            ca.next(NA);
-          }
+          fence_proxy_async();   // the MMAs read what these stores wrote
         }
-        // the oldest row of this tile is not read again
-        mbar_arrive(bar_rawfree + 8 * rq.slot);
-        rq.next(R);
+        if (tid == 0) has_lo[lq.slot] = any;
+        mbar_arrive(bar_ready + 8 * lq.slot);
       }
-      // the item's last KH - 1 rows
-      for (int q = g.Ho; q < Q; ++q, rq.next(R)) mbar_arrive(bar_rawfree + 8 * rq.slot);
     }
   } else {
     // ---------------- drain warps: accumulator -> output rows ----------------
     const int m = tid - kM, wl = m >> 5, tl = m & 31;
     const int ew = warp & 3;
-    Cursor cd{0, 0};
+    Cursor cd{0, 0}, rq{0, 0}, lq{0, 0};
     const int64_t cstride = (int64_t)g.Ho * g.Wo * g.T;
     const int64_t rstride = (int64_t)g.Wo * g.T;
     const int nco = min(g.npad, g.Co - co0);
@@ -359,17 +348,33 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
         const uint32_t acc = cd.slot;
         const bool ok = wait_or_dead(bar_mma + 8 * acc, cd.wraps & 1u, dead);
         tc_fence_after();
+        // This warp has seen every tile up to this one complete: no MMA reads the tile's oldest
+        // row any more, nor, after an item's last tile, its other rows.
+        if (lane == 0) {
+          const int nfree = (ho == g.Ho - 1) ? KH : 1;
+          for (int i = 0; i < nfree; ++i, rq.next(R), lq.next(RL)) {
+            mbar_arrive(bar_rawfree + 8 * rq.slot);
+            mbar_arrive(bar_lofree + 8 * lq.slot);
+          }
+        }
         const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + acc * (uint32_t)g.npad;
+        // the tile's npad columns in as few loads as their count allows: 32 at a time, then 16
 #pragma unroll 1
-        for (int cb = 0; cb < g.npad; cb += 16) {
-          uint32_t r[16];
-          tmem_ld16(taddr + cb, r);
+        for (int cb = 0; cb < g.npad;) {
+          uint32_t r[32];
+          const int ncol = (g.npad - cb >= 32) ? 32 : 16;
+          if (ncol == 32) {
+            tmem_ld32(taddr + cb, r);
+          } else {
+            tmem_ld16(taddr + cb, *reinterpret_cast<uint32_t(*)[16]>(r));
+          }
           tmem_ld_wait();
           if (ok && live_pos) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
-              if (cb + e < nco) dst[(cb + e) * cstride] = __uint_as_float(r[e]);
+            for (int e = 0; e < 32; ++e)
+              if (e < ncol && cb + e < nco) dst[(cb + e) * cstride] = __uint_as_float(r[e]);
           }
+          cb += ncol;
         }
         tc_fence_before();
         mbar_arrive(bar_accfree + 8 * acc);
@@ -385,14 +390,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   }
 }
 
-// input channels per K-chunk: 3 x 3 -> 8 (72 columns, nine MMAs), 5 x 5 -> 2 (50 -> 56 columns, seven MMAs),
-// 1 x 1 -> 32; picked so that common channel counts fill their chunks
-constexpr int cig_for(int kh, int kw) { return kh * kw == 1 ? 32 : (kh * kw == 9 ? 8 : 2); }
-
 struct TcPlan {
   ConvTc g;
   size_t smem;
-  int cig;
   bool ok;
 };
 
@@ -404,28 +404,25 @@ TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int
   if (T < kTT || (T & 3) || Ci > 256 || N > 65535 * 16 || H > (1 << 20) || W > (1 << 20) || T > (1 << 28)) return p;
   const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
   if (Ho < 1 || Wo < 1) return p;
-  const int cig = cig_for((int)kh, (int)kw);
-  const int kc = cig * (int)(kh * kw), kcpad = (kc + 7) & ~7;
-  const int nchunk = (int)((Ci + cig - 1) / cig);
+  const int cg = (int)((Ci + 7) / 8);
   const int ngroup = (int)((Co + kAccCols - 1) / kAccCols);
   const int64_t co_last = Co - (int64_t)(ngroup - 1) * kAccCols;
   // every channel group is launched with the same MMA N: the widest group, padded to 16
   const int npad = (int)(((ngroup > 1 ? kAccCols : co_last) + 15) & ~15);
-  const int slot = (int)(Ci * (kWG + kw - 1) * 128);
-  const int64_t ktot = (int64_t)nchunk * kcpad;
+  const int64_t slot = (int64_t)(kWG + kw - 1) * cg * 1024;
+  const int64_t ktot = kh * kw * cg * 8;
   const int64_t b_bytes = (((ktot + 31) / 32) * npad * 128 + 1023) & ~1023LL;
-  const int64_t fixed = 2 * b_bytes + 8 * (2 * kMaxRing + 4 * kMaxSlots) + 128 + 1024;
-  // rows in flight beyond the kh live ones: as many as fit in about 200 KB, at most 16, at least 2
-  int64_t ahead = (200 * 1024 - fixed) / slot - kh;
+  const int64_t fixed = 2 * b_bytes + 8 * (2 * kMaxRing + 2 * kMaxLo + 2 * kMaxAcc) + 128 + 1024 + (kh + 2) * slot;
+  // rows in flight beyond the kh live ones: as many as fit in 224 KB, at most 16, at least 2
+  int64_t ahead = (224 * 1024 - fixed) / slot - kh;
   if (ahead > 16) ahead = 16;
   if (ahead < 2 || ngroup > 65535) return p;
   const int R = (int)(kh + ahead);
   const int64_t smem = fixed + (int64_t)R * slot;
-  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, nchunk, npad,
-               (int)((Wo + kWG - 1) / kWG), (int)((T + kTT - 1) / kTT), slot, R, (int)b_bytes};
+  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, cg, npad,
+               (int)((Wo + kWG - 1) / kWG), (int)((T + kTT - 1) / kTT), (int)slot, R, (int)b_bytes};
   // at least 120 KB so that two CTAs (two TMEM allocations of 512 columns) never share an SM
   p.smem = (size_t)(smem < 120 * 1024 ? 120 * 1024 : smem);
-  p.cig = cig;
   p.ok = true;
   return p;
 }
@@ -441,10 +438,14 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
   if ((((uintptr_t)x) | ((uintptr_t)y)) & 15u) return SB_OK;
   const TcPlan p = plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T);
   if (!p.ok) return SB_OK;
+  // The box lists its dimensions as (steps, channels, columns, rows, samples): that is the order a
+  // row slot has in shared memory.  Channels past Ci are out of range and read zeros.
   CUtensorMap xmap;
-  const uint64_t dims[5] = {(uint64_t)T, (uint64_t)W, (uint64_t)H, (uint64_t)Ci, (uint64_t)N};
-  const uint32_t box[5] = {(uint32_t)kTT, (uint32_t)(kWG + kw - 1), 1u, (uint32_t)Ci, 1u};
-  int rc = make_map_5d(&xmap, x, dims, box);
+  const uint64_t dims[5] = {(uint64_t)T, (uint64_t)Ci, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+  const uint64_t strides[4] = {(uint64_t)(H * W * T * 4), (uint64_t)(T * 4), (uint64_t)(W * T * 4),
+                               (uint64_t)(Ci * H * W * T * 4)};
+  const uint32_t box[5] = {(uint32_t)kTT, (uint32_t)(8 * p.g.cg), (uint32_t)(kWG + kw - 1), 1u, 1u};
+  int rc = make_map_5d(&xmap, x, dims, strides, box, 2);
   if (rc != SB_OK) return rc;
   const int64_t nitems = (int64_t)p.g.N * p.g.nwg * p.g.ntc;
   const int ngroup = (int)((Co + kAccCols - 1) / kAccCols);
@@ -452,15 +453,15 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
   const dim3 grid((unsigned)gx, (unsigned)ngroup);
   unsigned int* status = status_ptr();
   if (!status) return SB_ERR_CUDA;
-#define SB_GO(KH, KW, CIG)                                                                                   \
+#define SB_GO(KH, KW)                                                                                        \
   {                                                                                                          \
-    auto fn = conv_tc_kernel<KH, KW, CIG>;                                                                   \
+    auto fn = conv_tc_kernel<KH, KW>;                                                                        \
     SB_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem)); \
     fn<<<grid, kThreads, p.smem, st>>>(xmap, weight, y, p.g, status);                                        \
   }
-  if (kh == 1) SB_GO(1, 1, cig_for(1, 1))
-  else if (kh == 3) SB_GO(3, 3, cig_for(3, 3))
-  else SB_GO(5, 5, cig_for(5, 5))
+  if (kh == 1) SB_GO(1, 1)
+  else if (kh == 3) SB_GO(3, 3)
+  else SB_GO(5, 5)
 #undef SB_GO
   SB_CUDA(cudaGetLastError());
   *taken = true;
@@ -469,8 +470,7 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
 
 }  // namespace sb
 
-// the contraction must be long enough for the tile hand-offs to pay off (measured: 5 x 5 over two
-// channels, 50 taps, runs faster on the fp32 kernel; 3 x 3 over sixteen, 144 taps, twice as fast here)
+// the contraction must be long enough for the tile hand-offs to pay off
 constexpr int64_t kMinTapsForAuto = 64;
 
 extern "C" int sb_conv_fits_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh,

@@ -59,14 +59,15 @@ namespace {
 constexpr int kM = 128;                  // rows per block = MMA M
 constexpr int kN = 32;                   // outputs per tile = steps per box
 constexpr int kBoxBytes = kM * kN * 4;   // 16 KB
-constexpr int kARing = 6;                // operand slots in TMEM: 3 in use + 3 ahead
+constexpr int kNumIssue = 2;             // MMA-issuing threads, one accumulator each
+constexpr int kARing = (512 - kNumIssue * 2 * kN) / (2 * kN);   // operand slots in TMEM: 3 in use, the rest ahead
 constexpr int kBBoxBytes = 2 * kN * 128; // one 64 x 32 box of the Toeplitz factor: rows 0-31 hi, 32-63 lo
 constexpr int kAccCols = 2 * kN;         // hi*hi + lo*hi | hi*lo
-constexpr int kColA = 2 * kAccCols;              // 128: operand slot s at kColA + 64 s, hi | lo
+constexpr int kColA = kNumIssue * kAccCols;      // operand slot s at kColA + 64 s, hi | lo
 constexpr int kTmemCols = 512;
 
 // warps: split 0-3, drain 4-7, two issue warps, producer warp
-constexpr int kIssueWarp = 8, kProdWarp = 10;
+constexpr int kIssueWarp = 8, kProdWarp = kIssueWarp + kNumIssue;
 constexpr int kThreads = 32 * (kProdWarp + 1);
 constexpr int kRing = 11;                                // landing slots in shared memory
 constexpr int kOffRaw = 0;
@@ -74,9 +75,9 @@ constexpr int kOffB = kOffRaw + kRing * kBoxBytes;
 constexpr int kOffStage = kOffB + 3 * kBBoxBytes;        // output staging, 4 KB private to each drain warp
 constexpr int kOffSq = kOffStage + kBoxBytes;            // 128 row shifts (>> 2)
 constexpr int kOffBar = kOffSq + kM * 4;
-// barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[2], acc_free[2];
+// barriers: full[kRing], raw_free[kRing], a_ready[kARing], a_free[kARing], mma_done[kNumIssue], acc_free[kNumIssue];
 // then the TMEM base word, the dead flag, has_lo[kARing]
-constexpr int kNumBars = 2 * kRing + 2 * kARing + 4;
+constexpr int kNumBars = 2 * kRing + 2 * kARing + 2 * kNumIssue;
 constexpr int kSmemBytes = kOffBar + 8 * kNumBars + 8 + 4 * kARing + 8 + 1024;  // + slack to align the base
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(kColA + kARing * 2 * kN == kTmemCols, "TMEM column budget");
@@ -96,7 +97,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
   const uint32_t bar_aready = bar_rawfree + 8 * kRing;
   const uint32_t bar_afree = bar_aready + 8 * kARing;
   const uint32_t bar_mma = bar_afree + 8 * kARing;
-  const uint32_t bar_free = bar_mma + 16;
+  const uint32_t bar_free = bar_mma + 8 * kNumIssue;
   volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(sm + kOffBar + 8 * kNumBars);
   volatile int* dead = reinterpret_cast<volatile int*>(sm + kOffBar + 8 * kNumBars + 4);
   volatile int* has_lo = reinterpret_cast<volatile int*>(sm + kOffBar + 8 * kNumBars + 8);  // [kARing]
@@ -110,7 +111,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       mbar_init(bar_aready + 8 * i, kM);
       mbar_init(bar_afree + 8 * i, 4);   // one arrival per drain warp
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kNumIssue; ++i) {
       mbar_init(bar_mma + 8 * i, 1);
       mbar_init(bar_free + 8 * i, kM);
     }
@@ -182,7 +183,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       }
     }
     __syncwarp();
-  } else if (warp == kIssueWarp || warp == kIssueWarp + 1) {
+  } else if (warp >= kIssueWarp && warp < kIssueWarp + kNumIssue) {
     // ---------------- issue: the MMAs of every other tile (one thread per warp) ----------------
     // One thread issues an MMA every ~46 cycles whatever its size; two threads do twice that.
     const uint32_t me = (uint32_t)(warp - kIssueWarp);   // this thread's accumulator
@@ -192,11 +193,11 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       uint32_t ause = 0, tcount = 0;
       for (int64_t f = 0; f < total; ++f) {
         if (a >= 2) {
-          if ((tcount & 1u) == me) {
+          if (tcount % kNumIssue == me) {
             const uint32_t acc = me;
             bool ok2;
             ok2 = wait_or_dead(bar_aready + 8 * as, ause & 1u, dead);
-            if (tcount >= 2) ok2 = wait_or_dead(bar_free + 8 * acc, ((tcount >> 1) - 1u) & 1u, dead) && ok2;
+            if (tcount >= kNumIssue) ok2 = wait_or_dead(bar_free + 8 * acc, (tcount / kNumIssue - 1u) & 1u, dead) && ok2;
             tc_fence_after();
             if (ok2) {
               const uint32_t d_tmem = tmem + acc * kAccCols;
@@ -225,8 +226,8 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       }
       // nothing may still be writing TMEM when it is freed: wait for this thread's last tile
       if (tcount > me) {
-        const uint32_t last = ((tcount - 1u - me) & ~1u) + me;
-        mbar_wait(bar_mma + 8 * me, (last >> 1) & 1u);
+        const uint32_t own = (tcount - 1u - me) / kNumIssue + 1u;   // tiles this thread issued
+        mbar_wait(bar_mma + 8 * me, (own - 1u) & 1u);
       }
     }
     __syncwarp();
@@ -326,9 +327,9 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
     for (int64_t b = 0; b < my_nblk; ++b, blk += gridDim.x) {
       const int64_t row = blk * kM + et;
       for (int tile = 0; tile < ntile; ++tile, ++tcount) {
-        const int acc = (int)(tcount & 1u);
+        const int acc = (int)(tcount % kNumIssue);
         bool ok;
-        ok = wait_or_dead(bar_mma + 8 * acc, (tcount >> 1) & 1u, dead);
+        ok = wait_or_dead(bar_mma + 8 * acc, (tcount / kNumIssue) & 1u, dead);
         tc_fence_after();
         // This warp has now seen every tile up to this one complete, so nothing reads the tile's
         // oldest box any more (nor, after a block's last tile, the two newer ones): the operand

@@ -14,6 +14,16 @@ constexpr uint32_t kTf32Mask = 0xffffe000u;
 // Only the low word depends on the address.
 constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3ffffu) >> 4) | (1u << 16); }
+// Descriptor of an M-major TF32 operand.  The only layout tcgen05.mma takes for it is the 128-byte
+// swizzle over 32-byte chunks (what TMA writes with SWIZZLE_128B_ATOM_32B): 32 consecutive rows of
+// the tile are the 128 contiguous bytes of one K index, four K indices sit 128 bytes apart (one
+// 512-byte atom), the next four 512 bytes further on (the stride offset), and the next 32 rows
+// start `row_group_stride` bytes further on (the leading offset).
+constexpr uint32_t kDescHiMMajor = (uint32_t)(512 >> 4) | (1u << 14) | (1u << 29);
+__device__ __forceinline__ uint32_t desc_lo_mmajor(uint32_t saddr, uint32_t row_group_stride) {
+  return ((saddr & 0x3ffffu) >> 4) | ((row_group_stride >> 4) << 16);
+}
+constexpr uint32_t kIdescAMajorM = 1u << 15;   // instruction descriptor flag: A is M-major
 // Instruction descriptor: D = f32, A = B = tf32, both K-major, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -28,6 +38,19 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32
       "mov.b64 db, {%2, %4};\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, both operands through shared-memory descriptors (A's high word
+// is passed in: an M-major operand states its strides differently from the K-major B).
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -113,6 +136,28 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
+}
+// N consecutive columns (a multiple of 8) in as few stores as the x64 / x32 / x16 / x8 shapes allow
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* v) {
+  static_assert(N % 8 == 0, "whole 8-column groups");
+  if constexpr (N >= 64) {
+    tmem_st64(taddr, *reinterpret_cast<const uint32_t(*)[64]>(v));
+    tmem_st_cols<N - 64>(taddr + 64, v + 64);
+  } else if constexpr (N >= 32) {
+    tmem_st32(taddr, *reinterpret_cast<const uint32_t(*)[32]>(v));
+    tmem_st_cols<N - 32>(taddr + 32, v + 32);
+  } else if constexpr (N >= 16) {
+    tmem_st16(taddr, *reinterpret_cast<const uint32_t(*)[16]>(v));
+    tmem_st_cols<N - 16>(taddr + 16, v + 16);
+  } else if constexpr (N >= 8) {
+    tmem_st8(taddr, *reinterpret_cast<const uint32_t(*)[8]>(v));
+  }
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
