@@ -75,7 +75,7 @@ NCU_TRAFFIC_PER_UNIT = {
     'delta_bwd': 7.74,
     'sdnn_fwd': 7.76,
     'shift': 7.64,
-    'fir_conv': 7.78,
+    'fir_conv': 7.76,
     'delay_fir_fwd': 7.75,
     'delay_fir_bwd': 7.76,
     'cuba_fwd_train': 15.67,
@@ -84,6 +84,8 @@ NCU_TRAFFIC_PER_UNIT = {
     'ath_fwd': 11.29,
     'apth_fwd': 15.45,
     'res_fwd': 15.70,
+    'res_bwd': 15.64,
+    'res_bwd_pgrad': 24.21,
     'adres_fwd': 23.63,
     'spike_fwd': 7.67,
     'spike_bwd': 11.76,
@@ -166,6 +168,7 @@ WORKLOADS = {
     'cuba_fwd_cfg0': Workload('cuba_fwd_cfg0', (16, 512, 1000), 12),
     # the same through slayer.neuron.cuba.Neuron.forward: the kernel plus the Python / ATen glue of one call
     'cuba_fwd_cfg0_api': Workload('cuba_fwd_cfg0_api', (16, 512, 1000), 12),
+    'cuba_fwd_cfg0_graph': Workload('cuba_fwd_cfg0_graph', (16, 512, 1000), 12),   # the same call replayed as a CUDA graph
     # block output path: spikes written one step late plus a per-neuron axonal delay of 0..62 steps, same 12 B
     'cuba_fwd_delayed': Workload('cuba_fwd_delayed', (64, 8192, 2000), 12),
     # backward of the same: g_spike + voltage in, g_x out
@@ -444,9 +447,12 @@ def build_step(name, shape, device, seed):
             return _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=False, want_spike=True,
                                  spike_delay=1, axon_delay=d['delay'])
         return step, 1, d
-    if name == 'cuba_fwd_cfg0_api':
+    if name in ('cuba_fwd_cfg0_api', 'cuba_fwd_cfg0_graph'):
         import lava_dl_b200.slayer as slayer
         neuron = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03).to(device)
+        if name == 'cuba_fwd_cfg0_graph':
+            graphed = slayer.utils.Graphed(neuron, d['x'])
+            return (lambda: graphed(graphed.input)), 1, (d, neuron, graphed)
 
         def step():
             with torch.no_grad():
@@ -911,7 +917,7 @@ def time_steps(step, steps, warmup, device, dist, sampler=None):
 
 # legs reported beside the headline in the default run: every benchmark configuration's kernels
 EXTRA_LEGS = ('cuba_bwd', 'alif_fwd', 'alif_bwd', 'adrf_fwd', 'adrf_bwd', 'shift', 'fir_conv', 'delay_fir_fwd',
-              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cfg4_fwd', 'cfg4_train')
+              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cuba_fwd_cfg0_graph', 'cfg4_fwd', 'cfg4_train')
 
 
 def run_extra_legs(device, dist, world, rank, steps=5, warmup=3, legs=EXTRA_LEGS):

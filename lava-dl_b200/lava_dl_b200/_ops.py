@@ -718,10 +718,7 @@ def conv_dgrad(grad_y, weight, padding):
     kh, kw = weight.shape[2], weight.shape[3]
     wt = weight.detach()[:, :, :, :, 0] if weight.dim() == 5 else weight.detach()
     wt = wt.flip(2, 3).transpose(0, 1).contiguous()
-    # gradients are not exact in TF32, so the tensor-core kernel would run its three-product form:
-    # measured slower than the fp32 kernel on the benchmark network, which therefore takes the
-    # latter whenever it can launch the shape
+    # gradients are not exact in TF32: the tensor-core kernel splits them into TF32 pairs (still faster
+    # than the fp32 kernel where the swapped problem fits it); the library chooses
     pad = (kh - 1 - int(padding[0]), kw - 1 - int(padding[1]))
-    n, co, ho = grad_y.shape[0], grad_y.shape[1], grad_y.shape[2]
-    fp32_ok = 0 < n * (ho + 2 * pad[0] - kh + 1) <= 65535 and co * kh * kw * 16 * 4 <= 96 * 1024
-    return conv_fwd(grad_y, wt, pad, path=0 if fp32_ok else -1)
+    return conv_fwd(grad_y, wt, pad, path=-1)

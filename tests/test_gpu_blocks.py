@@ -168,3 +168,30 @@ def test_wide_cuba_recurrent_takes_the_stepwise_walk(cuda, slayer):
         fast = recurrent.recurrent_walk(z, small.neuron, mat)
         slow = recurrent._StepwiseRecurrent.apply(z, twin.neuron, mat)
     assert_exact(fast, slow, 'one-launch kernel against the stepwise walk')
+
+
+def test_graphed_replay_of_an_inference_call(cuda, slayer):
+    """``utils.Graphed`` replays a neuron's (and a block chain's) forward as one CUDA graph:
+    the same spikes as the eager call on every new input, refused for persistent state."""
+    gen = torch.Generator().manual_seed(5)
+    neuron = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03).to(cuda)
+    x0 = torch.empty(4, 96, 64).normal_(0.3, 1.0, generator=gen).to(cuda)
+    graphed = slayer.utils.Graphed(neuron, x0)
+    for _ in range(3):
+        x = torch.empty(4, 96, 64).normal_(0.3, 1.0, generator=gen).to(cuda)
+        with torch.no_grad():
+            want = neuron(x)
+        assert_exact(graphed(x), want, 'graphed neuron forward')
+    net = torch.nn.Sequential(slayer.block.cuba.Dense(dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03), 96, 40),
+                              slayer.block.cuba.Dense(dict(threshold=1.25, current_decay=0.25, voltage_decay=0.03), 40, 10)).to(cuda)
+    s0 = (torch.rand(4, 96, 64, generator=gen) < 0.2).float().to(cuda)
+    gnet = slayer.utils.Graphed(net, s0)
+    s1 = (torch.rand(4, 96, 64, generator=gen) < 0.2).float().to(cuda)
+    with torch.no_grad():
+        want = net(s1)
+    assert_exact(gnet(s1), want, 'graphed chain of blocks')
+    with pytest.raises(RuntimeError):
+        graphed(torch.zeros(4, 96, 32, device=cuda))
+    keeper = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03, persistent_state=True).to(cuda)
+    with pytest.raises(RuntimeError):
+        slayer.utils.Graphed(keeper, x0)
