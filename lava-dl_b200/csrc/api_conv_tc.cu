@@ -10,10 +10,13 @@
 // row lands in shared memory as [column][channel][32 steps] (a 5-D TMA box whose
 // dimensions are listed in that order, 128-byte swizzle over 32-byte chunks), which is exactly the
 // M-major TF32 operand layout of tcgen05.mma -- 32 positions contiguous, channels 128
-// bytes apart in atoms of four, the next output column one column stride further on.  Tap
-// (i, j) over channels 8 g .. 8 g + 7 is then one MMA (K = 8) whose descriptor
-// starts j columns and g channel groups into the slot of row ho + i; the padding
-// is the zero fill of the TMA box, in space and in the channel count alike.
+// bytes apart in atoms of four, the next output column one column stride further on.  An
+// MMA (K = 8) reads eight consecutive 128-byte (column, channel) rows of the slot of input row
+// ho + i: with 8 or more channels per column that is tap (i, j) over channels 8 g .. 8 g + 7
+// (the descriptor starts j columns and g atoms into the slot); with 2 or 4 channels per column
+// it is 4 or 2 neighbouring taps at once (the weights of taps past kw are zeros), so a
+// 2-channel 5 x 5 layer takes 10 MMAs per tile instead of 25 with zero-filled channels.  The
+// padding is the zero fill of the TMA box, in space and in the channel count alike.
 //
 // Spikes are 0 / 1 and block weights sit on a 1/32 grid, both exact in TF32, so
 // the fp32 accumulation gives bit for bit the sums of the fp32 kernel and of the
@@ -35,7 +38,7 @@
 //     128-byte swizzle) is built once per CTA in shared memory.  An MMA with an M-major operand
 //     holds its thread for well over a hundred cycles while the pipe accepts the next thread's
 //     (16 -> 32 channels, 3 x 3, [32, 16, 16, 16, 300]: 0.42 / 0.23 / 0.19 / 0.31 ms with 1 / 2 / 3 / 4
-//     issue threads; 0.11 ms with the MMAs taken out).
+//     issue threads; 0.11 ms with the MMAs taken out; 0.15 ms with the MMAs of a kernel row in one loop).
 //   drain (4 warps): tcgen05.ld of the accumulator, one coalesced 128-byte store
 //     per warp and output channel; having seen a tile complete they also hand its
 //     oldest row slot back to the producer -- every tcgen05 instruction, commits
@@ -72,10 +75,12 @@ constexpr int kMaxLo = 8;                    // lo slots: kh + 2
 
 struct ConvTc {
   int N, Ci, Co, H, W, Ho, Wo, ph, pw, T;
-  int cg;          // groups of 8 input channels (the last one zero filled past Ci)
+  int cpc;         // channels per column of a row slot: 2, 4, or a multiple of 8 (zero filled past Ci)
+  int nm;          // MMAs per kernel row: each reads 8 consecutive 128-byte (column, channel) rows of the slot
+  int box_bytes;   // bytes one TMA box delivers: columns x cpc x 128
   int npad;        // MMA N: output channels of this launch's channel groups, padded to 16
   int nwg, ntc;    // work-item grid: column groups, time chunks
-  int slot_bytes;  // one input row in shared memory: (4 + kw - 1) columns x 8 cg channels x 128 B
+  int slot_bytes;  // stride of the row slots (box_bytes rounded up to 1024)
   int ring;        // row slots: kh live rows + rows requested ahead (the TMA latency to hide)
   int b_bytes;     // one of the two weight factors in shared memory
 };
@@ -105,8 +110,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   constexpr uint32_t RL = KH + 2;              // lo slots
   static_assert(KH + 2 <= kMaxLo && KH + 2 <= kMaxRing, "ring too small for the kernel height");
   const uint32_t R = (uint32_t)g.ring;
-  const uint32_t G = (uint32_t)g.cg;
-  const uint32_t col_bytes = G * 1024u;        // one column of a row slot: 8 G channels x 128 B
+  const uint32_t NM = (uint32_t)g.nm;
+  const uint32_t col_bytes = (uint32_t)g.cpc * 128u;   // one column of a row slot
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -152,15 +157,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   }
 
   // Weight factor of this CTA's channel group, split into two TF32 values, K-major with the
-  // 128-byte swizzle: column k' = ((i * KW + j) * G + group) * 8 + channel in group, rows = output channels.
+  // 128-byte swizzle: rows = output channels, column k' = (i * NM + m) * 8 + r, where MMA m of kernel
+  // row i reads the slot's rows 8 m .. 8 m + 7 -- with 8 or more channels per column that is tap
+  // j = m / (cpc / 8) over channels 8 (m % (cpc / 8)) + r, with 2 or 4 channels per column it is taps
+  // j = m (8 / cpc) + r / cpc over channel r % cpc (taps past KW get zero weights).
   const int co0 = blockIdx.y * kAccCols;
-  const int ktot = KH * KW * (int)G * 8;
+  const int ktot = KH * (int)NM * 8;
   int any_blo = 0;
   for (int e = tid; e < g.npad * ktot; e += kThreads) {
     const int co = e / ktot, kp = e - co * ktot;
-    const int q = kp >> 3, tap = q / (int)G, ci = (q - tap * (int)G) * 8 + (kp & 7);
+    const int q = kp >> 3, r = kp & 7, i = q / (int)NM, m = q - i * (int)NM;
+    int j, ci;
+    if (g.cpc >= 8) {
+      const int G = g.cpc >> 3;
+      j = m / G;
+      ci = (m - j * G) * 8 + r;
+    } else {
+      j = m * (8 / g.cpc) + r / g.cpc;
+      ci = r % g.cpc;
+    }
+    const int tap = i * KW + j;
     float v = 0.f;
-    if (ci < g.Ci && co0 + co < g.Co) v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + ci) * (KH * KW) + tap);
+    if (j < KW && ci < g.Ci && co0 + co < g.Co) v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + ci) * (KH * KW) + tap);
     const uint32_t hi = tf32_rn(v), lo = tf32_rn(__fsub_rn(v, __uint_as_float(hi)));
     any_blo |= (lo != 0u);
     const int kk = kp & 31;
@@ -188,7 +206,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
         for (int q = 0; q < Q; ++q, rq.next(R)) {
           if (rq.wraps >= 1 && !wait_or_dead(bar_rawfree + 8 * rq.slot, (rq.wraps - 1u) & 1u, dead)) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * rq.slot;
-          mbar_expect_tx(bar, (uint32_t)g.slot_bytes);
+          mbar_expect_tx(bar, (uint32_t)g.box_bytes);
           // box dimensions: steps, channels, columns, rows, samples
           tma_load_5d(base + off_ring + rq.slot * g.slot_bytes, &xmap, tc * kTT, 0, wg * kWG - g.pw, q - g.ph, n, bar);
         }
@@ -244,33 +262,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
               const uint32_t row_hi = base + off_ring + rs[i] * g.slot_bytes;
               const uint32_t row_lo = base + off_lo + ls[i] * g.slot_bytes;
               const bool alo = has_lo[ls[i]] != 0;
-#pragma unroll
-              for (int j = 0; j < KW; ++j) {
-                // tap (i, j), channels 8 cgi ..: the operand starts j columns and cgi atoms into the row.
-                // Three loops with run-time trip counts rather than three conditional MMAs per
-                // channel group: a predicated-off MMA still takes its ~46 cycles on the issue path.
-                const uint32_t a_hi = row_hi + (uint32_t)j * col_bytes, a_lo = row_lo + (uint32_t)j * col_bytes;
-                const uint32_t kp0 = (uint32_t)(i * KW + j) * G * 8u;
+              // MMA m of this kernel row reads the slot's rows 8 m .. 8 m + 7 (the next output column
+              // starts one column further on: the leading offset).  Three loops with run-time trip
+              // counts rather than three conditional MMAs per step: a predicated-off MMA still takes
+              // its ~46 cycles on the issue path.
+              const uint32_t kp0 = (uint32_t)i * NM * 8u;
 #pragma unroll 1
-                for (uint32_t cgi = 0; cgi < G; ++cgi) {
-                  const uint32_t kp = kp0 + cgi * 8u;
-                  umma_ss(d_tmem, desc_lo_mmajor(a_hi + cgi * 1024u, col_bytes),
-                          a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, first);
-                  first = 1u;
-                }
-                const uint32_t nblo = any_blo ? G : 0u, nalo = alo ? G : 0u;
+              for (uint32_t m = 0; m < NM; ++m) {
+                const uint32_t kp = kp0 + m * 8u;
+                umma_ss(d_tmem, desc_lo_mmajor(row_hi + m * 1024u, col_bytes),
+                        a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, first);
+                first = 1u;
+              }
+              const uint32_t nblo = any_blo ? NM : 0u, nalo = alo ? NM : 0u;
 #pragma unroll 1
-                for (uint32_t cgi = 0; cgi < nblo; ++cgi) {
-                  const uint32_t kp = kp0 + cgi * 8u;
-                  umma_ss(d_tmem, desc_lo_mmajor(a_hi + cgi * 1024u, col_bytes),
-                          a_deschi, blo + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
-                }
+              for (uint32_t m = 0; m < nblo; ++m) {
+                const uint32_t kp = kp0 + m * 8u;
+                umma_ss(d_tmem, desc_lo_mmajor(row_hi + m * 1024u, col_bytes),
+                        a_deschi, blo + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
+              }
 #pragma unroll 1
-                for (uint32_t cgi = 0; cgi < nalo; ++cgi) {
-                  const uint32_t kp = kp0 + cgi * 8u;
-                  umma_ss(d_tmem, desc_lo_mmajor(a_lo + cgi * 1024u, col_bytes),
-                          a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
-                }
+              for (uint32_t m = 0; m < nalo; ++m) {
+                const uint32_t kp = kp0 + m * 8u;
+                umma_ss(d_tmem, desc_lo_mmajor(row_lo + m * 1024u, col_bytes),
+                        a_deschi, bhi + (kp >> 5) * box16 + ((kp & 31u) >> 2), idesc, 1u);
               }
             }
           }
@@ -297,7 +312,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
         wait_or_dead(bar_full + 8 * rq.slot, rq.wraps & 1u, dead);
         uint8_t* row = sm + off_ring + rq.slot * g.slot_bytes;
         uint32_t low = 0;
-        for (int off = tid * 16; off < g.slot_bytes; off += kM * 16) {
+        for (int off = tid * 16; off < g.box_bytes; off += kM * 16) {
           const uint4 v = *reinterpret_cast<const uint4*>(row + off);
           low |= v.x | v.y | v.z | v.w;
         }
@@ -315,7 +330,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
         if (any) {
           // hi = x truncated to TF32 stays in the row's own slot, lo = x - hi (exact) goes to the lo slot
           uint8_t* lorow = sm + off_lo + lq.slot * g.slot_bytes;
-          for (int off = tid * 16; off < g.slot_bytes; off += kM * 16) {
+          for (int off = tid * 16; off < g.box_bytes; off += kM * 16) {
             uint4 v = *reinterpret_cast<const uint4*>(row + off);
             uint4 h, l;
             h.x = v.x & kTf32Mask; l.x = __float_as_uint(__fsub_rn(__uint_as_float(v.x), __uint_as_float(h.x)));
@@ -404,13 +419,19 @@ TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int
   if (T < kTT || (T & 3) || Ci > 256 || N > 65535 * 16 || H > (1 << 20) || W > (1 << 20) || T > (1 << 28)) return p;
   const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
   if (Ho < 1 || Wo < 1) return p;
-  const int cg = (int)((Ci + 7) / 8);
+  // channels per column of a row slot: few channels are packed 2 or 4 to a column, so that the eight
+  // rows an MMA reads span several taps instead of zero-filled channels
+  const int cpc = Ci <= 2 ? 2 : (Ci <= 4 ? 4 : (int)((Ci + 7) / 8) * 8);
+  const int per = cpc < 8 ? 8 / cpc : 1;                                 // columns (taps) per MMA
+  const int nm = cpc < 8 ? (int)((kw + per - 1) / per) : (int)kw * (cpc / 8);
+  const int wcols = cpc < 8 ? (kWG - 1) + nm * per : (int)(kWG + kw - 1);
   const int ngroup = (int)((Co + kAccCols - 1) / kAccCols);
   const int64_t co_last = Co - (int64_t)(ngroup - 1) * kAccCols;
   // every channel group is launched with the same MMA N: the widest group, padded to 16
   const int npad = (int)(((ngroup > 1 ? kAccCols : co_last) + 15) & ~15);
-  const int64_t slot = (int64_t)(kWG + kw - 1) * cg * 1024;
-  const int64_t ktot = kh * kw * cg * 8;
+  const int64_t box_bytes = (int64_t)wcols * cpc * 128;
+  const int64_t slot = (box_bytes + 1023) & ~1023LL;
+  const int64_t ktot = kh * nm * 8;
   const int64_t b_bytes = (((ktot + 31) / 32) * npad * 128 + 1023) & ~1023LL;
   const int64_t fixed = 2 * b_bytes + 8 * (2 * kMaxRing + 2 * kMaxLo + 2 * kMaxAcc) + 128 + 1024 + (kh + 2) * slot;
   // rows in flight beyond the kh live ones: as many as fit in 224 KB, at most 16, at least 2
@@ -419,7 +440,7 @@ TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int
   if (ahead < 2 || ngroup > 65535) return p;
   const int R = (int)(kh + ahead);
   const int64_t smem = fixed + (int64_t)R * slot;
-  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, cg, npad,
+  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, cpc, nm, (int)box_bytes, npad,
                (int)((Wo + kWG - 1) / kWG), (int)((T + kTT - 1) / kTT), (int)slot, R, (int)b_bytes};
   // at least 120 KB so that two CTAs (two TMEM allocations of 512 columns) never share an SM
   p.smem = (size_t)(smem < 120 * 1024 ? 120 * 1024 : smem);
@@ -444,7 +465,7 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
   const uint64_t dims[5] = {(uint64_t)T, (uint64_t)Ci, (uint64_t)W, (uint64_t)H, (uint64_t)N};
   const uint64_t strides[4] = {(uint64_t)(H * W * T * 4), (uint64_t)(T * 4), (uint64_t)(W * T * 4),
                                (uint64_t)(Ci * H * W * T * 4)};
-  const uint32_t box[5] = {(uint32_t)kTT, (uint32_t)(8 * p.g.cg), (uint32_t)(kWG + kw - 1), 1u, 1u};
+  const uint32_t box[5] = {(uint32_t)kTT, (uint32_t)p.g.cpc, (uint32_t)(p.g.box_bytes / (p.g.cpc * 128)), 1u, 1u};
   int rc = make_map_5d(&xmap, x, dims, strides, box, 2);
   if (rc != SB_OK) return rc;
   const int64_t nitems = (int64_t)p.g.N * p.g.nwg * p.g.ntc;
@@ -470,7 +491,8 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
 
 }  // namespace sb
 
-// the contraction must be long enough for the tile hand-offs to pay off
+// the contraction must be long enough for the tile hand-offs to pay off (2 -> 16 channels, 5 x 5, 50
+// taps, at [32, 2, 32, 32, 300]: 0.53 ms on either kernel; 16 -> 32, 3 x 3, 144 taps: 0.15 against 0.79 ms)
 constexpr int64_t kMinTapsForAuto = 64;
 
 extern "C" int sb_conv_fits_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh,
