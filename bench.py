@@ -165,6 +165,7 @@ def make_inputs(name, shape, device, seed):
 WORKLOADS = {
     # headline: fused CUBA forward, x in, spike + voltage out = 12 B per neuron-step
     'cuba_fwd': Workload('cuba_fwd', (64, 8192, 2000), 12),
+    'cuba_fwd_infer': Workload('cuba_fwd_infer', (64, 8192, 2000), 8),   # x in, fp32 spikes out: forward under no_grad
     'cuba_fwd_cfg0': Workload('cuba_fwd_cfg0', (16, 512, 1000), 12),
     # the same through slayer.neuron.cuba.Neuron.forward: the kernel plus the Python / ATen glue of one call
     'cuba_fwd_cfg0_api': Workload('cuba_fwd_cfg0_api', (16, 512, 1000), 12),
@@ -174,8 +175,10 @@ WORKLOADS = {
     # backward of the same: g_spike + voltage in, g_x out
     'cuba_bwd': Workload('cuba_bwd', (64, 8192, 2000), 12),
     'alif_fwd': Workload('alif_fwd', (64, 4096, 2000), 16),
+    'alif_fwd_infer': Workload('alif_fwd_infer', (64, 4096, 2000), 8),   # x in, fp32 spikes out: forward under no_grad
     'alif_bwd': Workload('alif_bwd', (64, 4096, 2000), 16),
     'adrf_fwd': Workload('adrf_fwd', (64, 8192, 1000), 24),
+    'adrf_fwd_infer': Workload('adrf_fwd_infer', (64, 8192, 1000), 12),   # re, im in, fp32 spikes out
     'adrf_bwd': Workload('adrf_bwd', (64, 8192, 1000), 24),
     'li_fwd': Workload('li_fwd', (64, 8192, 2000), 8),
     'li_bwd': Workload('li_bwd', (64, 8192, 2000), 8),
@@ -458,6 +461,13 @@ def build_step(name, shape, device, seed):
             with torch.no_grad():
                 return neuron(d['x'])
         return step, 1, (d, neuron)
+    if name == 'cuba_fwd_infer':
+        cd, vd = one(1024), one(123)
+
+        def step():
+            return _ops.cuba_fwd(d['x'], cd, vd, zeros, zeros, THR, W_SCALE, want_current=False, want_spike=True,
+                                 want_voltage=False)
+        return step, 1, d
     if name.startswith('cuba_fwd'):
         cd, vd = one(1024), one(123)
 
@@ -473,13 +483,13 @@ def build_step(name, shape, device, seed):
         def step():
             return _ops.cuba_bwd(d['g'], d['voltage'], THR, None, cd, vd, 125.0, 0.1, False, False)
         return step, 1, d
-    if name in ('alif_fwd', 'alif_bwd'):
+    if name in ('alif_fwd', 'alif_fwd_infer', 'alif_bwd'):
         cd, vd, td, rd = one(819), one(205), one(410), one(410)
         ths = torch.ones(lead, device=device)
         args = (d['x'], cd, vd, rd, td, zeros, zeros, zeros, ths, 0.5, 1.0, W_SCALE)
-        if name == 'alif_fwd':
+        if name in ('alif_fwd', 'alif_fwd_infer'):
             def step():
-                return _ops.alif_fwd(*args, dynamics_mode=False)
+                return _ops.alif_fwd(*args, dynamics_mode=False, spikes_only=name.endswith('infer'))
             return step, 1, d
         (spk, vol, thsum), _ = _ops.alif_fwd(*args, dynamics_mode=False)
         d.update(voltage=vol, thsum=thsum)
@@ -488,16 +498,17 @@ def build_step(name, shape, device, seed):
         def step():
             return _ops.cuba_bwd(d['g'], d['voltage'], d['thsum'], None, cd, vd, 100.0, 0.1, False, False)
         return step, 1, d
-    if name in ('adrf_fwd', 'adrf_bwd'):
+    if name in ('adrf_fwd', 'adrf_fwd_infer', 'adrf_bwd'):
         gen = torch.Generator(device=device).manual_seed(seed + 1)
         period = 10 + 30 * torch.rand(C, device=device, generator=gen)
         sd = (4096 * torch.sin(2 * np.pi / period) * 0.9).round()
         cdec = (4096 * torch.cos(2 * np.pi / period) * 0.9).round()
         ad = dict(ref_decay=one(410), th_decay=one(410), ref_state=zeros, th_state=0.5 * torch.ones(lead, device=device),
                   th_step=0.25, th0=0.5)
-        if name == 'adrf_fwd':
+        if name in ('adrf_fwd', 'adrf_fwd_infer'):
             def step():
-                return _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad)
+                return _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad,
+                                   spikes_only=name.endswith('infer'))
             return step, 1, d
         outs, _ = _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad)
         d.update(real=outs[1], imag=outs[2], thsum=outs[3])
@@ -916,7 +927,7 @@ def time_steps(step, steps, warmup, device, dist, sampler=None):
 
 
 # legs reported beside the headline in the default run: every benchmark configuration's kernels
-EXTRA_LEGS = ('cuba_bwd', 'alif_fwd', 'alif_bwd', 'adrf_fwd', 'adrf_bwd', 'shift', 'fir_conv', 'delay_fir_fwd',
+EXTRA_LEGS = ('cuba_fwd_infer', 'cuba_bwd', 'alif_fwd', 'alif_fwd_infer', 'alif_bwd', 'adrf_fwd', 'adrf_fwd_infer', 'adrf_bwd', 'shift', 'fir_conv', 'delay_fir_fwd',
               'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cuba_fwd_cfg0_graph', 'cfg4_fwd', 'cfg4_train')
 
 

@@ -158,7 +158,9 @@ int sb_cspike_bwd(const float* re, const float* im, const float* thr_tensor, flo
  * CUBA (neuron/cuba.py:274-421): thr = fp32(threshold + eps).
  * Outputs: current (nullable), voltage, spike (nullable);
  * final_c/final_v/final_s (nullable float[rows]) = last time bin of
- * current, voltage (before reset) and spike.
+ * current, voltage (before reset) and spike.  voltage may be null when only
+ * binary spikes are wanted (current null, graded 0): what Neuron.forward
+ * returns when nothing will be differentiated, 8 B per neuron-step instead of 12.
  * spike_delay = 1 (binary spikes only) writes the spike series one step late,
  * spike_out[t] = spike[t-1], which is the one-step inter-layer delay of the
  * blocks (block/base.py:15-39) at no extra memory traffic; delay_head
@@ -202,7 +204,9 @@ int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_
  * thsum = threshold + refractory.  mode 1: dynamics() -> current, voltage,
  * threshold, refractory (out0..out3).  spike_delay = 1 (mode 0, binary spikes):
  * the spike series is written one step late, delay_head (nullable float[rows])
- * supplying its first step, as in sb_cuba_fwd; sb_cuba_bwd undoes it. */
+ * supplying its first step, as in sb_cuba_fwd; sb_cuba_bwd undoes it.
+ * Mode 0 with out1 and out2 null (binary spikes): only the spikes are written,
+ * what Neuron.forward returns when nothing will be differentiated. */
 int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* ref_decay, int64_t n_ref_decay, const float* th_decay, int64_t n_th_decay,
                 const float* cstate, const float* vstate, const float* ref_state, const float* th_state,
@@ -215,7 +219,8 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
  * spike, re, im (out0..out2) with scalar threshold.  adapt = 1, mode 0:
  * spike, re, im, th + ref.  adapt = 1, mode 1: re, im, threshold, refractory.
  * spike_delay / delay_head (mode 0, binary spikes) as in sb_cuba_fwd; sb_rf_bwd
- * takes the same spike_delay to read the gradient of the late series. */
+ * takes the same spike_delay to read the gradient of the late series.
+ * Mode 0 with out1, out2 (and out3) null (binary spikes): only the spikes are written. */
 int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
               int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
               int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,

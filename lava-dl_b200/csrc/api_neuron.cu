@@ -66,7 +66,8 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
   SB_REQUIRE(counts_ok({n_cdecay, n_vdecay}, nmax), "decay counts disagree");
   SB_REQUIRE(w_scale > 0 && is_pow2(w_scale), "fused kernels need a power-of-two w_scale (got %d)", w_scale);
   SB_REQUIRE(cdecay && vdecay && cstate && vstate, "null parameter pointer");
-  SB_REQUIRE(voltage != nullptr, "voltage output is required");
+  SB_REQUIRE(voltage != nullptr || (spike != nullptr && !graded && current == nullptr),
+             "without the voltage series only binary spikes can be returned");
   const Scale sc = make_scale(w_scale);
   // reset: int64 voltage >= Python float (thr * w_scale), evaluated in fp32 (leaky_integrator.py:218-225)
   const float thr_scaled = (float)(threshold * (double)w_scale);
@@ -85,6 +86,13 @@ int sb_cuba_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
     out[no++] = voltage;                                                                            \
     if (S) out[no++] = spike;                                                                       \
     return launch_rowscan<CubaFwd<C, S, G>>(p, rg, in, out, st, bd);                                \
+  }
+  if (voltage == nullptr) {
+    // inference: spikes only (x in, fp32 spikes out, 8 bytes per neuron-step instead of 12)
+    typename CubaFwd<false, true, false, false>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate,
+                                                           final_c, final_v, final_s, k_reset, k_spike, spike_scale, sc};
+    float* out[1] = {spike};
+    return launch_rowscan<CubaFwd<false, true, false, false>>(p, rg, in, out, st, bd);
   }
   if (current) {
     if (spike) { if (graded) SB_GO(true, true, true) else SB_GO(true, true, false) }
@@ -222,6 +230,14 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
                                      final_c, final_v, final_th, final_ref, final_s, spike_scale, sc}; \
     return launch_rowscan<AlifFwd<D, G>>(p, rg, in, out, st, bd);                                    \
   }
+  if (mode == 0 && out1 == nullptr && out2 == nullptr) {
+    // inference: spikes only (voltage and threshold series are what the backward pass reads)
+    SB_REQUIRE(!graded && out0 != nullptr, "without the voltage and threshold series only binary spikes can be returned");
+    typename AlifFwd<false, false, true>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,
+                                                    final_c, final_v, final_th, final_ref, final_s, spike_scale, sc};
+    float* lean[1] = {out0};
+    return launch_rowscan<AlifFwd<false, false, true>>(p, rg, in, lean, st, bd);
+  }
   if (mode == 1) SB_GO(true, false)
   else if (graded) SB_GO(false, true)
   else SB_GO(false, false)
@@ -268,6 +284,19 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
     typename RfFwd<A, D, G>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,      \
                                       final_s, spike_scale, sc};                                     \
     return launch_rowscan<RfFwd<A, D, G>>(p, rg, in, out, st, bd);                                   \
+  }
+  if (mode == 0 && out1 == nullptr && out2 == nullptr && out3 == nullptr) {
+    // inference: spikes only
+    SB_REQUIRE(!graded && out0 != nullptr, "without the state series only binary spikes can be returned");
+    float* lean[1] = {out0};
+    if (adapt) {
+      typename RfFwd<true, false, false, true>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,
+                                                          final_s, spike_scale, sc};
+      return launch_rowscan<RfFwd<true, false, false, true>>(p, rg, in, lean, st, bd);
+    }
+    typename RfFwd<false, false, false, true>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,
+                                                         final_s, spike_scale, sc};
+    return launch_rowscan<RfFwd<false, false, false, true>>(p, rg, in, lean, st, bd);
   }
   if (adapt) {
     if (mode == 1) SB_GO(true, true, false)

@@ -496,9 +496,10 @@ struct CubaFwd {
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = (OUT_SPK && !GRADED) ? 1 : 0;  // binary spikes leave as bits
   static constexpr bool HAS_FAST = true;
-  // boxes per stage by the number of tiles a stage holds: 3 for one (inference), 2 for two (training:
-  // current + voltage; 3.44 -> 3.12 ms at [64,8192,2000]), else 1
-  SB_PIPE(3, ((NOUT - NBIT) <= 1 ? 3 : ((NOUT - NBIT) == 2 ? 2 : 1)), 32);
+  // boxes per stage by the number of tiles a stage holds: 3 for one (spikes + voltage), 2 for two (training:
+  // current + voltage; 3.44 -> 3.12 ms at [64,8192,2000]), else 1; with no output tile at all (spikes only:
+  // the stage holds the input) 2 boxes, 0.85 -> 0.89 of copy bandwidth against 3
+  SB_PIPE(3, ((NOUT - NBIT) == 0 ? 2 : ((NOUT - NBIT) <= 1 ? 3 : ((NOUT - NBIT) == 2 ? 2 : 1))), 32);
   static constexpr int IV = OUT_CUR ? 1 : 0, IS = IV + (OUT_VOL ? 1 : 0);
   struct Params {
     DecayVec cdecay, vdecay;
@@ -633,17 +634,22 @@ struct CubaBwd {
 //   spike = voltage >= th + ref   (fp32 comparison of the returned series)
 // DYN: outputs current, voltage, threshold, refractory (what dynamics() returns)
 // else: outputs voltage, threshold + refractory, spike (what forward() needs)
+// LEAN: binary spikes only (forward() when nothing will be differentiated: the
+//       voltage and threshold series are what the backward pass reads)
 // ===========================================================================
-template <bool DYN, bool GRADED>
+template <bool DYN, bool GRADED, bool LEAN = false>
 struct AlifFwd {
-  static constexpr int NIN = 1, NOUT = DYN ? 4 : 3;
+  static_assert(!LEAN || (!DYN && !GRADED), "spikes only: forward mode, binary spikes");
+  static constexpr int NIN = 1, NOUT = LEAN ? 1 : (DYN ? 4 : 3);
   static constexpr bool REVERSE = false;
   // binary spikes leave as bits (which is what lets the block's one-step delay ride on the store);
   // with two boxes per stage that runs as fast as spikes on a TMA tile with four stages of one box
   // (0.777 against 0.779 of copy bandwidth; one box per stage: 0.72)
   static constexpr int NBIT = (!DYN && !GRADED) ? 1 : 0;
   static constexpr bool HAS_FAST = true;
-  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((!DYN && NBIT) ? 2 : 1), (DYN ? 16 : 32));
+  // LEAN: the stage holds the input only and the step chain, not memory, sets the pace: one box per stage, so that
+  // 18 warps fit an SM (0.57 -> 0.68 of copy bandwidth at 8 bytes per step against two boxes)
+  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((!DYN && NBIT && !LEAN) ? 2 : 1), (DYN ? 16 : 32));
   struct Params {
     DecayVec cdecay, vdecay;
     const float* cstate;
@@ -687,7 +693,11 @@ struct AlifFwd {
       const float thsum = __fadd_rn(thf, reff);
       const bool sp = vf >= thsum;
       last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, vf), spike_scale) : (sp ? 1.f : 0.f);
-      b[0] = vf; b[1] = thsum; b[2] = last_s;
+      if constexpr (LEAN) {
+        b[0] = last_s;
+      } else {
+        b[0] = vf; b[1] = thsum; b[NOUT - 1] = last_s;
+      }
     }
     s.commit(v >= s.th_new + s.ref_new);
   }
@@ -711,16 +721,19 @@ struct AlifFwd {
 //   spike = (re >= thr) * (im[t-1] < 0) * (im >= 0),  im[-1] = imag state
 // DYN (ADAPT only): outputs re, im, threshold, refractory
 // else            : outputs re, im, [threshold + refractory], spike
+// LEAN            : binary spikes only (forward() when nothing will be differentiated)
 // ===========================================================================
-template <bool ADAPT, bool DYN, bool GRADED>
+template <bool ADAPT, bool DYN, bool GRADED, bool LEAN = false>
 struct RfFwd {
   static_assert(ADAPT || !DYN, "DYN needs ADAPT");
-  static constexpr int NIN = 2, NOUT = ADAPT ? 4 : 3;
+  static_assert(!LEAN || (!DYN && !GRADED), "spikes only: forward mode, binary spikes");
+  static constexpr int NIN = 2, NOUT = LEAN ? 1 : (ADAPT ? 4 : 3);
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = (!DYN && !GRADED) ? 1 : 0;
   static constexpr bool HAS_FAST = true;
   // three tiles per stage (adaptive forward): four stages measured best (adrf_fwd 0.78 -> 0.81 of copy bandwidth)
-  SB_PIPE(((NOUT - NBIT) == 3 ? 4 : 3), 1, ((NOUT - NBIT) >= 4 ? 16 : 32));
+  // LEAN (two input tiles per stage, no output tile): two stages of one box, 14 warps per SM (0.46 -> 0.62)
+  SB_PIPE((LEAN ? 2 : ((NOUT - NBIT) == 3 ? 4 : 3)), 1, ((NOUT - NBIT) >= 4 ? 16 : 32));
   struct Params {
     ResParams res;
     AthParams ath;    // ADAPT only
@@ -764,14 +777,22 @@ struct RfFwd {
         const float thsum = __fadd_rn(thf, rff);
         const bool sp = (ref_ >= thsum) && im_prev_neg && (r.im >= 0);
         last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
-        b[0] = ref_; b[1] = imf; b[2] = thsum; b[3] = last_s;
+        if constexpr (LEAN) {
+          b[0] = last_s;
+        } else {
+          b[0] = ref_; b[1] = imf; b[NOUT - 2] = thsum; b[NOUT - 1] = last_s;
+        }
       }
       s.commit(r.re >= s.th_new + s.ref_new && r.im >= 0 && im_old_i < 0);
       im_old_i = r.im;
     } else {
       const bool sp = (r.re >= k_spike) && im_prev_neg && (r.im >= 0);
       last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
-      b[0] = ref_; b[1] = imf; b[2] = last_s;
+      if constexpr (LEAN) {
+        b[0] = last_s;
+      } else {
+        b[0] = ref_; b[1] = imf; b[NOUT - 1] = last_s;
+      }
     }
     im_prev_neg = r.im < 0;
   }

@@ -425,16 +425,17 @@ def _vec(shape_like):
 
 
 def cuba_fwd(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_current, want_spike, graded=False,
-             spike_scale=1.0, spike_delay=0, delay_head=None, axon_delay=None, axon_delay_ts=1.0):
+             spike_scale=1.0, spike_delay=0, delay_head=None, axon_delay=None, axon_delay_ts=1.0, want_voltage=True):
     """Returns dict with current/voltage/spike series and final_c/final_v/final_s.
     ``spike_delay=1`` returns the spike series one step late (``delay_head`` fills t = 0);
-    ``axon_delay`` (one value per neuron, 0..62 steps) delays each row further."""
+    ``axon_delay`` (one value per neuron, 0..62 steps) delays each row further.
+    ``want_voltage=False`` (binary spikes only, no current) leaves the voltage series unwritten."""
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
     cs, vs = row_state(cstate, x), row_state(vstate, x)
     cur = torch.empty_like(x) if want_current else None
-    vol = torch.empty_like(x)
+    vol = torch.empty_like(x) if want_voltage else None
     spk = torch.empty_like(x) if want_spike else None
     fc, fv = _vec(x), _vec(x)
     fs = _vec(x) if want_spike else None
@@ -540,7 +541,9 @@ def cuba_recurrent_bwd(grad_spike, voltage, rec, threshold, tau_rho, scale_rho, 
 
 
 def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0, w_scale,
-             dynamics_mode, graded=False, spike_scale=1.0, spike_delay=0, delay_head=None):
+             dynamics_mode, graded=False, spike_scale=1.0, spike_delay=0, delay_head=None, spikes_only=False):
+    """``spikes_only`` (forward mode, binary spikes): the voltage and threshold series, which only
+    the backward pass reads, are not written; ``outs`` is then ``[spike, None, None]``."""
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
@@ -548,6 +551,10 @@ def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, 
     cs, vs = row_state(cstate, x), row_state(vstate, x)
     rs, ts = row_state(ref_state, x), row_state(th_state, x)
     outs = [torch.empty_like(x) for _ in range(4 if dynamics_mode else 3)]
+    if spikes_only:
+        if dynamics_mode or graded:
+            raise ValueError('spikes_only needs forward mode and binary spikes')
+        outs = [outs[0], None, None]
     fin = [_vec(x) for _ in range(5)]
     g = geom(x, cd.numel(), vd.numel(), rd.numel(), td.numel())
     head = None if delay_head is None else row_state(delay_head, x)
@@ -561,8 +568,10 @@ def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, 
 
 
 def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_scale, graded=False,
-           spike_scale=1.0, adaptive=None, dynamics_mode=False, spike_delay=0, delay_head=None):
-    """``adaptive`` = None for RF, else dict(ref_decay, th_decay, ref_state, th_state, th_step, th0)."""
+           spike_scale=1.0, adaptive=None, dynamics_mode=False, spike_delay=0, delay_head=None, spikes_only=False):
+    """``adaptive`` = None for RF, else dict(ref_decay, th_decay, ref_state, th_state, th_step, th0).
+    ``spikes_only`` (forward mode, binary spikes): the state series, which only the backward pass
+    reads, are not written; ``outs`` is then ``[spike, None, ...]``."""
     N.require_cuda(re_in, im_in)
     re_in, im_in = _c(re_in), _c(im_in)
     sd, cd = _param(sin_decay, re_in), _param(cos_decay, re_in)
@@ -579,6 +588,10 @@ def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_
         counts = (sd.numel(),)
     nout = 4 if adapt else 3
     outs = [torch.empty_like(re_in) for _ in range(nout)]
+    if spikes_only:
+        if dynamics_mode or graded:
+            raise ValueError('spikes_only needs forward mode and binary spikes')
+        outs = [outs[0]] + [None] * (nout - 1)
     fin = [_vec(re_in) for _ in range(5)]
     g = geom(re_in, *counts)
     head = None if delay_head is None else row_state(delay_head, re_in)

@@ -52,11 +52,15 @@ class _FusedForward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step,
                 th0, w_scale, tau_rho, scale_rho, graded, spike_delay=0, delay_head=None):
+        # the voltage and threshold series are what the backward pass reads: with nothing to
+        # differentiate (inference) they are not written, three quarters of the kernel's stores
+        lean = not graded and not any(ctx.needs_input_grad)
         (spike, voltage, thsum), fin = _ops.alif_fwd(
             input, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0,
             w_scale, dynamics_mode=False, graded=graded, spike_scale=1.0, spike_delay=spike_delay,
-            delay_head=delay_head)
-        ctx.save_for_backward(voltage, thsum, cdecay, vdecay)
+            delay_head=delay_head, spikes_only=lean)
+        if not lean:
+            ctx.save_for_backward(voltage, thsum, cdecay, vdecay)
         ctx.consts = (tau_rho, scale_rho, graded, spike_delay)
         extras = (fin['final_c'], fin['final_v'], fin['final_th'], fin['final_ref'], fin['final_s'])
         ctx.mark_non_differentiable(*extras)

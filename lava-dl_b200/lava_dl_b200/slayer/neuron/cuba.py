@@ -67,10 +67,17 @@ class _FusedForward(torch.autograd.Function):
                 spike_delay=0, delay_head=None, axon_delay=None, axon_ts=1, axon_grad_scale=1):
         need_dgrad = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
         ctx.set_materialize_grads(False)   # no zero tensors for the outputs nobody differentiates
+        # the voltage series is what the backward pass reads: with nothing to differentiate (inference)
+        # it is not written at all, a third of the kernel's traffic
+        need_voltage = graded or any(ctx.needs_input_grad)
         r = _ops.cuba_fwd(input, cdecay, vdecay, cstate, vstate, threshold, w_scale,
                           want_current=need_dgrad, want_spike=True, graded=graded, spike_scale=1.0,
                           spike_delay=spike_delay, delay_head=delay_head,
-                          axon_delay=None if axon_delay is None else axon_delay.data, axon_delay_ts=axon_ts)
+                          axon_delay=None if axon_delay is None else axon_delay.data, axon_delay_ts=axon_ts,
+                          want_voltage=need_voltage)
+        if not need_voltage:
+            ctx.mark_non_differentiable(r['final_c'], r['final_v'], r['final_s'])
+            return r['spike'], None, r['final_c'], r['final_v'], r['final_s']
         saved = [r['voltage'], cdecay, vdecay]
         if need_dgrad:
             saved.append(r['current'])

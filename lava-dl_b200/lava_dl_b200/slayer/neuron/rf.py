@@ -39,11 +39,16 @@ class _FusedForward(torch.autograd.Function):
         if ref_decay is not None:
             ad = dict(ref_decay=ref_decay, th_decay=th_decay, ref_state=ref_state, th_state=th_state,
                       th_step=th_step, th0=th0)
+        # the state series are what the backward pass reads: with nothing to differentiate
+        # (inference) only the spikes are written
+        lean = not graded and not any(ctx.needs_input_grad)
         outs, fin = _ops.rf_fwd(real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold,
                                 w_scale, graded=graded, spike_scale=1.0, adaptive=ad, spike_delay=spike_delay,
-                                delay_head=delay_head)
+                                delay_head=delay_head, spikes_only=lean)
         spike, real, imag = outs[:3]
-        if ad is None:
+        if lean:
+            ctx.threshold = threshold
+        elif ad is None:
             ctx.save_for_backward(real, imag, sin_decay, cos_decay)
             ctx.threshold = threshold
         else:

@@ -460,6 +460,40 @@ def test_cuba_packed_spikes(shape, misalign, want_voltage, cuda, ops):
 
 @pytest.mark.parametrize('shape', SHAPES)
 @pytest.mark.parametrize('misalign', [False, True])
+def test_cuba_forward_without_the_voltage_series(shape, misalign, cuda, ops):
+    """What ``Neuron.forward`` runs when nothing will be differentiated: fp32 spikes and the final
+    states, the voltage series left unwritten -- with and without the one-step delay and an axonal
+    delay table.  The spikes are those of the oracle; a neuron in ``no_grad`` takes this path."""
+    rng = rng_for('novolt', shape)
+    B, C, T = shape
+    x = rng.normal(0.3, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, C, 800, 1300), decays(rng, C, 50, 300)
+    cs, vs = quant(rng.normal(0, 0.5, size=shape[:-1])), quant(rng.normal(0, 0.5, size=shape[:-1]))
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    axon = rng.integers(0, min(62, T), size=C).astype(np.float32)
+    want = O.cuba(x, 1.25, cd, vd, cstate=cs, vstate=vs)
+    args = (dev(x, cuda, misalign), dev(cd, cuda), dev(vd, cuda), dev(cs, cuda), dev(vs, cuda), 1.25 + 0.01 / W, W)
+    for delay, use_axon in ((0, False), (1, False), (1, True)):
+        kw = dict(want_current=False, want_spike=True, spike_delay=delay, delay_head=dev(head, cuda) if delay else None,
+                  axon_delay=dev(axon, cuda) if use_axon else None)
+        full = ops.cuba_fwd(*args, **kw)
+        lean = ops.cuba_fwd(*args, want_voltage=False, **kw)
+        assert lean['voltage'] is None
+        assert_exact(lean['spike'], full['spike'].cpu().numpy(), f'spikes without the voltage series (delay {delay}, axon {use_axon})')
+        if not use_axon:
+            spike = want['spike']
+            if delay:
+                spike = np.concatenate([head[..., None], spike[..., :-1]], axis=-1)
+            assert_exact(lean['spike'], spike, f'spikes against the oracle (delay {delay})')
+        assert_exact(lean['final_c'], want['current'][..., -1], 'final current')
+        assert_exact(lean['final_v'], want['voltage'][..., -1], 'final voltage')
+        assert_exact(lean['final_s'], want['spike'][..., -1], 'final spike')
+    with pytest.raises(RuntimeError):
+        ops.cuba_fwd(*args, want_current=True, want_spike=True, want_voltage=False)
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('misalign', [False, True])
 def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
     """Spikes written one step late inside the kernel == shift(spike, 1) with the head
     value at t = 0, and the backward reads the gradient of the late series."""
@@ -491,6 +525,60 @@ def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
     assert_close(gcd, ref['grad_current_decay'], 'grad current decay',
                  scale=pgrad_scale(1, (ref['grad_x'], want['current'])))
     assert_close(gvd, ref['grad_voltage_decay'], 'grad voltage decay', scale=pgrad_scale(1, (g_c, want['voltage'])))
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+def test_alif_and_resonator_spikes_only(shape, cuda, ops):
+    """The forward kernels of the ALIF, RF and ADRF neurons without the series that only the
+    backward pass reads (what ``forward`` runs when nothing will be differentiated): the same
+    spikes and final states as the full kernels and as the oracle, with and without the one-step delay."""
+    rng = rng_for('lean', shape)
+    B, C, T = shape
+    head = (rng.uniform(size=shape[:-1]) < 0.5).astype(np.float32)
+    zeros = dev(np.zeros(shape[:-1]), cuda)
+    x = rng.normal(0.2, 1.0, size=shape).astype(np.float32)
+    cd, vd = decays(rng, C, 700, 900), decays(rng, C, 150, 250)
+    td, rd = decays(rng, C, 300, 500), decays(rng, C, 300, 500)
+    ths = quant(rng.uniform(0.8, 1.5, size=shape[:-1]))
+    want = O.alif(x, 1.0, 0.5, cd, vd, td, rd, th_state=ths)
+    args = (dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(rd, cuda), dev(td, cuda), zeros, zeros, zeros,
+            dev(ths, cuda), 0.5, 1.0, W)
+    for delay in (0, 1):
+        kw = dict(dynamics_mode=False, spike_delay=delay, delay_head=dev(head, cuda) if delay else None)
+        full, fin_full = ops.alif_fwd(*args, **kw)
+        lean, fin = ops.alif_fwd(*args, spikes_only=True, **kw)
+        assert lean[1] is None and lean[2] is None
+        assert_exact(lean[0], full[0].cpu().numpy(), f'ALIF spikes only (delay {delay})')
+        if not delay:
+            assert_exact(lean[0], want['spike'], 'ALIF spikes only against the oracle')
+        for k in fin:
+            assert_exact(fin[k], fin_full[k].cpu().numpy(), f'ALIF {k}')
+    with pytest.raises(ValueError):
+        ops.alif_fwd(*args, dynamics_mode=True, spikes_only=True)
+
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    sd, cdk = sincos(rng, C)
+    for adaptive in (False, True):
+        if adaptive:
+            want = O.adrf(re_in, im_in, 0.5, 0.25, sd, cdk, td, rd, th_state=ths)
+            ad = dict(ref_decay=dev(rd, cuda), th_decay=dev(td, cuda), ref_state=zeros, th_state=dev(ths, cuda),
+                      th_step=0.25, th0=0.5)
+        else:
+            want = O.rf(re_in, im_in, 0.5, sd, cdk)
+            ad = None
+        for delay in (0, 1):
+            kw = dict(adaptive=ad, spike_delay=delay, delay_head=dev(head, cuda) if delay else None)
+            a = (dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cdk, cuda), zeros, zeros, 0.5, W)
+            full, fin_full = ops.rf_fwd(*a, **kw)
+            lean, fin = ops.rf_fwd(*a, spikes_only=True, **kw)
+            assert all(o is None for o in lean[1:])
+            assert_exact(lean[0], full[0].cpu().numpy(), f'resonator spikes only (adaptive={adaptive}, delay {delay})')
+            if not delay:
+                assert_exact(lean[0], want['spike'], f'resonator spikes only against the oracle (adaptive={adaptive})')
+            for k in fin:
+                if adaptive or k not in ('final_th', 'final_ref'):   # the plain resonator has no threshold state
+                    assert_exact(fin[k], fin_full[k].cpu().numpy(), f'resonator {k}')
 
 
 @pytest.mark.parametrize('shape', SHAPES)
