@@ -174,9 +174,9 @@ WORKLOADS = {
     'cuba_fwd_delayed': Workload('cuba_fwd_delayed', (64, 8192, 2000), 12),
     # backward of the same: g_spike + voltage in, g_x out
     'cuba_bwd': Workload('cuba_bwd', (64, 8192, 2000), 12),
-    'alif_fwd': Workload('alif_fwd', (64, 4096, 2000), 16),
+    'alif_fwd': Workload('alif_fwd', (64, 4096, 2000), 12),   # x in; spike and voltage - threshold out (training forward)
     'alif_fwd_infer': Workload('alif_fwd_infer', (64, 4096, 2000), 8),   # x in, fp32 spikes out: forward under no_grad
-    'alif_bwd': Workload('alif_bwd', (64, 4096, 2000), 16),
+    'alif_bwd': Workload('alif_bwd', (64, 4096, 2000), 12),   # grad_spike and voltage - threshold in; grad_x out
     'adrf_fwd': Workload('adrf_fwd', (64, 8192, 1000), 24),
     'adrf_fwd_infer': Workload('adrf_fwd_infer', (64, 8192, 1000), 12),   # re, im in, fp32 spikes out
     'adrf_bwd': Workload('adrf_bwd', (64, 8192, 1000), 24),
@@ -489,14 +489,15 @@ def build_step(name, shape, device, seed):
         args = (d['x'], cd, vd, rd, td, zeros, zeros, zeros, ths, 0.5, 1.0, W_SCALE)
         if name in ('alif_fwd', 'alif_fwd_infer'):
             def step():
-                return _ops.alif_fwd(*args, dynamics_mode=False, spikes_only=name.endswith('infer'))
+                return _ops.alif_fwd(*args, dynamics_mode=False, spikes_only=name.endswith('infer'),
+                                     margin=not name.endswith('infer'))
             return step, 1, d
-        (spk, vol, thsum), _ = _ops.alif_fwd(*args, dynamics_mode=False)
-        d.update(voltage=vol, thsum=thsum)
+        (spk, margin, _), _ = _ops.alif_fwd(*args, dynamics_mode=False, margin=True)
+        d.update(margin=margin)
         del d['x'], spk
 
         def step():
-            return _ops.cuba_bwd(d['g'], d['voltage'], d['thsum'], None, cd, vd, 100.0, 0.1, False, False)
+            return _ops.cuba_bwd(d['g'], d['margin'], 0.0, None, cd, vd, 100.0, 0.1, False, False)
         return step, 1, d
     if name in ('adrf_fwd', 'adrf_fwd_infer', 'adrf_bwd'):
         gen = torch.Generator(device=device).manual_seed(seed + 1)

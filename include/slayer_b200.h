@@ -206,7 +206,10 @@ int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_
  * the spike series is written one step late, delay_head (nullable float[rows])
  * supplying its first step, as in sb_cuba_fwd; sb_cuba_bwd undoes it.
  * Mode 0 with out1 and out2 null (binary spikes): only the spikes are written,
- * what Neuron.forward returns when nothing will be differentiated. */
+ * what Neuron.forward returns when nothing will be differentiated.  Mode 0 with
+ * out2 null: out1 receives voltage - (threshold + refractory) instead of the
+ * voltage; sb_cuba_bwd on it with the scalar threshold 0 gives the same input
+ * gradient as on the two series (the surrogate reads only their difference). */
 int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const float* vdecay, int64_t n_vdecay,
                 const float* ref_decay, int64_t n_ref_decay, const float* th_decay, int64_t n_th_decay,
                 const float* cstate, const float* vstate, const float* ref_state, const float* th_state,

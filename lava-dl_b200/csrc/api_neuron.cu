@@ -238,6 +238,18 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
     float* lean[1] = {out0};
     return launch_rowscan<AlifFwd<false, false, true>>(p, rg, in, lean, st, bd);
   }
+  if (mode == 0 && out1 != nullptr && out2 == nullptr) {
+    // training without learnable decays: out1 = voltage - (threshold + refractory), all the backward pass reads
+    float* two[2] = {out1, out0};
+    if (graded) {
+      typename AlifFwd<false, true, false, true>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,
+                                                           final_c, final_v, final_th, final_ref, final_s, spike_scale, sc};
+      return launch_rowscan<AlifFwd<false, true, false, true>>(p, rg, in, two, st, bd);
+    }
+    typename AlifFwd<false, false, false, true>::Params p{{cdecay, n_cdecay}, {vdecay, n_vdecay}, cstate, vstate, ap,
+                                                          final_c, final_v, final_th, final_ref, final_s, spike_scale, sc};
+    return launch_rowscan<AlifFwd<false, false, false, true>>(p, rg, in, two, st, bd);
+  }
   if (mode == 1) SB_GO(true, false)
   else if (graded) SB_GO(false, true)
   else SB_GO(false, false)

@@ -636,11 +636,15 @@ struct CubaBwd {
 // else: outputs voltage, threshold + refractory, spike (what forward() needs)
 // LEAN: binary spikes only (forward() when nothing will be differentiated: the
 //       voltage and threshold series are what the backward pass reads)
+// MARGIN: outputs voltage - (threshold + refractory), spike.  The surrogate gradient of the spike reads
+//       nothing but that difference (spike/spike.py:10-23), and without learnable decays the reverse
+//       scans read nothing else of the forward pass: one series instead of two, in both directions.
 // ===========================================================================
-template <bool DYN, bool GRADED, bool LEAN = false>
+template <bool DYN, bool GRADED, bool LEAN = false, bool MARGIN = false>
 struct AlifFwd {
   static_assert(!LEAN || (!DYN && !GRADED), "spikes only: forward mode, binary spikes");
-  static constexpr int NIN = 1, NOUT = LEAN ? 1 : (DYN ? 4 : 3);
+  static_assert(!MARGIN || (!DYN && !LEAN), "the margin form is a forward mode");
+  static constexpr int NIN = 1, NOUT = LEAN ? 1 : (MARGIN ? 2 : (DYN ? 4 : 3));
   static constexpr bool REVERSE = false;
   // binary spikes leave as bits (which is what lets the block's one-step delay ride on the store);
   // with two boxes per stage that runs as fast as spikes on a TMA tile with four stages of one box
@@ -649,7 +653,7 @@ struct AlifFwd {
   static constexpr bool HAS_FAST = true;
   // LEAN: the stage holds the input only and the step chain, not memory, sets the pace: one box per stage, so that
   // 18 warps fit an SM (0.57 -> 0.68 of copy bandwidth at 8 bytes per step against two boxes)
-  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((!DYN && NBIT && !LEAN) ? 2 : 1), (DYN ? 16 : 32));
+  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((MARGIN && NBIT) ? 3 : ((!DYN && NBIT && !LEAN) ? 2 : 1)), (DYN ? 16 : 32));
   struct Params {
     DecayVec cdecay, vdecay;
     const float* cstate;
@@ -695,6 +699,8 @@ struct AlifFwd {
       last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, vf), spike_scale) : (sp ? 1.f : 0.f);
       if constexpr (LEAN) {
         b[0] = last_s;
+      } else if constexpr (MARGIN) {
+        b[0] = __fsub_rn(vf, thsum); b[1] = last_s;
       } else {
         b[0] = vf; b[1] = thsum; b[NOUT - 1] = last_s;
       }

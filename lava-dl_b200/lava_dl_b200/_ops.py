@@ -541,9 +541,12 @@ def cuba_recurrent_bwd(grad_spike, voltage, rec, threshold, tau_rho, scale_rho, 
 
 
 def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0, w_scale,
-             dynamics_mode, graded=False, spike_scale=1.0, spike_delay=0, delay_head=None, spikes_only=False):
+             dynamics_mode, graded=False, spike_scale=1.0, spike_delay=0, delay_head=None, spikes_only=False,
+             margin=False):
     """``spikes_only`` (forward mode, binary spikes): the voltage and threshold series, which only
-    the backward pass reads, are not written; ``outs`` is then ``[spike, None, None]``."""
+    the backward pass reads, are not written; ``outs`` is then ``[spike, None, None]``.
+    ``margin`` (forward mode): ``outs`` is ``[spike, voltage - (threshold + refractory), None]`` -- the
+    one series the backward pass needs when the decays are not learnt (``cuba_bwd`` on it with threshold 0)."""
     N.require_cuda(x)
     x = _c(x)
     cd, vd = _param(cdecay, x), _param(vdecay, x)
@@ -555,6 +558,10 @@ def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, 
         if dynamics_mode or graded:
             raise ValueError('spikes_only needs forward mode and binary spikes')
         outs = [outs[0], None, None]
+    elif margin:
+        if dynamics_mode:
+            raise ValueError('margin needs forward mode')
+        outs = [outs[0], outs[1], None]
     fin = [_vec(x) for _ in range(5)]
     g = geom(x, cd.numel(), vd.numel(), rd.numel(), td.numel())
     head = None if delay_head is None else row_state(delay_head, x)

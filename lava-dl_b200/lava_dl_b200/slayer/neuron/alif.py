@@ -55,12 +55,14 @@ class _FusedForward(torch.autograd.Function):
         # the voltage and threshold series are what the backward pass reads: with nothing to
         # differentiate (inference) they are not written, three quarters of the kernel's stores
         lean = not graded and not any(ctx.needs_input_grad)
-        (spike, voltage, thsum), fin = _ops.alif_fwd(
+        # otherwise one series: the spike's surrogate gradient reads voltage - (threshold + refractory)
+        # and, the decays not being learnt on this path, the reverse scans read nothing else
+        (spike, margin, _), fin = _ops.alif_fwd(
             input, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, th_state, th_step, th0,
             w_scale, dynamics_mode=False, graded=graded, spike_scale=1.0, spike_delay=spike_delay,
-            delay_head=delay_head, spikes_only=lean)
+            delay_head=delay_head, spikes_only=lean, margin=not lean)
         if not lean:
-            ctx.save_for_backward(voltage, thsum, cdecay, vdecay)
+            ctx.save_for_backward(margin, cdecay, vdecay)
         ctx.consts = (tau_rho, scale_rho, graded, spike_delay)
         extras = (fin['final_c'], fin['final_v'], fin['final_th'], fin['final_ref'], fin['final_s'])
         ctx.mark_non_differentiable(*extras)
@@ -68,9 +70,9 @@ class _FusedForward(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_spike, *_):
-        voltage, thsum, cdecay, vdecay = ctx.saved_tensors
+        margin, cdecay, vdecay = ctx.saved_tensors
         tau_rho, scale_rho, graded, spike_delay = ctx.consts
-        g_in, _, _ = _ops.cuba_bwd(grad_spike, voltage, thsum, None, cdecay, vdecay, tau_rho, scale_rho, graded,
+        g_in, _, _ = _ops.cuba_bwd(grad_spike, margin, 0.0, None, cdecay, vdecay, tau_rho, scale_rho, graded,
                                    False, spike_delay=spike_delay)
         return (g_in,) + (None,) * 16
 

@@ -528,6 +528,37 @@ def test_cuba_fused_step_delay(shape, misalign, cuda, ops):
 
 
 @pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('graded', [False, True])
+def test_alif_margin_form(shape, graded, cuda, ops):
+    """The training forward of the ALIF neuron writes voltage - (threshold + refractory) as one
+    series: exactly the difference of the two series of the three-output kernel, and the backward
+    pass on it (threshold 0) returns the same input gradient, bit for bit."""
+    rng = rng_for('margin', shape)
+    B, C, T = shape
+    zeros = dev(np.zeros(shape[:-1]), cuda)
+    x = rng.normal(0.2, 1.0, size=shape).astype(np.float32)
+    gs = rng.normal(size=shape).astype(np.float32)
+    cd, vd = decays(rng, C, 700, 900), decays(rng, C, 150, 250)
+    td, rd = decays(rng, C, 300, 500), decays(rng, C, 300, 500)
+    ths = quant(rng.uniform(0.8, 1.5, size=shape[:-1]))
+    args = (dev(x, cuda), dev(cd, cuda), dev(vd, cuda), dev(rd, cuda), dev(td, cuda), zeros, zeros, zeros,
+            dev(ths, cuda), 0.5, 1.0, W)
+    for delay in ((0,) if graded else (0, 1)):
+        (spike, voltage, thsum), fin_full = ops.alif_fwd(*args, dynamics_mode=False, graded=graded, spike_delay=delay)
+        (spike_m, margin, none), fin = ops.alif_fwd(*args, dynamics_mode=False, graded=graded, spike_delay=delay, margin=True)
+        assert none is None
+        assert_exact(spike_m, spike.cpu().numpy(), 'spikes of the margin form')
+        assert_exact(margin, (voltage - thsum).cpu().numpy(), 'margin = voltage - (threshold + refractory)')
+        for k in fin:
+            assert_exact(fin[k], fin_full[k].cpu().numpy(), k)
+        g_two, _, _ = ops.cuba_bwd(dev(gs, cuda), voltage, thsum, None, dev(cd, cuda), dev(vd, cuda), 100.0, 0.1, graded,
+                                   False, spike_delay=delay)
+        g_one, _, _ = ops.cuba_bwd(dev(gs, cuda), margin, 0.0, None, dev(cd, cuda), dev(vd, cuda), 100.0, 0.1, graded,
+                                   False, spike_delay=delay)
+        assert_exact(g_one, g_two.cpu().numpy(), 'input gradient from the margin')
+
+
+@pytest.mark.parametrize('shape', SHAPES)
 def test_alif_and_resonator_spikes_only(shape, cuda, ops):
     """The forward kernels of the ALIF, RF and ADRF neurons without the series that only the
     backward pass reads (what ``forward`` runs when nothing will be differentiated): the same
