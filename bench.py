@@ -177,9 +177,9 @@ WORKLOADS = {
     'alif_fwd': Workload('alif_fwd', (64, 4096, 2000), 12),   # x in; spike and voltage - threshold out (training forward)
     'alif_fwd_infer': Workload('alif_fwd_infer', (64, 4096, 2000), 8),   # x in, fp32 spikes out: forward under no_grad
     'alif_bwd': Workload('alif_bwd', (64, 4096, 2000), 12),   # grad_spike and voltage - threshold in; grad_x out
-    'adrf_fwd': Workload('adrf_fwd', (64, 8192, 1000), 24),
+    'adrf_fwd': Workload('adrf_fwd', (64, 8192, 1000), 20),   # re, im in; spike, re - threshold, im out (training forward)
     'adrf_fwd_infer': Workload('adrf_fwd_infer', (64, 8192, 1000), 12),   # re, im in, fp32 spikes out
-    'adrf_bwd': Workload('adrf_bwd', (64, 8192, 1000), 24),
+    'adrf_bwd': Workload('adrf_bwd', (64, 8192, 1000), 20),   # grad_spike, re - threshold, im in; grad_re, grad_im out
     'li_fwd': Workload('li_fwd', (64, 8192, 2000), 8),
     'li_bwd': Workload('li_bwd', (64, 8192, 2000), 8),
     # sigma-delta family (next to the path): running sum, delta encoder, fused relu neuron, 8 B per step each
@@ -509,14 +509,14 @@ def build_step(name, shape, device, seed):
         if name in ('adrf_fwd', 'adrf_fwd_infer'):
             def step():
                 return _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad,
-                                   spikes_only=name.endswith('infer'))
+                                   spikes_only=name.endswith('infer'), margin=not name.endswith('infer'))
             return step, 1, d
-        outs, _ = _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad)
-        d.update(real=outs[1], imag=outs[2], thsum=outs[3])
+        outs, _ = _ops.rf_fwd(d['re'], d['im'], sd, cdec, zeros, zeros, 0.5, W_SCALE, adaptive=ad, margin=True)
+        d.update(margin=outs[1], imag=outs[2])
         del d['re'], d['im'], outs
 
         def step():
-            return _ops.rf_bwd(d['g'], d['real'], d['imag'], d['thsum'], sd, cdec, 50.0, 0.1, False, False)
+            return _ops.rf_bwd(d['g'], d['margin'], d['imag'], 0.0, sd, cdec, 50.0, 0.1, False, False)
         return step, 1, d
     if name == 'li_fwd':
         d['x'] = torch.empty(shape, device=device).normal_(0.3, 1.0)

@@ -223,7 +223,10 @@ int sb_alif_fwd(const float* x, const float* cdecay, int64_t n_cdecay, const flo
  * spike, re, im, th + ref.  adapt = 1, mode 1: re, im, threshold, refractory.
  * spike_delay / delay_head (mode 0, binary spikes) as in sb_cuba_fwd; sb_rf_bwd
  * takes the same spike_delay to read the gradient of the late series.
- * Mode 0 with out1, out2 (and out3) null (binary spikes): only the spikes are written. */
+ * Mode 0 with out1, out2 (and out3) null (binary spikes): only the spikes are written.
+ * adapt = 1, mode 0 with out3 null: out1 receives re - (threshold + refractory) instead of
+ * re; sb_rf_bwd on it with the scalar threshold 0 and no sin / cos gradients gives the same
+ * input gradients (the spike's gradient reads re only through that difference). */
 int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, const float* cos_decay,
               int64_t n_decay, const float* ref_decay, int64_t n_ref_decay, const float* th_decay,
               int64_t n_th_decay, const float* re_state, const float* im_state, const float* ref_state,

@@ -310,6 +310,18 @@ int sb_rf_fwd(const float* re_in, const float* im_in, const float* sin_decay, co
                                                          final_s, spike_scale, sc};
     return launch_rowscan<RfFwd<false, false, false, true>>(p, rg, in, lean, st, bd);
   }
+  if (adapt && mode == 0 && out1 != nullptr && out2 != nullptr && out3 == nullptr) {
+    // training without sin / cos gradients: out1 = re - (threshold + refractory), out2 = im
+    float* three[3] = {out1, out2, out0};
+    if (graded) {
+      typename RfFwd<true, false, true, false, true>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,
+                                                                final_s, spike_scale, sc};
+      return launch_rowscan<RfFwd<true, false, true, false, true>>(p, rg, in, three, st, bd);
+    }
+    typename RfFwd<true, false, false, false, true>::Params p{rp, ap, k_spike, final_re, final_im, final_th, final_ref,
+                                                               final_s, spike_scale, sc};
+    return launch_rowscan<RfFwd<true, false, false, false, true>>(p, rg, in, three, st, bd);
+  }
   if (adapt) {
     if (mode == 1) SB_GO(true, true, false)
     else if (graded) SB_GO(true, false, true)

@@ -653,7 +653,8 @@ struct AlifFwd {
   static constexpr bool HAS_FAST = true;
   // LEAN: the stage holds the input only and the step chain, not memory, sets the pace: one box per stage, so that
   // 18 warps fit an SM (0.57 -> 0.68 of copy bandwidth at 8 bytes per step against two boxes)
-  SB_PIPE((DYN ? 3 : (NBIT ? 3 : 4)), ((MARGIN && NBIT) ? 3 : ((!DYN && NBIT && !LEAN) ? 2 : 1)), (DYN ? 16 : 32));
+  // MARGIN (one output tile per stage): five stages of one box, 0.73 -> 0.76 against three stages of three
+  SB_PIPE(((MARGIN && NBIT) ? 5 : (DYN ? 3 : (NBIT ? 3 : 4))), ((!DYN && NBIT && !LEAN && !MARGIN) ? 2 : 1), (DYN ? 16 : 32));
   struct Params {
     DecayVec cdecay, vdecay;
     const float* cstate;
@@ -728,12 +729,16 @@ struct AlifFwd {
 // DYN (ADAPT only): outputs re, im, threshold, refractory
 // else            : outputs re, im, [threshold + refractory], spike
 // LEAN            : binary spikes only (forward() when nothing will be differentiated)
+// MARGIN (ADAPT)  : outputs re - (threshold + refractory), im, spike: the gradient of the complex spike
+//                   reads re only through that difference (spike/complex.py:144-167), and without sin / cos
+//                   gradients the reverse scan reads nothing else of the forward pass
 // ===========================================================================
-template <bool ADAPT, bool DYN, bool GRADED, bool LEAN = false>
+template <bool ADAPT, bool DYN, bool GRADED, bool LEAN = false, bool MARGIN = false>
 struct RfFwd {
   static_assert(ADAPT || !DYN, "DYN needs ADAPT");
   static_assert(!LEAN || (!DYN && !GRADED), "spikes only: forward mode, binary spikes");
-  static constexpr int NIN = 2, NOUT = LEAN ? 1 : (ADAPT ? 4 : 3);
+  static_assert(!MARGIN || (ADAPT && !DYN && !LEAN), "the margin form belongs to the adaptive forward");
+  static constexpr int NIN = 2, NOUT = LEAN ? 1 : (MARGIN ? 3 : (ADAPT ? 4 : 3));
   static constexpr bool REVERSE = false;
   static constexpr int NBIT = (!DYN && !GRADED) ? 1 : 0;
   static constexpr bool HAS_FAST = true;
@@ -785,6 +790,8 @@ struct RfFwd {
         last_s = GRADED ? __fdiv_rn(__fmul_rn(sp ? 1.f : 0.f, ref_), spike_scale) : (sp ? 1.f : 0.f);
         if constexpr (LEAN) {
           b[0] = last_s;
+        } else if constexpr (MARGIN) {
+          b[0] = __fsub_rn(ref_, thsum); b[1] = imf; b[2] = last_s;
         } else {
           b[0] = ref_; b[1] = imf; b[NOUT - 2] = thsum; b[NOUT - 1] = last_s;
         }

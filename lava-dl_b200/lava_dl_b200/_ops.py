@@ -575,10 +575,13 @@ def alif_fwd(x, cdecay, vdecay, ref_decay, th_decay, cstate, vstate, ref_state, 
 
 
 def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_scale, graded=False,
-           spike_scale=1.0, adaptive=None, dynamics_mode=False, spike_delay=0, delay_head=None, spikes_only=False):
+           spike_scale=1.0, adaptive=None, dynamics_mode=False, spike_delay=0, delay_head=None, spikes_only=False,
+           margin=False):
     """``adaptive`` = None for RF, else dict(ref_decay, th_decay, ref_state, th_state, th_step, th0).
     ``spikes_only`` (forward mode, binary spikes): the state series, which only the backward pass
-    reads, are not written; ``outs`` is then ``[spike, None, ...]``."""
+    reads, are not written; ``outs`` is then ``[spike, None, ...]``.
+    ``margin`` (adaptive, forward mode): ``outs`` is ``[spike, re - (threshold + refractory), im, None]`` -- what
+    the backward pass needs when sin / cos are not learnt (``rf_bwd`` on it with threshold 0)."""
     N.require_cuda(re_in, im_in)
     re_in, im_in = _c(re_in), _c(im_in)
     sd, cd = _param(sin_decay, re_in), _param(cos_decay, re_in)
@@ -599,6 +602,10 @@ def rf_fwd(re_in, im_in, sin_decay, cos_decay, re_state, im_state, threshold, w_
         if dynamics_mode or graded:
             raise ValueError('spikes_only needs forward mode and binary spikes')
         outs = [outs[0]] + [None] * (nout - 1)
+    elif margin:
+        if dynamics_mode or not adapt:
+            raise ValueError('margin needs the adaptive neuron in forward mode')
+        outs = outs[:3] + [None]
     fin = [_vec(re_in) for _ in range(5)]
     g = geom(re_in, *counts)
     head = None if delay_head is None else row_state(delay_head, re_in)

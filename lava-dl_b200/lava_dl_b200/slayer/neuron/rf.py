@@ -42,12 +42,18 @@ class _FusedForward(torch.autograd.Function):
         # the state series are what the backward pass reads: with nothing to differentiate
         # (inference) only the spikes are written
         lean = not graded and not any(ctx.needs_input_grad)
+        # adaptive neuron, sin / cos not learnt: the backward pass reads re only through
+        # re - (threshold + refractory), so that one series replaces two
+        margin = ad is not None and not lean and not (ctx.needs_input_grad[2] or ctx.needs_input_grad[3])
         outs, fin = _ops.rf_fwd(real_input, imag_input, sin_decay, cos_decay, real_state, imag_state, threshold,
                                 w_scale, graded=graded, spike_scale=1.0, adaptive=ad, spike_delay=spike_delay,
-                                delay_head=delay_head, spikes_only=lean)
+                                delay_head=delay_head, spikes_only=lean, margin=margin)
         spike, real, imag = outs[:3]
         if lean:
             ctx.threshold = threshold
+        elif margin:
+            ctx.save_for_backward(real, imag, sin_decay, cos_decay)
+            ctx.threshold = 0.0
         elif ad is None:
             ctx.save_for_backward(real, imag, sin_decay, cos_decay)
             ctx.threshold = threshold

@@ -559,6 +559,42 @@ def test_alif_margin_form(shape, graded, cuda, ops):
 
 
 @pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('graded', [False, True])
+def test_adrf_margin_form(shape, graded, cuda, ops):
+    """The training forward of the adaptive resonator without sin / cos gradients writes
+    re - (threshold + refractory) and im: the difference of the series of the four-output kernel,
+    and the backward pass on it (threshold 0) returns the same input gradients, bit for bit."""
+    rng = rng_for('rmargin', shape)
+    B, C, T = shape
+    zeros = dev(np.zeros(shape[:-1]), cuda)
+    re_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    im_in = rng.normal(0, 0.5, size=shape).astype(np.float32)
+    gs = rng.normal(size=shape).astype(np.float32)
+    sd, cdk = sincos(rng, C)
+    td, rd = decays(rng, C, 300, 500), decays(rng, C, 300, 500)
+    ths = quant(rng.uniform(0.3, 0.8, size=shape[:-1]))
+    ad = dict(ref_decay=dev(rd, cuda), th_decay=dev(td, cuda), ref_state=zeros, th_state=dev(ths, cuda), th_step=0.25, th0=0.5)
+    a = (dev(re_in, cuda), dev(im_in, cuda), dev(sd, cuda), dev(cdk, cuda), zeros, zeros, 0.5, W)
+    for delay in ((0,) if graded else (0, 1)):
+        full, fin_full = ops.rf_fwd(*a, adaptive=ad, graded=graded, spike_delay=delay)
+        lean, fin = ops.rf_fwd(*a, adaptive=ad, graded=graded, spike_delay=delay, margin=True)
+        assert lean[3] is None
+        assert_exact(lean[0], full[0].cpu().numpy(), 'spikes of the margin form')
+        assert_exact(lean[1], (full[1] - full[3]).cpu().numpy(), 'margin = re - (threshold + refractory)')
+        assert_exact(lean[2], full[2].cpu().numpy(), 'imaginary series')
+        for k in fin:
+            assert_exact(fin[k], fin_full[k].cpu().numpy(), k)
+        two = ops.rf_bwd(dev(gs, cuda), full[1], full[2], full[3], dev(sd, cuda), dev(cdk, cuda), 50.0, 0.1, graded, False,
+                         spike_delay=delay)
+        one = ops.rf_bwd(dev(gs, cuda), lean[1], lean[2], 0.0, dev(sd, cuda), dev(cdk, cuda), 50.0, 0.1, graded, False,
+                         spike_delay=delay)
+        assert_exact(one[0], two[0].cpu().numpy(), 'grad_re from the margin')
+        assert_exact(one[1], two[1].cpu().numpy(), 'grad_im from the margin')
+    with pytest.raises(ValueError):
+        ops.rf_fwd(*a, adaptive=None, margin=True)
+
+
+@pytest.mark.parametrize('shape', SHAPES)
 def test_alif_and_resonator_spikes_only(shape, cuda, ops):
     """The forward kernels of the ALIF, RF and ADRF neurons without the series that only the
     backward pass reads (what ``forward`` runs when nothing will be differentiated): the same
