@@ -62,12 +62,15 @@ THR = 1.25 + 0.01 / 4096
 # proportion to the batch: roofline.traffic = this figure x the units of a launch.
 NCU_TRAFFIC_PER_UNIT = {
     'cuba_fwd': 11.70,
+    'cuba_fwd_infer': 7.76,
     'cuba_fwd_delayed': 11.70,
     'cuba_bwd': 11.88,
-    'alif_fwd': 15.28,
-    'alif_bwd': 15.82,
-    'adrf_fwd': 23.61,
-    'adrf_bwd': 24.04,
+    'alif_fwd': 11.31,
+    'alif_fwd_infer': 7.46,
+    'alif_bwd': 11.63,
+    'adrf_fwd': 19.69,
+    'adrf_fwd_infer': 12.01,
+    'adrf_bwd': 19.82,
     'li_fwd': 7.75,
     'li_bwd': 7.73,
     'sigma_fwd': 7.74,

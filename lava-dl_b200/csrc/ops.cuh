@@ -744,7 +744,8 @@ struct RfFwd {
   static constexpr bool HAS_FAST = true;
   // three tiles per stage (adaptive forward): four stages measured best (adrf_fwd 0.78 -> 0.81 of copy bandwidth)
   // LEAN (two input tiles per stage, no output tile): two stages of one box, 14 warps per SM (0.46 -> 0.62)
-  SB_PIPE((LEAN ? 2 : ((NOUT - NBIT) == 3 ? 4 : 3)), 1, ((NOUT - NBIT) >= 4 ? 16 : 32));
+  // MARGIN (two output tiles): four stages, 0.77 -> 0.82
+  SB_PIPE((LEAN ? 2 : (((NOUT - NBIT) == 3 || MARGIN) ? 4 : 3)), 1, ((NOUT - NBIT) >= 4 ? 16 : 32));
   struct Params {
     ResParams res;
     AthParams ath;    // ADAPT only
@@ -830,7 +831,9 @@ struct RfBwd {
   static constexpr int NIN = 3 + (TENSOR_THR ? 1 : 0), NOUT = 2;
   static constexpr bool REVERSE = true;
   static constexpr int NBIT = 0;
-  SB_PIPE((PGRAD ? 3 : 6), 1, 16);   // six stages measured best without sin/cos gradients (adrf_bwd 0.82 -> 0.87)
+  // six stages of 16 steps measured best with a threshold series and no sin/cos gradients (0.82 -> 0.87); with a scalar
+  // threshold (three input tiles: the plain resonator, and the adaptive one's margin form) four stages of 32 steps (0.85 -> 0.88)
+  SB_PIPE((PGRAD ? 3 : (TENSOR_THR ? 6 : 4)), 1, ((PGRAD || TENSOR_THR) ? 16 : 32));
   struct Params {
     DecayVec sin_decay, cos_decay;
     CSurrogate sg;
