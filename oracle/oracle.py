@@ -175,7 +175,7 @@ def adres_fwd(re_in, im_in, sin_decay, cos_decay, ref_decay, th_decay, re_state,
 def _thr(threshold, like):
     if isinstance(threshold, np.ndarray) and threshold.size > 1:
         return _f(np.broadcast_to(threshold, like.shape)), 0.0
-    return None, float(np.float32(threshold))
+    return None, float(np.asarray(threshold, dtype=np.float32).reshape(-1)[0])
 
 
 def spike_fwd(v, threshold, graded=False, scale=1):
