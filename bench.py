@@ -228,6 +228,7 @@ SYNAPSE = ('pool_', 'conv5_', 'conv3_')
 # one-step delay); units = neuron-steps over all seven spiking layers (33291 neurons per sample)
 WORKLOADS['cfg4_fwd'] = Workload('cfg4_fwd', (32, 2, 128, 128, 300), 0)
 WORKLOADS['cfg4_train'] = Workload('cfg4_train', (32, 2, 128, 128, 300), 0)
+WORKLOADS['cfg4_fwd_graph'] = Workload('cfg4_fwd_graph', (32, 2, 128, 128, 300), 0)   # cfg4_fwd replayed as one CUDA graph
 # dense recurrent CUBA block (block.cuba.Recurrent, 512 -> 512 neurons): one launch per direction for the walk over time
 WORKLOADS['recurrent_fwd'] = Workload('recurrent_fwd', (128, 512, 300), 0)
 WORKLOADS['recurrent_train'] = Workload('recurrent_train', (128, 512, 300), 0)
@@ -269,12 +270,19 @@ def build_step(name, shape, device, seed):
         x = (torch.rand(shape, device=device, generator=gen) < 0.02).float()
         params = [q for q in net.parameters() if q.requires_grad]
 
-        def forward():
-            y = x
+        def forward_of(y):
             for layer in net:
                 y = layer(y)
             return y
 
+        def forward():
+            return forward_of(x)
+
+        if name == 'cfg4_fwd_graph':
+            # the same forward pass captured once and replayed as one CUDA graph: at a few samples per GPU
+            # the eager pass is bound by the ~60 launches it makes, not by their kernels
+            graphed = slayer.utils.Graphed(lambda inp: forward_of(inp), x)
+            return (lambda: graphed(graphed.input)), 10, (net, x, graphed)
         if not train:
             def step():
                 with torch.no_grad():
@@ -932,7 +940,7 @@ def time_steps(step, steps, warmup, device, dist, sampler=None):
 
 # legs reported beside the headline in the default run: every benchmark configuration's kernels
 EXTRA_LEGS = ('cuba_fwd_infer', 'cuba_bwd', 'alif_fwd', 'alif_fwd_infer', 'alif_bwd', 'adrf_fwd', 'adrf_fwd_infer', 'adrf_bwd', 'shift', 'fir_conv', 'delay_fir_fwd',
-              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cuba_fwd_cfg0_graph', 'cfg4_fwd', 'cfg4_train')
+              'delay_fir_bwd', 'cuba_fwd_cfg0', 'cuba_fwd_cfg0_api', 'cuba_fwd_cfg0_graph', 'cfg4_fwd', 'cfg4_fwd_graph', 'cfg4_train')
 
 
 def run_extra_legs(device, dist, world, rank, steps=5, warmup=3, legs=EXTRA_LEGS):

@@ -127,7 +127,10 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
                                             # a width that is no multiple of four; 1 x 1; a partial channel chunk
                                             ((2, 16, 6, 6, 64), 32, 3, 1), ((1, 2, 9, 10, 44), 16, 5, 2),
                                             ((2, 16, 5, 7, 32), 70, 3, 1), ((2, 24, 3, 5, 96), 24, 1, 0),
-                                            ((1, 11, 4, 9, 36), 5, 3, 0), ((3, 3, 12, 12, 300), 8, 5, 1)])
+                                            ((1, 11, 4, 9, 36), 5, 3, 0), ((3, 3, 12, 12, 300), 8, 5, 1),
+                                            # few input channels packed 2 or 4 to a column: one channel 5 x 5, three channels 1 x 1
+                                            # and 3 x 3 (an MMA's eight rows then span several taps, or several output columns)
+                                            ((2, 1, 6, 7, 36), 8, 5, 2), ((2, 3, 5, 6, 64), 8, 1, 0), ((2, 4, 6, 7, 36), 8, 3, 0)])
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
