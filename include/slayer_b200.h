@@ -348,6 +348,11 @@ int sb_conv_uses_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int6
 int sb_conv_fits_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw,
                               int64_t ph, int64_t pw, int64_t T);
 
+/* 1 when sb_conv_wgrad takes the problem (accumulator tiles of one CTA, one output row staged in
+ * shared memory, T % 4 == 0), else 0: the caller then falls back (the mirror package uses ATen's
+ * convolution backward). */
+int sb_conv_wgrad_fits(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw,
+                       int64_t ph, int64_t pw, int64_t T);
 /* Weight gradient of the same convolution (what convolution_backward returns for
  * the weight of the Conv3d at synapse/layer.py:297-323), fp32:
  *   grad_weight[co,ci,i,j] = sum_{n,ho,wo,t} grad_y[n,co,ho,wo,t] * x[n,ci,ho+i-ph,wo+j-pw,t].

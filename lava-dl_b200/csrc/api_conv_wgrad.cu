@@ -66,33 +66,44 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
   // Staging with cp.async, double buffered: a thread keeps one (column, time word) position of
   // the row and walks down the rows, so the loop has no divisions; positions outside the tensor
   // (channels past Co, rows and columns of the zero padding, time past T) are zero filled.
-  const int dz_lane = tid % (g.Wo * kQ), dz_r0 = tid / (g.Wo * kQ), dz_rstep = max(nthreads / (g.Wo * kQ), 1);
-  const int x_lane = tid % (g.Wp * kQ), x_r0 = tid / (g.Wp * kQ), x_rstep = max(nthreads / (g.Wp * kQ), 1);
+  // A row has P = columns x time words positions.  With at least P threads, tid / P rows are staged side by
+  // side; with fewer (a narrow layer with few accumulator tiles, or a wide image) every thread takes
+  // several positions of a row.
+  const int dz_P = g.Wo * kQ, x_P = g.Wp * kQ;
+  const bool dz_wide = nthreads >= dz_P, x_wide = nthreads >= x_P;
+  const int dz_lane0 = dz_wide ? tid % dz_P : tid, dz_r0 = dz_wide ? tid / dz_P : 0;
+  const int dz_rstep = dz_wide ? nthreads / dz_P : 1, dz_lstep = dz_wide ? dz_P : nthreads;
+  const int x_lane0 = x_wide ? tid % x_P : tid, x_r0 = x_wide ? tid / x_P : 0;
+  const int x_rstep = x_wide ? nthreads / x_P : 1, x_lstep = x_wide ? x_P : nthreads;
   auto stage = [&](int q0, int buf) {
     const uint32_t dst0 = sm_base + (uint32_t)(buf * buf_words) * 16u;
-    if (tid < dz_rstep * g.Wo * kQ) {
-      const int q = dz_lane % kQ, w = dz_lane / kQ;
-      const bool tin = q0 + q < TV;
-      const float* src = dz + (((int64_t)n * g.Co * g.Ho + ho) * g.Wo + w) * g.T + (int64_t)(q0 + q) * 4;
-      for (int co = dz_r0; co < rows_dz; co += dz_rstep) {
-        const bool ok = tin && co < g.Co;
-        const float* p = ok ? src + (int64_t)co * g.Ho * g.Wo * g.T : dz;
-        const int row = (co % kTile) * g.ncog + co / kTile;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + (uint32_t)(row * g.dz_row + dz_lane) * 16u),
-                     "l"(p), "r"(ok ? 16 : 0) : "memory");
+    if (dz_r0 < dz_rstep) {
+      for (int lane = dz_lane0; lane < dz_P; lane += dz_lstep) {
+        const int q = lane % kQ, w = lane / kQ;
+        const bool tin = q0 + q < TV;
+        const float* src = dz + (((int64_t)n * g.Co * g.Ho + ho) * g.Wo + w) * g.T + (int64_t)(q0 + q) * 4;
+        for (int co = dz_r0; co < rows_dz; co += dz_rstep) {
+          const bool ok = tin && co < g.Co;
+          const float* p = ok ? src + (int64_t)co * g.Ho * g.Wo * g.T : dz;
+          const int row = (co % kTile) * g.ncog + co / kTile;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + (uint32_t)(row * g.dz_row + lane) * 16u),
+                       "l"(p), "r"(ok ? 16 : 0) : "memory");
+        }
       }
     }
-    if (tid < x_rstep * g.Wp * kQ) {
-      const int q = x_lane % kQ, wp = x_lane / kQ, win = wp - g.pw;
-      const bool cin = q0 + q < TV && win >= 0 && win < g.W;
-      const float* src = x + ((int64_t)n * g.Ci * g.H * g.W + win) * g.T + (int64_t)(q0 + q) * 4;
-      for (int r = x_r0; r < rows_x; r += x_rstep) {
-        const int ci = r / g.kh, hin = ho + (r - ci * g.kh) - g.ph;
-        const bool ok = cin && hin >= 0 && hin < g.H;
-        const float* p = ok ? src + ((int64_t)ci * g.H + hin) * g.W * g.T : x;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     ::"r"(dst0 + (uint32_t)(rows_dz * g.dz_row + r * g.x_row + q * g.Wp + wp) * 16u), "l"(p), "r"(ok ? 16 : 0)
-                     : "memory");
+    if (x_r0 < x_rstep) {
+      for (int lane = x_lane0; lane < x_P; lane += x_lstep) {
+        const int q = lane % kQ, wp = lane / kQ, win = wp - g.pw;
+        const bool cin = q0 + q < TV && win >= 0 && win < g.W;
+        const float* src = x + ((int64_t)n * g.Ci * g.H * g.W + win) * g.T + (int64_t)(q0 + q) * 4;
+        for (int r = x_r0; r < rows_x; r += x_rstep) {
+          const int ci = r / g.kh, hin = ho + (r - ci * g.kh) - g.ph;
+          const bool ok = cin && hin >= 0 && hin < g.H;
+          const float* p = ok ? src + ((int64_t)ci * g.H + hin) * g.W * g.T : x;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                       ::"r"(dst0 + (uint32_t)(rows_dz * g.dz_row + r * g.x_row + q * g.Wp + wp) * 16u), "l"(p), "r"(ok ? 16 : 0)
+                       : "memory");
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -197,6 +208,17 @@ extern "C" int64_t sb_conv_wgrad_scratch_bytes(int64_t N, int64_t Ci, int64_t Co
   const int64_t Ho = H + 2 * ph - kh + 1;
   if (N <= 0 || Ho <= 0) return 0;
   return N * Ho * Co * Ci * kh * kw * (int64_t)sizeof(float);
+}
+
+extern "C" int sb_conv_wgrad_fits(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw,
+                                  int64_t ph, int64_t pw, int64_t T) {
+  if (N < 0 || Ci < 1 || Co < 1 || H < 0 || W < 0 || T < 0 || kh < 1 || kw < 1 || ph < 0 || pw < 0 || (T & 3)) return 0;
+  const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+  if (Ho < 1 || Wo < 1 || N * Ho >= (1LL << 31) || Co * Ci * kh * kw >= (1LL << 31)) return 0;
+  if (((Co + kTile - 1) / kTile) * ((Ci * kh * kw + kTile - 1) / kTile) > kMaxThreads) return 0;
+  WgradGeom g;
+  size_t smem;
+  return wgrad_plan(N, Ci, Co, H, W, kh, kw, ph, pw, T, &g, &smem) == SB_OK ? 1 : 0;
 }
 
 extern "C" int sb_conv_wgrad(const float* x, const float* grad_y, float* grad_weight, void* scratch, int64_t N,

@@ -717,11 +717,14 @@ def conv_fwd(x, weight, padding, path=-1):
     return y
 
 
-def conv_wgrad_supported(x, weight):
-    """The weight-gradient kernel needs T % 4 == 0 and at most 384 accumulator tiles of 8 x 8."""
-    co, ci, kh, kw = weight.shape[:4]
-    tiles = ((co + 7) // 8) * ((ci * kh * kw + 7) // 8)
-    return x.shape[-1] % 4 == 0 and tiles <= 384 and x.data_ptr() % 16 == 0
+def conv_wgrad_supported(x, weight, padding=(0, 0)):
+    """Whether the weight-gradient kernel takes the layer: ``T % 4 == 0``, at most 384 accumulator
+    tiles of 8 x 8, one output row staged within its shared memory (the library decides)."""
+    if x.dim() != 5 or x.data_ptr() % 16 != 0:
+        return False
+    n, ci, h, w, t = x.shape
+    co, _, kh, kw = weight.shape[:4]
+    return N.load().sb_conv_wgrad_fits(n, ci, co, h, w, kh, kw, int(padding[0]), int(padding[1]), t) == 1
 
 
 def conv_wgrad(x, grad_y, weight_shape, padding):

@@ -122,7 +122,7 @@ class _SpikeConv(torch.autograd.Function):
         flipped = (kh - 1 - ctx.padding[0], kw - 1 - ctx.padding[1], 0)
         own_dgrad = flipped[0] >= 0 and flipped[1] >= 0 and _ops.conv_fwd_supported(
             grad_output, weight.transpose(0, 1), (1, 1, 1), flipped, (1, 1, 1), 1)
-        own_wgrad = _ops.conv_wgrad_supported(input, weight) and grad_output.data_ptr() % 16 == 0
+        own_wgrad = _ops.conv_wgrad_supported(input, weight, ctx.padding) and grad_output.data_ptr() % 16 == 0
         grad_input = grad_weight = None
         if ctx.needs_input_grad[0] and own_dgrad:
             grad_input = _ops.conv_dgrad(grad_output, weight, ctx.padding)

@@ -130,7 +130,10 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
                                             ((1, 11, 4, 9, 36), 5, 3, 0), ((3, 3, 12, 12, 300), 8, 5, 1),
                                             # few input channels packed 2 or 4 to a column: one channel 5 x 5, three channels 1 x 1
                                             # and 3 x 3 (an MMA's eight rows then span several taps, or several output columns)
-                                            ((2, 1, 6, 7, 36), 8, 5, 2), ((2, 3, 5, 6, 64), 8, 1, 0), ((2, 4, 6, 7, 36), 8, 3, 0)])
+                                            ((2, 1, 6, 7, 36), 8, 5, 2), ((2, 3, 5, 6, 64), 8, 1, 0), ((2, 4, 6, 7, 36), 8, 3, 0),
+                                            # rows with more (column, time word) positions than the weight-gradient kernel has
+                                            # threads; a row too wide for its shared memory (ATen takes that gradient)
+                                            ((1, 1, 4, 100, 8), 8, 3, 1), ((1, 2, 4, 260, 8), 16, 5, 2)])
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
