@@ -75,7 +75,8 @@ constexpr int kMaxLo = 8;                    // lo slots: kh + 2
 
 struct ConvTc {
   int N, Ci, Co, H, W, Ho, Wo, ph, pw, T;
-  int cpc;         // channels per column of a row slot: 2, 4, or a multiple of 8 (zero filled past Ci)
+  int ci0, cib;    // this launch's block of input channels: ci0 .. ci0 + cib - 1 (wide layers take several launches)
+  int cpc;         // channels per column of a row slot: 2, 4, or a multiple of 8 (zero filled past the block)
   int nm;          // MMAs per kernel row: each reads 8 consecutive 128-byte (column, channel) rows of the slot
   int box_bytes;   // bytes one TMA box delivers: columns x cpc x 128
   int npad;        // MMA N: output channels of this launch's channel groups, padded to 16
@@ -103,7 +104,9 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-template <int KH, int KW>
+// ACC: this launch adds to y (a block of input channels after the first); a kernel of its own, because the
+// read-modify-write of the drain warps needs registers the plain kernel should not pay for
+template <int KH, int KW, bool ACC>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict__ wgt, float* __restrict__ y,
                const ConvTc g, unsigned int* status) {
@@ -178,7 +181,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
     }
     const int tap = i * KW + j;
     float v = 0.f;
-    if (j < KW && ci < g.Ci && co0 + co < g.Co) v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + ci) * (KH * KW) + tap);
+    if (j < KW && ci < g.cib && co0 + co < g.Co)
+      v = __ldg(wgt + ((int64_t)(co0 + co) * g.Ci + g.ci0 + ci) * (KH * KW) + tap);
     const uint32_t hi = tf32_rn(v), lo = tf32_rn(__fsub_rn(v, __uint_as_float(hi)));
     any_blo |= (lo != 0u);
     const int kk = kp & 31;
@@ -208,7 +212,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           const uint32_t bar = bar_full + 8 * rq.slot;
           mbar_expect_tx(bar, (uint32_t)g.box_bytes);
           // box dimensions: steps, channels, columns, rows, samples
-          tma_load_5d(base + off_ring + rq.slot * g.slot_bytes, &xmap, tc * kTT, 0, wg * kWG - g.pw, q - g.ph, n, bar);
+          tma_load_5d(base + off_ring + rq.slot * g.slot_bytes, &xmap, tc * kTT, g.ci0, wg * kWG - g.pw, q - g.ph, n, bar);
         }
       }
       if (*dead) {
@@ -385,9 +389,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           }
           tmem_ld_wait();
           if (ok && live_pos) {
+            if constexpr (ACC) {
+              // loads first, sixteen at a time: written as load-add-store per channel the stores would keep
+              // each next load waiting (the compiler cannot tell that the channels do not alias)
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (e < ncol && cb + e < nco) dst[(cb + e) * cstride] = __uint_as_float(r[e]);
+              for (int h = 0; h < 32; h += 16) {
+                float prev[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                  prev[e] = (h + e < ncol && cb + h + e < nco) ? __ldcg(dst + (cb + h + e) * cstride) : 0.f;
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                  if (h + e < ncol && cb + h + e < nco)
+                    dst[(cb + h + e) * cstride] = __fadd_rn(prev[e], __uint_as_float(r[h + e]));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (e < ncol && cb + e < nco) dst[(cb + e) * cstride] = __uint_as_float(r[e]);
+            }
           }
           cb += ncol;
         }
@@ -411,17 +431,15 @@ struct TcPlan {
   bool ok;
 };
 
-TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph,
-                    int64_t pw, int64_t T) {
+// Plan for one launch over a block of `cb` input channels (the whole layer when cb == Ci).
+TcPlan plan_block(int64_t N, int64_t Ci, int64_t cb, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph,
+                  int64_t pw, int64_t T) {
   TcPlan p{};
   p.ok = false;
-  if (!((kh == 1 && kw == 1) || (kh == 3 && kw == 3) || (kh == 5 && kw == 5))) return p;
-  if (T < kTT || (T & 3) || Ci > 256 || N > 65535 * 16 || H > (1 << 20) || W > (1 << 20) || T > (1 << 28)) return p;
   const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
-  if (Ho < 1 || Wo < 1) return p;
   // channels per column of a row slot: few channels are packed 2 or 4 to a column, so that the eight
   // rows an MMA reads span several taps instead of zero-filled channels
-  const int cpc = Ci <= 2 ? 2 : (Ci <= 4 ? 4 : (int)((Ci + 7) / 8) * 8);
+  const int cpc = cb <= 2 ? 2 : (cb <= 4 ? 4 : (int)((cb + 7) / 8) * 8);
   const int per = cpc < 8 ? 8 / cpc : 1;                                 // columns (taps) per MMA
   const int nm = cpc < 8 ? (int)((kw + per - 1) / per) : (int)kw * (cpc / 8);
   const int wcols = cpc < 8 ? (kWG - 1) + nm * per : (int)(kWG + kw - 1);
@@ -440,11 +458,34 @@ TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int
   if (ahead < 2 || ngroup > 65535) return p;
   const int R = (int)(kh + ahead);
   const int64_t smem = fixed + (int64_t)R * slot;
-  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, cpc, nm, (int)box_bytes, npad,
-               (int)((Wo + kWG - 1) / kWG), (int)((T + kTT - 1) / kTT), (int)slot, R, (int)b_bytes};
+  p.g = ConvTc{(int)N, (int)Ci, (int)Co, (int)H, (int)W, (int)Ho, (int)Wo, (int)ph, (int)pw, (int)T, 0, (int)cb, cpc, nm,
+               (int)box_bytes, npad, (int)((Wo + kWG - 1) / kWG), (int)((T + kTT - 1) / kTT), (int)slot, R, (int)b_bytes};
   // at least 120 KB so that two CTAs (two TMEM allocations of 512 columns) never share an SM
   p.smem = (size_t)(smem < 120 * 1024 ? 120 * 1024 : smem);
   p.ok = true;
+  return p;
+}
+
+// The whole layer in one launch when its rings and weights fit shared memory; else in blocks of input
+// channels, each launch after the first adding to the output (the fewest blocks, of equal size rounded up
+// to 8 channels).  *nblocks says how many launches.
+TcPlan plan_conv_tc(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph,
+                    int64_t pw, int64_t T, int* nblocks) {
+  TcPlan p{};
+  p.ok = false;
+  *nblocks = 0;
+  if (!((kh == 1 && kw == 1) || (kh == 3 && kw == 3) || (kh == 5 && kw == 5))) return p;
+  if (T < kTT || (T & 3) || Ci > 1024 || N > 65535 * 16 || H > (1 << 20) || W > (1 << 20) || T > (1 << 28)) return p;
+  const int64_t Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+  if (Ho < 1 || Wo < 1) return p;
+  p = plan_block(N, Ci, Ci, Co, H, W, kh, kw, ph, pw, T);
+  if (p.ok) { *nblocks = 1; return p; }
+  for (int nb = 2; nb <= 16 && Ci / nb >= 8; ++nb) {
+    const int64_t cb = (((Ci + nb - 1) / nb) + 7) & ~7LL;
+    p = plan_block(N, Ci, cb, Co, H, W, kh, kw, ph, pw, T);
+    if (p.ok) { *nblocks = (int)((Ci + cb - 1) / cb); return p; }
+  }
+  p.ok = false;
   return p;
 }
 
@@ -457,7 +498,8 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
                 int64_t kh, int64_t kw, int64_t ph, int64_t pw, int64_t T, cudaStream_t st, bool* taken) {
   *taken = false;
   if ((((uintptr_t)x) | ((uintptr_t)y)) & 15u) return SB_OK;
-  const TcPlan p = plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T);
+  int nblocks = 0;
+  const TcPlan p = plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T, &nblocks);
   if (!p.ok) return SB_OK;
   // The box lists its dimensions as (steps, channels, columns, rows, samples): that is the order a
   // row slot has in shared memory.  Channels past Ci are out of range and read zeros.
@@ -474,11 +516,22 @@ int conv_tc_try(const float* x, const float* weight, float* y, int64_t N, int64_
   const dim3 grid((unsigned)gx, (unsigned)ngroup);
   unsigned int* status = status_ptr();
   if (!status) return SB_ERR_CUDA;
+  // one launch per block of input channels; every launch after the first adds to y
 #define SB_GO(KH, KW)                                                                                        \
   {                                                                                                          \
-    auto fn = conv_tc_kernel<KH, KW>;                                                                        \
+    auto fn = conv_tc_kernel<KH, KW, false>;                                                                 \
+    auto fn_acc = conv_tc_kernel<KH, KW, true>;                                                              \
     SB_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem)); \
-    fn<<<grid, kThreads, p.smem, st>>>(xmap, weight, y, p.g, status);                                        \
+    if (nblocks > 1)                                                                                         \
+      SB_CUDA(cudaFuncSetAttribute((const void*)fn_acc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem)); \
+    ConvTc gb = p.g;                                                                                         \
+    const int block = gb.cib;                                                                                \
+    for (int b = 0; b < nblocks; ++b) {                                                                      \
+      gb.ci0 = b * block;                                                                                    \
+      gb.cib = (int)(Ci - gb.ci0 < block ? Ci - gb.ci0 : block);                                             \
+      if (b == 0) fn<<<grid, kThreads, p.smem, st>>>(xmap, weight, y, gb, status);                           \
+      else fn_acc<<<grid, kThreads, p.smem, st>>>(xmap, weight, y, gb, status);                              \
+    }                                                                                                        \
   }
   if (kh == 1) SB_GO(1, 1)
   else if (kh == 3) SB_GO(3, 3)
@@ -497,10 +550,12 @@ constexpr int64_t kMinTapsForAuto = 64;
 
 extern "C" int sb_conv_fits_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh,
                                          int64_t kw, int64_t ph, int64_t pw, int64_t T) {
-  return plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T).ok ? 1 : 0;
+  int nb = 0;
+  return plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T, &nb).ok ? 1 : 0;
 }
 
 extern "C" int sb_conv_uses_tensor_cores(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh,
                                          int64_t kw, int64_t ph, int64_t pw, int64_t T) {
-  return (Ci * kh * kw >= kMinTapsForAuto && plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T).ok) ? 1 : 0;
+  int nb = 0;
+  return (Ci * kh * kw >= kMinTapsForAuto && plan_conv_tc(N, Ci, Co, H, W, kh, kw, ph, pw, T, &nb).ok) ? 1 : 0;
 }

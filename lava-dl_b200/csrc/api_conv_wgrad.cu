@@ -165,13 +165,24 @@ conv_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dz, flo
   }
 }
 
+// Sum of the N * Ho partial gradients in a fixed order.  A 32 x 8 thread block owns 32 neighbouring
+// outputs: thread (x, y) adds every eighth partial of output x (coalesced across x), the eight
+// slices meet in shared memory.  (One thread per output walking all partials left 18 blocks of
+// latency-bound threads: 0.05 ms per layer.)
 __global__ void conv_wgrad_fold_kernel(const float* __restrict__ partial, float* __restrict__ grad_w, int nparts,
                                        int nout) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= nout) return;
+  __shared__ double part[8][33];
+  const int i = blockIdx.x * 32 + threadIdx.x;
   double s = 0.0;
-  for (int p = 0; p < nparts; ++p) s += (double)partial[(size_t)p * nout + i];
-  grad_w[i] = (float)s;
+  if (i < nout)
+    for (int p = threadIdx.y; p < nparts; p += 8) s += (double)partial[(size_t)p * nout + i];
+  part[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < nout) {
+#pragma unroll
+    for (int y = 1; y < 8; ++y) s += part[y][threadIdx.x];
+    grad_w[i] = (float)s;
+  }
 }
 
 int wgrad_plan(int64_t N, int64_t Ci, int64_t Co, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t ph,
@@ -247,8 +258,8 @@ extern "C" int sb_conv_wgrad(const float* x, const float* grad_y, float* grad_we
   const int threads = ((g.owners * g.wgroups + 31) / 32) * 32;
   conv_wgrad_kernel<<<(unsigned)(N * Ho), threads, smem, st>>>(x, grad_y, (float*)scratch, g);
   SB_CUDA(cudaGetLastError());
-  conv_wgrad_fold_kernel<<<(unsigned)((nout + 255) / 256), 256, 0, st>>>((const float*)scratch, grad_weight,
-                                                                          (int)(N * Ho), (int)nout);
+  conv_wgrad_fold_kernel<<<(unsigned)((nout + 31) / 32), dim3(32, 8), 0, st>>>((const float*)scratch, grad_weight,
+                                                                                (int)(N * Ho), (int)nout);
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

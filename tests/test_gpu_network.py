@@ -133,7 +133,10 @@ def test_sum_pool_kernel_matches_conv3d(shape, k, cuda):
                                             ((2, 1, 6, 7, 36), 8, 5, 2), ((2, 3, 5, 6, 64), 8, 1, 0), ((2, 4, 6, 7, 36), 8, 3, 0),
                                             # rows with more (column, time word) positions than the weight-gradient kernel has
                                             # threads; a row too wide for its shared memory (ATen takes that gradient)
-                                            ((1, 1, 4, 100, 8), 8, 3, 1), ((1, 2, 4, 260, 8), 16, 5, 2)])
+                                            ((1, 1, 4, 100, 8), 8, 3, 1), ((1, 2, 4, 260, 8), 16, 5, 2),
+                                            # wide layers: the tensor-core kernel takes the input channels in blocks (three launches
+                                            # of 16, 16 and 8 channels; the input gradient of the second in two of 16)
+                                            ((2, 40, 6, 6, 64), 32, 3, 1), ((2, 16, 6, 9, 32), 32, 3, 1)])
 def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     """The direct convolution synapse kernel against F.conv3d: exact on spikes with
     weights on the 1/32 grid (every partial sum is representable), 1e-5 on floats;
