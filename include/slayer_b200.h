@@ -332,7 +332,8 @@ int sb_pool_bwd(const float* grad_y, const float* weight, float* grad_x, int64_t
  * (after the pre-hook), y [N, Co, H+2ph-kh+1, W+2pw-kw+1, T].
  * Two kernels: an implicit GEMM on the tensor cores (tcgen05, operands split into TF32 pairs so
  * that the result keeps fp32 accuracy; bit-exact for spikes and weights on a 1/32 grid) for 1x1,
- * 3x3 and 5x5 kernels with T a multiple of 4 and >= 32 and 16-byte aligned tensors, and an fp32
+ * 3x3 and 5x5 kernels with T a multiple of 4 and >= 32 and 16-byte aligned tensors (a layer too
+ * wide for its shared memory runs in blocks of input channels, one launch each), and an fp32
  * kernel for every shape with N * Ho <= 65535 and the weights of 16 output channels in 96 KB.
  * sb_conv_fwd picks the tensor cores when the shape allows and the contraction is long enough to
  * pay for them (Ci * kh * kw >= 64); sb_conv_fwd_path takes the choice from the caller:
