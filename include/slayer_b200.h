@@ -194,6 +194,14 @@ int sb_cuba_fwd_packed(const float* x, const float* cdecay, int64_t n_cdecay, co
  * thr_tensor (nullable): per-element threshold (ALIF passes th + ref).
  * grad_cdecay/grad_vdecay (nullable, both or none) need `current` and scratch.
  * spike_delay = 1: grad_spike is the gradient of the one-step-late series. */
+/* Host side of sb_cuba_fwd_packed: expands spike_bits (host memory, uint32[rows][ceil(T / 32)]) into
+ * the fp32 0 / 1 tensor out (host memory, float[rows][T]) that Neuron.forward returns, on `threads`
+ * CPU threads (0 = all).  stream_ordered = 0: done on return.  stream_ordered = 1: enqueued on
+ * `stream` as a host function, i.e. after the copy of the bits that was queued there before it and
+ * before whatever is queued after it; both buffers must stay alive until the stream reaches it. */
+int sb_unpack_spikes_host(const uint32_t* spike_bits, float* out, int64_t rows, int64_t T, int threads,
+                          int stream_ordered, void* stream);
+
 int sb_cuba_bwd(const float* grad_spike, const float* voltage, const float* thr_tensor, float thr,
                 const float* current, const float* cdecay, int64_t n_cdecay, const float* vdecay,
                 int64_t n_vdecay, float* grad_x, float* grad_cdecay, float* grad_vdecay, void* scratch_c,

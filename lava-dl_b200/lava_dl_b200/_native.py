@@ -85,6 +85,7 @@ SIGNATURES = {
     'sb_conv_wgrad_scratch_bytes': (_I64, [_I64] * 7),
     'sb_conv_wgrad': (c_int, [_P, _P, _P, _P] + [_I64] * 10 + [_P]),
     'sb_conv_wgrad_fits': (c_int, [_I64] * 10),
+    'sb_unpack_spikes_host': (c_int, [_P, _P, _I64, _I64, c_int, c_int, _P]),
     'sb_broadcast_fill': (c_int, [_P, _P, _I64, _P]),
     'sb_shift_fir_bwd': (c_int, [_P, _P, _I64, c_float, c_float, _P, _I64, c_float, _P, _I64, _I64, _P]),
 }

@@ -475,12 +475,31 @@ def cuba_fwd_packed(x, cdecay, vdecay, cstate, vstate, threshold, w_scale, want_
     return dict(spike_bits=bits, voltage=vol, final_c=fc, final_v=fv, final_s=fs)
 
 
-def unpack_spikes(bits, T):
-    """fp32 0/1 tensor ``bits.shape[:-1] + (T,)`` from the packed words of ``cuba_fwd_packed``
-    (plain torch ops, on whatever device ``bits`` lives)."""
-    shifts = torch.arange(32, device=bits.device, dtype=torch.int32)
-    b = (bits.unsqueeze(-1) >> shifts) & 1
-    return b.reshape(bits.shape[:-1] + (-1,))[..., :T].to(torch.float32)
+def unpack_spikes(bits, T, out=None, stream=None, threads=0):
+    """fp32 0/1 tensor ``bits.shape[:-1] + (T,)`` from the packed words of ``cuba_fwd_packed``.
+
+    CUDA ``bits``: plain torch ops on the device.  CPU ``bits`` (the result copied to the host as
+    bits, 1/32 of the bytes): expanded by the library on ``threads`` CPU threads (0 = all) into
+    ``out`` (allocated when ``None``).  With ``stream`` (a ``torch.cuda.Stream``) the expansion is
+    queued on that stream as a host function -- after a non-blocking copy of the bits queued there
+    before, before anything queued later -- and ``out`` is complete once the stream has passed it."""
+    if bits.is_cuda:
+        shifts = torch.arange(32, device=bits.device, dtype=torch.int32)
+        b = (bits.unsqueeze(-1) >> shifts) & 1
+        return b.reshape(bits.shape[:-1] + (-1,))[..., :T].to(torch.float32)
+    if bits.dtype != torch.int32 or not bits.is_contiguous() or bits.shape[-1] != (T + 31) // 32:
+        raise ValueError('bits must be a contiguous int32 tensor with ceil(T / 32) words per row')
+    shape = tuple(bits.shape[:-1]) + (T,)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32)
+    elif tuple(out.shape) != shape or out.dtype != torch.float32 or not out.is_contiguous() or out.is_cuda:
+        raise ValueError(f'out must be a contiguous fp32 CPU tensor of shape {shape}')
+    rows = bits.numel() // max(bits.shape[-1], 1)
+    rc = N.load().sb_unpack_spikes_host(c_void_p(bits.data_ptr()), c_void_p(out.data_ptr()), rows, T, int(threads),
+                                        0 if stream is None else 1, c_void_p(0 if stream is None else stream.cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f'sb_unpack_spikes_host failed ({rc}): {N.last_error()}')
+    return out
 
 
 def cuba_bwd(grad_spike, voltage, threshold, current, cdecay, vdecay, tau_rho, scale_rho, graded, need_decay_grad,

@@ -195,3 +195,26 @@ def test_graphed_replay_of_an_inference_call(cuda, slayer):
     keeper = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03, persistent_state=True).to(cuda)
     with pytest.raises(RuntimeError):
         slayer.utils.Graphed(keeper, x0)
+
+
+def test_packed_result_expanded_on_the_host_in_stream_order(cuda, slayer):
+    """A packed inference result copied to the host as bits and expanded there by the library,
+    queued on the copy's stream: once the stream is through, the host tensor is what ``forward``
+    returns (1/32 of the bytes crossed PCIe)."""
+    gen = torch.Generator().manual_seed(11)
+    neuron = slayer.neuron.cuba.Neuron(threshold=1.25, current_decay=0.25, voltage_decay=0.03).to(cuda)
+    x = torch.empty(3, 200, 333).normal_(0.3, 1.0, generator=gen).to(cuda)
+    with torch.no_grad():
+        want = neuron(x).cpu()
+        bits = neuron.forward_packed(x)
+    side = torch.cuda.Stream(cuda)
+    side.wait_stream(torch.cuda.current_stream(cuda))
+    bits_host = torch.empty(bits.shape, dtype=torch.int32, pin_memory=True)
+    out = torch.full(want.shape, -1.0).pin_memory()
+    with torch.cuda.stream(side):
+        bits_host.copy_(bits, non_blocking=True)
+        got = slayer.utils.unpack_spikes(bits_host, x.shape[-1], out=out, stream=side)
+    side.synchronize()
+    assert got is out
+    assert_exact(out, want.numpy(), 'host expansion of the packed spikes')
+    assert_exact(slayer.utils.unpack_spikes(bits_host, x.shape[-1]), want.numpy(), 'synchronous host expansion')

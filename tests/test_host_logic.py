@@ -201,3 +201,23 @@ def test_replicate_matches_reference():
         assert (x.grad == steps).all()
     with pytest.raises(NotImplementedError):
         replicate(torch.zeros(3), 4)
+
+
+def test_unpack_spikes_on_the_host():
+    """Packed spike words expanded on the CPU by the library (no GPU involved): every bit lands at
+    step 32 w + i of its row, rows whose length is no multiple of 32 stop at T, any thread count."""
+    import torch
+    from lava_dl_b200 import _ops
+    gen = torch.Generator().manual_seed(3)
+    for shape, T in (((3, 5), 77), ((2, 4, 6), 64), ((7,), 1), ((1, 33), 300), ((0, 4), 40)):
+        words = (T + 31) // 32
+        bits = torch.randint(-2 ** 31, 2 ** 31 - 1, shape + (words,), generator=gen, dtype=torch.int64).to(torch.int32)
+        shifts = torch.arange(32, dtype=torch.int32)
+        want = ((bits.unsqueeze(-1) >> shifts) & 1).reshape(shape + (32 * words,))[..., :T].to(torch.float32)
+        for threads in (1, 3, 0):
+            got = _ops.unpack_spikes(bits, T, threads=threads)
+            assert got.shape == want.shape and torch.equal(got, want)
+        out = torch.full(shape + (T,), -1.0)
+        assert _ops.unpack_spikes(bits, T, out=out) is out and torch.equal(out, want)
+    with pytest.raises(ValueError):
+        _ops.unpack_spikes(torch.zeros(2, 3, dtype=torch.int32), 200)
