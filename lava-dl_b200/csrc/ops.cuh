@@ -689,6 +689,21 @@ struct AlifFwd {
     c = (FAST ? mul_shift12_pos(c, cmul) : mul_shift12(c, cmul)) + to_fixed(w, a[0]);
     v = (FAST ? mul_shift12_pos(v, vmul) : mul_shift12(v, vmul)) + c;
     s.template decay<FAST>();
+    if constexpr ((LEAN || MARGIN) && !GRADED) {
+      // The spike compares voltage / w with threshold / w + refractory / w in fp32; w is a power of two here, and
+      // scaling by a power of two commutes with fp32 rounding, so the comparison (and the margin, scaled once
+      // at the end) is taken on the unscaled conversions: the same bits with two or three multiplies fewer.
+      const float vi = __int2float_rn(v);
+      const float ti = __fadd_rn(__int2float_rn(s.th_new), __int2float_rn(s.ref_new));
+      last_s = (vi >= ti) ? 1.f : 0.f;
+      if constexpr (LEAN) {
+        b[0] = last_s;
+      } else {
+        b[0] = __fmul_rn(__fsub_rn(vi, ti), inv_w); b[1] = last_s;
+      }
+      s.commit(v >= s.th_new + s.ref_new);
+      return;
+    }
     const float vf = from_fixed<true>(v, w, inv_w);
     const float thf = from_fixed<true>(s.th_new, w, inv_w);
     const float reff = from_fixed<true>(s.ref_new, w, inv_w);
@@ -779,6 +794,23 @@ struct RfFwd {
     r.keep();
     const float ref_ = from_fixed<true>(r.re, w, inv_w);
     const float imf = from_fixed<true>(r.im, w, inv_w);
+    if constexpr (ADAPT && (LEAN || MARGIN) && !GRADED) {
+      // as in the ALIF kernel: compare (and subtract) before the power-of-two scaling, the same bits
+      s.template decay<FAST>();
+      const float rei = __int2float_rn(r.re);
+      const float ti = __fadd_rn(__int2float_rn(s.th_new), __int2float_rn(s.ref_new));
+      const bool sp = (rei >= ti) && im_prev_neg && (r.im >= 0);
+      last_s = sp ? 1.f : 0.f;
+      if constexpr (LEAN) {
+        b[0] = last_s;
+      } else {
+        b[0] = __fmul_rn(__fsub_rn(rei, ti), inv_w); b[1] = imf; b[2] = last_s;
+      }
+      s.commit(r.re >= s.th_new + s.ref_new && r.im >= 0 && im_old_i < 0);
+      im_old_i = r.im;
+      im_prev_neg = r.im < 0;
+      return;
+    }
     if (ADAPT) {
       s.template decay<FAST>();
       const float thf = from_fixed<true>(s.th_new, w, inv_w);
