@@ -32,7 +32,8 @@
 //   producer (1 thread): one TMA box per input row into a ring of row slots --
 //     the kh rows a tile reads plus the rows requested ahead.
 //   scan (4 warps): reads each landed row once with 128-bit loads, decides
-//     whether it needs lo parts and writes them if so (ring of kh + 2 lo slots).
+//     whether it needs lo parts and writes them if so (ring of kh + 2 lo slots, taken only by
+//     rows that need one: rows of spikes are scanned as far ahead as the row ring reaches).
 //   issue (3 threads, taking tiles in turn): kh x kw x ceil(Ci / 8) MMAs (kind::tf32, M128, N = Co
 //     padded to 16) per tile into a ring of TMEM accumulators; B (the weights, split, K-major,
 //     128-byte swizzle) is built once per CTA in shared memory.  An MMA with an M-major operand
@@ -126,14 +127,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   const int off_bar = off_lo + RL * g.slot_bytes;
   const uint32_t bar_full = base + off_bar;                // [R]   a row has landed
   const uint32_t bar_rawfree = bar_full + 8 * kMaxRing;    // [R]   no MMA reads the row any more
-  const uint32_t bar_ready = bar_rawfree + 8 * kMaxRing;   // [RL]  the row is scanned (and split)
-  const uint32_t bar_lofree = bar_ready + 8 * kMaxLo;      // [RL]
+  const uint32_t bar_ready = bar_rawfree + 8 * kMaxRing;   // [R]   the row is scanned (and split)
+  const uint32_t bar_lofree = bar_ready + 8 * kMaxRing;    // [RL]  a lo slot is read no more
   const uint32_t bar_mma = bar_lofree + 8 * kMaxLo;        // [NACC]
   const uint32_t bar_accfree = bar_mma + 8 * kMaxAcc;      // [NACC]
-  constexpr int kBarBytes = 8 * (2 * kMaxRing + 2 * kMaxLo + 2 * kMaxAcc);
+  constexpr int kBarBytes = 8 * (3 * kMaxRing + kMaxLo + 2 * kMaxAcc);
   volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(sm + off_bar + kBarBytes);
   volatile int* dead = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 4);
-  volatile int* has_lo = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 8);  // [RL]
+  // [R] per row slot: 0 = the row is exact in TF32, else 1 + the lo slot that holds its lo parts
+  volatile int* has_lo = reinterpret_cast<volatile int*>(sm + off_bar + kBarBytes + 8);
   const uint32_t NACC = (uint32_t)(kTmemCols / g.npad) < (uint32_t)kMaxAcc ? (uint32_t)(kTmemCols / g.npad)
                                                                            : (uint32_t)kMaxAcc;
 
@@ -141,11 +143,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
     for (uint32_t i = 0; i < R; ++i) {
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_rawfree + 8 * i, 4);     // one arrival per drain warp
-    }
-    for (uint32_t i = 0; i < RL; ++i) {
       mbar_init(bar_ready + 8 * i, kM);
-      mbar_init(bar_lofree + 8 * i, 4);
     }
+    for (uint32_t i = 0; i < RL; ++i) mbar_init(bar_lofree + 8 * i, 4);
     for (int i = 0; i < kMaxAcc; ++i) {
       mbar_init(bar_mma + 8 * i, 1);
       mbar_init(bar_accfree + 8 * i, kM);
@@ -230,7 +230,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
       const uint32_t bhi = desc_lo(base + off_bhi), blo = desc_lo(base + off_blo);
       const uint32_t a_deschi = kDescHiMMajor;
       const uint32_t box16 = (uint32_t)(g.npad * 128) >> 4;   // one 32-column box of the factor, in 16-byte units
-      Cursor rq{0, 0}, lq{0, 0}, cd{0, 0};   // oldest live row, its lo slot, accumulators
+      Cursor rq{0, 0}, cd{0, 0};   // oldest live row, accumulators
       uint32_t last_acc = 0, last_phase = 0, tiles = 0, turn = 0;   // turn: whose tile this is
       bool ok = true;
       for (int64_t item = blockIdx.x; item < nitems; item += gridDim.x) {
@@ -240,7 +240,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           if (!mine) {
             cd.next(NACC);
             rq.next(R);
-            lq.next(RL);
             continue;
           }
           const uint32_t acc = cd.slot;
@@ -248,14 +247,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           const uint32_t d_tmem = tmem + acc * (uint32_t)g.npad;
           // rows ho .. ho + KH - 1 of this item (all of them are waited for: the tile before this one was
           // another thread's)
-          uint32_t rs[KH], ls[KH];
+          uint32_t rs[KH];
           {
-            Cursor r = rq, l = lq;
+            Cursor r = rq;
 #pragma unroll
-            for (int i = 0; i < KH; ++i, r.next(R), l.next(RL)) {
-              ok = wait_or_dead(bar_ready + 8 * l.slot, l.wraps & 1u, dead) && ok;
+            for (int i = 0; i < KH; ++i, r.next(R)) {
+              ok = wait_or_dead(bar_ready + 8 * r.slot, r.wraps & 1u, dead) && ok;
               rs[i] = r.slot;
-              ls[i] = l.slot;
             }
           }
           tc_fence_after();
@@ -264,8 +262,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
 #pragma unroll
             for (int i = 0; i < KH; ++i) {
               const uint32_t row_hi = base + off_ring + rs[i] * g.slot_bytes;
-              const uint32_t row_lo = base + off_lo + ls[i] * g.slot_bytes;
-              const bool alo = has_lo[ls[i]] != 0;
+              const int lo_slot = has_lo[rs[i]] - 1;
+              const bool alo = lo_slot >= 0;
+              const uint32_t row_lo = base + off_lo + (alo ? lo_slot : 0) * g.slot_bytes;
               // MMA m of this kernel row reads the slot's rows 8 m .. 8 m + 7 (the next output column
               // starts one column further on: the leading offset).  Three loops with run-time trip
               // counts rather than three conditional MMAs per step: a predicated-off MMA still takes
@@ -297,10 +296,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
           last_acc = acc; last_phase = cd.wraps & 1u; ++tiles;
           cd.next(NACC);
           rq.next(R);
-          lq.next(RL);
         }
         // the item's last KH - 1 rows belong to no further tile
-        for (int q = g.Ho; q < Q; ++q) { rq.next(R); lq.next(RL); }
+        for (int q = g.Ho; q < Q; ++q) rq.next(R);
       }
       // nothing may still be writing TMEM when it is freed: wait for this thread's last tile
       if (tiles >= 1) mbar_wait(bar_mma + 8 * last_acc, last_phase);
@@ -309,10 +307,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
   } else if (warp < 4) {
     // ---------------- scan warps: does a landed row need lo parts? ----------------
     // Each thread reads its 16-byte words of the slot (the same offsets in the lo slot: both
-    // start on a 1024-byte boundary, so the swizzle pattern is the same).
+    // start on a 1024-byte boundary, so the swizzle pattern is the same).  Only a row that needs
+    // lo parts takes a lo slot (the next of their ring) and waits for it; rows of spikes run as far
+    // ahead of the tiles as the row ring allows.
     Cursor rq{0, 0}, lq{0, 0};
     for (int64_t item = blockIdx.x; item < nitems; item += gridDim.x) {
-      for (int q = 0; q < Q; ++q, rq.next(R), lq.next(RL)) {
+      for (int q = 0; q < Q; ++q, rq.next(R)) {
         wait_or_dead(bar_full + 8 * rq.slot, rq.wraps & 1u, dead);
         uint8_t* row = sm + off_ring + rq.slot * g.slot_bytes;
         uint32_t low = 0;
@@ -329,9 +329,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
             : "=r"(any)
             : "r"(low & ~kTf32Mask), "n"(kM)
             : "memory");
-        // the lo slot (and its flag) of the row that used it KH + 2 rows ago is free?
-        if (lq.wraps >= 1) wait_or_dead(bar_lofree + 8 * lq.slot, (lq.wraps - 1u) & 1u, dead);
+        int flag = 0;
         if (any) {
+          // the lo slot's previous row is read no more?
+          if (lq.wraps >= 1) wait_or_dead(bar_lofree + 8 * lq.slot, (lq.wraps - 1u) & 1u, dead);
           // hi = x truncated to TF32 stays in the row's own slot, lo = x - hi (exact) goes to the lo slot
           uint8_t* lorow = sm + off_lo + lq.slot * g.slot_bytes;
           for (int off = tid * 16; off < g.box_bytes; off += kM * 16) {
@@ -345,16 +346,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
             *reinterpret_cast<uint4*>(lorow + off) = l;
           }
           fence_proxy_async();   // the MMAs read what these stores wrote
+          flag = 1 + (int)lq.slot;
+          lq.next(RL);
         }
-        if (tid == 0) has_lo[lq.slot] = any;
-        mbar_arrive(bar_ready + 8 * lq.slot);
+        if (tid == 0) has_lo[rq.slot] = flag;
+        mbar_arrive(bar_ready + 8 * rq.slot);
       }
     }
   } else {
     // ---------------- drain warps: accumulator -> output rows ----------------
     const int m = tid - kM, wl = m >> 5, tl = m & 31;
     const int ew = warp & 3;
-    Cursor cd{0, 0}, rq{0, 0}, lq{0, 0};
+    Cursor cd{0, 0}, rq{0, 0};
     const int64_t cstride = (int64_t)g.Ho * g.Wo * g.T;
     const int64_t rstride = (int64_t)g.Wo * g.T;
     const int nco = min(g.npad, g.Co - co0);
@@ -371,9 +374,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict
         // row any more, nor, after an item's last tile, its other rows.
         if (lane == 0) {
           const int nfree = (ho == g.Ho - 1) ? KH : 1;
-          for (int i = 0; i < nfree; ++i, rq.next(R), lq.next(RL)) {
+          for (int i = 0; i < nfree; ++i, rq.next(R)) {
+            const int lo_slot = has_lo[rq.slot] - 1;    // read before the row slot is handed back
             mbar_arrive(bar_rawfree + 8 * rq.slot);
-            mbar_arrive(bar_lofree + 8 * lq.slot);
+            if (lo_slot >= 0) mbar_arrive(bar_lofree + 8 * lo_slot);
           }
         }
         const uint32_t taddr = tmem + ((uint32_t)(ew * 32) << 16) + acc * (uint32_t)g.npad;
@@ -451,7 +455,7 @@ TcPlan plan_block(int64_t N, int64_t Ci, int64_t cb, int64_t Co, int64_t H, int6
   const int64_t slot = (box_bytes + 1023) & ~1023LL;
   const int64_t ktot = kh * nm * 8;
   const int64_t b_bytes = (((ktot + 31) / 32) * npad * 128 + 1023) & ~1023LL;
-  const int64_t fixed = 2 * b_bytes + 8 * (2 * kMaxRing + 2 * kMaxLo + 2 * kMaxAcc) + 128 + 1024 + (kh + 2) * slot;
+  const int64_t fixed = 2 * b_bytes + 8 * (3 * kMaxRing + kMaxLo + 2 * kMaxAcc) + 128 + 1024 + (kh + 2) * slot;
   // rows in flight beyond the kh live ones: as many as fit in 224 KB, at most 16, at least 2
   int64_t ahead = (224 * 1024 - fixed) / slot - kh;
   if (ahead > 16) ahead = 16;
