@@ -56,6 +56,13 @@ using namespace sb;
 
 namespace {
 
+// The filter's waits sleep 64 ns from the third failed poll on: the waiting warps of the other roles then
+// leave the issue slots of their scheduler to the warp that works (1.7 % faster than with 64 polls before
+// the first sleep of 32 ns; sleeping from the first poll on is slower again).
+__device__ __forceinline__ bool wait_fir(uint32_t bar, uint32_t parity, volatile int* dead) {
+  return wait_or_dead(bar, parity, dead, 1u, 64u);
+}
+
 constexpr int kM = 128;                  // rows per block = MMA M
 constexpr int kN = 32;                   // outputs per tile = steps per box
 constexpr int kBoxBytes = kM * kN * 4;   // 16 KB
@@ -170,7 +177,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       uint32_t use = 0;
       int64_t f = 0;
       for (; f < total; ++f) {
-        if (use >= 1 && !wait_or_dead(bar_rawfree + 8 * slot, (use - 1u) & 1u, dead)) break;
+        if (use >= 1 && !wait_fir(bar_rawfree + 8 * slot, (use - 1u) & 1u, dead)) break;
         const uint32_t bar = bar_full + 8 * slot;
         mbar_expect_tx(bar, kBoxBytes);
         tma_load_2d(base + kOffRaw + slot * kBoxBytes, &xmap, kN * (a - 2 + qoff), row0, bar);
@@ -196,8 +203,8 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
           if (tcount % kNumIssue == me) {
             const uint32_t acc = me;
             bool ok2;
-            ok2 = wait_or_dead(bar_aready + 8 * as, ause & 1u, dead);
-            if (tcount >= kNumIssue) ok2 = wait_or_dead(bar_free + 8 * acc, (tcount / kNumIssue - 1u) & 1u, dead) && ok2;
+            ok2 = wait_fir(bar_aready + 8 * as, ause & 1u, dead);
+            if (tcount >= kNumIssue) ok2 = wait_fir(bar_free + 8 * acc, (tcount / kNumIssue - 1u) & 1u, dead) && ok2;
             tc_fence_after();
             if (ok2) {
               const uint32_t d_tmem = tmem + acc * kAccCols;
@@ -252,7 +259,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         p0 = p1 = p2 = 0;
       }
       if (++a == narr) { a = 0; blk += gridDim.x; }
-      wait_or_dead(bar_full + 8 * slot, use & 1u, dead);
+      wait_fir(bar_full + 8 * slot, use & 1u, dead);
       const uint8_t* rowp = sm + kOffRaw + slot * kBoxBytes + tid * 128;
       uint32_t xr[32];
       uint32_t low = 0;
@@ -290,7 +297,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
         p0 = n0; p1 = n1; p2 = n2;
       }
       // the MMAs that read this operand slot's previous box have completed?
-      if (ause >= 1) wait_or_dead(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
+      if (ause >= 1) wait_fir(bar_afree + 8 * as, (ause - 1u) & 1u, dead);
       tc_fence_after();
       if (any) {
         uint32_t hl[64];
@@ -329,7 +336,7 @@ fir_tc_kernel(const __grid_constant__ CUtensorMap xmap, const float* __restrict_
       for (int tile = 0; tile < ntile; ++tile, ++tcount) {
         const int acc = (int)(tcount % kNumIssue);
         bool ok;
-        ok = wait_or_dead(bar_mma + 8 * acc, (tcount / kNumIssue) & 1u, dead);
+        ok = wait_fir(bar_mma + 8 * acc, (tcount / kNumIssue) & 1u, dead);
         tc_fence_after();
         // This warp has now seen every tile up to this one complete, so nothing reads the tile's
         // oldest box any more (nor, after a block's last tile, the two newer ones): the operand

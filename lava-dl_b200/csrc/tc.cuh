@@ -64,12 +64,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // Bounded wait that also gives up as soon as any thread of the CTA has given up
 // (the dead flag), so that one lost transfer costs one time-out, not one per wait.
-__device__ __forceinline__ bool wait_or_dead(uint32_t bar, uint32_t parity, volatile int* dead) {
+// `polls` failed polls pass before the first sleep of `nap` nanoseconds.
+__device__ __forceinline__ bool wait_or_dead(uint32_t bar, uint32_t parity, volatile int* dead, uint32_t polls = 64u,
+                                             uint32_t nap = 32u) {
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) {
+    if (it > polls) {
       if (*dead) return false;
-      __nanosleep(it > 4096 ? 256 : 32);
+      __nanosleep(it > 4096 ? 256 : nap);
     }
   }
   *dead = 1;
