@@ -200,6 +200,34 @@ def test_conv_kernel_matches_conv3d(shape, co, k, pad, cuda):
     assert_close(gw, wd.grad.numpy(), 'weight gradient of floats', scale=mw.grad.numpy() + 1e-30)
 
 
+@pytest.mark.parametrize('shape,co,k,pad', [((3, 16, 9, 10, 64), 32, 3, 1), ((2, 2, 12, 9, 96), 16, 5, 2)])
+def test_conv_tensor_cores_with_spike_rows_and_float_rows_mixed(shape, co, k, pad, cuda):
+    """Input rows of spikes (exact in TF32: no lo slot) interleaved with rows of floats (split into hi + lo,
+    each taking the next lo slot of the ring): the tensor-core kernel against the fp32 kernel, exact where a
+    whole receptive field is spikes, 1e-5 of the term magnitudes elsewhere."""
+    import torch.nn.functional as F
+    from lava_dl_b200 import _ops
+    from _util import assert_close
+    gen = torch.Generator().manual_seed(11 + sum(shape))
+    x = (torch.rand(shape, generator=gen) < 0.3).float()
+    floats = torch.randn(shape, generator=gen)
+    # image rows 1, 2 and 5 of every sample, and every row of the last sample's even channels, hold floats
+    mask = torch.zeros(shape, dtype=torch.bool)
+    mask[:, :, [1, 2, 5]] = True
+    mask[-1, ::2] = True
+    x = torch.where(mask, floats, x).to(cuda)
+    w = (torch.randint(-128, 127, (co, shape[1], k, k, 1), generator=gen).float() / 32).to(cuda)
+    tc = _ops.conv_fwd(x, w, (pad, pad), path=1)
+    ref = _ops.conv_fwd(x, w, (pad, pad), path=0)
+    mag = _ops.conv_fwd(x.abs(), w.abs(), (pad, pad), path=0)
+    assert_close(tc, ref, 'mixed rows, tensor cores against fp32 kernel', scale=mag.cpu().numpy() + 1e-30)
+    # output rows whose receptive field holds no float row: identical sums (sample 0: input rows 0 and 3, 4, 6..)
+    touched = F.max_pool3d(mask.float().amax(1, keepdim=True), (k, k, 1), 1, (pad, pad, 0)).to(cuda) > 0
+    clean = ~touched.expand_as(tc)
+    assert clean.any()
+    assert torch.equal(tc[clean], ref[clean])
+
+
 def test_block_axon_delay_fused_matches_unfused(cuda):
     """A CUBA dense block with a bounded axonal delay writes step delay and axonal
     delay inside the neuron kernel; an unbounded delay takes the separate shift.
